@@ -1,0 +1,156 @@
+/*
+ * mind_b200.h -- C ABI of libmind_b200: MIND's deterministic integer BLAS
+ * (int8 / int16 / Q16.16 GEMM, GEMV, dot) on NVIDIA B200 (sm_100a).
+ *
+ * Every entry point follows the calling convention of MIND's `__mind_blas_*`
+ * compiler intrinsics: all arguments and the result are int64_t, pointers are raw
+ * addresses cast to int64_t, matrices are dense row-major without a leading-
+ * dimension argument, B is the UN-transposed K x N operand, the caller owns every
+ * buffer and the output is fully overwritten.  Citations name files of the
+ * reference project (star-ga/mind) whose interface each symbol replaces.
+ *
+ * Pointers may be HOST addresses (the reference's semantics: the call copies the
+ * operands to the GPU, computes, copies the result back and returns when it is in
+ * place) or DEVICE addresses of the current CUDA device (the call only enqueues
+ * work on the library's stream, see mind_b200_set_stream; the result is complete in
+ * stream order).  Each pointer of a call is classified on its own, so host and
+ * device operands may be mixed; a call with any host pointer is synchronous.
+ *
+ * Results are bit-identical to the reference's rules: exact 64-bit sums truncated
+ * once to int32 (two's-complement wrap, never saturation); Q16.16 products are
+ * shifted right by 16 (arithmetic) BEFORE they are added.
+ *
+ * Errors: kernels return 0 on success, as the reference's do.  On failure they
+ * return a negative MIND_B200_ERR_* code, never abort, and leave a message for
+ * mind_b200_last_error() (thread-local, like mind_last_error in src/ffi/mod.rs:172-181
+ * of the reference).  There is no CPU fallback: without a usable B200 every compute
+ * entry point fails with MIND_B200_ERR_NO_DEVICE.  The dot entry points return the
+ * dot value itself, so they report failure only through mind_b200_last_error()
+ * (and return 0, as the reference's dot does on bad input,
+ * runtime-support/mind_intrinsics.c:1538).
+ */
+#ifndef MIND_B200_H
+#define MIND_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MIND_B200_OK 0
+#define MIND_B200_ERR_INVALID (-1)    /* null pointer with non-empty shape, negative size, ... */
+#define MIND_B200_ERR_CUDA (-2)       /* a CUDA runtime / driver call failed                  */
+#define MIND_B200_ERR_NO_DEVICE (-3)  /* no CUDA device, or the device is not sm_100           */
+#define MIND_B200_ERR_TIMEOUT (-4)    /* a bounded in-kernel wait ran out; result is invalid   */
+#define MIND_B200_ERR_TOO_LARGE (-5)  /* shape beyond a documented limit                       */
+
+/* ---- int8 GEMM:  C[i,j] = (i32) sum_k (i64)A[i,k] * (i64)B[k,j] -------------------------
+ * a: M x K int8, b: K x N int8, c: M x N int32.
+ * Replaces __mind_blas_matmul_mm_i8_v (src/mlir/lowering.rs:7687-7752, registry
+ * src/type_checker/mod.rs:2304) and its multithreaded twin __mind_blas_matmul_mm_i8_mt_v
+ * (src/mlir/lowering.rs:10368, registry :2310); the two are the same kernel here. */
+int64_t __mind_blas_matmul_mm_i8_v(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n);
+int64_t __mind_blas_matmul_mm_i8_mt_v(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n);
+
+/* ---- Q16.16 GEMM:  C[i,j] = (i32) sum_k ( ((i64)A[i,k] * (i64)B[k,j]) >> 16 ) -----------
+ * a, b, c: int32 holding Q16.16.  Replaces __mind_blas_matmul_mm_q16_v
+ * (src/mlir/lowering.rs:9300-9407, registry src/type_checker/mod.rs:2316) and
+ * __mind_blas_matmul_mm_q16_mt_v (src/mlir/lowering.rs:10019-10341, registry :2322). */
+int64_t __mind_blas_matmul_mm_q16_v(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n);
+int64_t __mind_blas_matmul_mm_q16_mt_v(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n);
+
+/* ---- Q16.16 GEMV:  scores[i] = (i32) sum_k ( (catalog[i,k] * query[k]) >> 16 ) -----------
+ * Replaces __mind_blas_gemv_q16_mt (src/mlir/lowering.rs:10019-10032, :9822-9996, registry
+ * src/type_checker/mod.rs:2332) and __mind_blas_matmul_rmajor_q16_v (src/mlir/lowering.rs:6675,
+ * registry :2294): same rule, same argument order (matrix, vector, out, rows, cols). */
+int64_t __mind_blas_gemv_q16_mt(int64_t catalog, int64_t query, int64_t scores, int64_t m, int64_t k);
+int64_t __mind_blas_matmul_rmajor_q16_v(int64_t w, int64_t x, int64_t y, int64_t rows, int64_t cols);
+
+/* ---- int16 GEMV:  y[r] = (i32) sum_i (i64)W[r,i] * (i64)x[i]  (no shift) ------------------
+ * Replaces __mind_blas_matmul_rmajor_i16_v (src/mlir/lowering.rs:10723, registry
+ * src/type_checker/mod.rs:2285). */
+int64_t __mind_blas_matmul_rmajor_i16_v(int64_t w, int64_t x, int64_t y, int64_t rows, int64_t cols);
+
+/* ---- dots: return (i64)(i32)acc -------------------------------------------------------------
+ * __mind_blas_dot_q16_v     src/mlir/lowering.rs:5695-5830, registry src/type_checker/mod.rs:2271
+ *                           (same value as __mind_blas_dot_q16, runtime-support/mind_intrinsics.c:1459-1547)
+ * __mind_blas_dot_l1_q16_v  src/mlir/lowering.rs:6057, registry :2260: sum |a[i] - b[i]|
+ * __mind_blas_dot_i16_v     src/mlir/lowering.rs:5861-6033, registry :2246 */
+int64_t __mind_blas_dot_q16_v(int64_t a, int64_t b, int64_t len);
+int64_t __mind_blas_dot_l1_q16_v(int64_t a, int64_t b, int64_t len);
+int64_t __mind_blas_dot_i16_v(int64_t a, int64_t b, int64_t len);
+
+/* ---- int16 GEMM:  C[i,j] = (i32) sum_k (i64)A[i,k] * (i64)B[k,j] -------------------------
+ * The reference has NO int16 GEMM; this composes its int16 row rule
+ * (benches/det_matmul_i16.rs:218-231, src/mlir/lowering.rs:5861) over the columns of an
+ * un-transposed K x N B, the layout of its int8 and Q16.16 GEMMs.  New symbol name. */
+int64_t __mind_b200_matmul_mm_i16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n);
+
+/* ---- names of the reference's identity-gate library -----------------------------------------
+ * The gate compiles a MIND source whose public functions wrap the intrinsics
+ * (tests/cross_substrate_identity.rs:69-144) and its drivers dlsym these names
+ * (tests/cross_substrate_identity/xnode_driver.c:148-156).  Exported so that the unmodified
+ * driver runs against this library.  NOTE gemmq takes B TRANSPOSED (N x K), as the gate's does
+ * (:82-94); gemmqmm and gemmq_kn take the un-transposed K x N B. */
+int64_t dotq(int64_t a, int64_t b, int64_t n);
+int64_t dotl1q(int64_t a, int64_t b, int64_t n);
+int64_t doti16(int64_t a, int64_t b, int64_t n);
+int64_t mmq(int64_t w, int64_t x, int64_t y, int64_t rows, int64_t cols);
+int64_t mmi16(int64_t w, int64_t x, int64_t y, int64_t rows, int64_t cols);
+int64_t gemvq(int64_t catalog, int64_t query, int64_t scores, int64_t m, int64_t k);
+int64_t gemmq(int64_t a, int64_t bt, int64_t c, int64_t m, int64_t k, int64_t n);
+int64_t gemmq_kn(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n);
+int64_t gemmqmm(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n);
+int64_t gemmi8(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n);
+int64_t gemmi8mt(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n);
+
+/* ---- library control (no counterpart in the reference's intrinsic surface) -------------------- */
+/* Message of the calling thread's last failure, or NULL (src/ffi/mod.rs:172-181). */
+const char* mind_b200_last_error(void);
+/* CUDA stream (cudaStream_t cast to int64_t; 0 = the legacy default stream) that every later
+ * call on the CURRENT device uses.  Default: the legacy default stream. */
+int64_t mind_b200_set_stream(int64_t cuda_stream);
+/* Blocks until the library's stream on the current device is idle; reports a kernel
+ * time-out recorded since the last call (MindRuntime::synchronize, src/runtime_interface.rs:41). */
+int64_t mind_b200_synchronize(void);
+/* Number of usable (sm_100) devices; 0 when none, never an error. */
+int64_t mind_b200_device_count(void);
+/* Kernels launched by this library in this process so far. */
+int64_t mind_b200_kernel_launches(void);
+/* Pre-sizes the current device's scratch (operand re-layouts) and staging (host operands)
+ * buffers so that later calls allocate nothing. */
+int64_t mind_b200_reserve(int64_t scratch_bytes, int64_t staging_bytes);
+/* Which kernel the int8 / int16 GEMMs use: 0 = tensor cores (tcgen05, default),
+ * 1 = the independent CUDA-core kernel kept as an on-device cross-check. */
+int64_t mind_b200_set_gemm_path(int64_t path);
+
+/* ---- seeded inputs and large-shape checking on the device ------------------------------------- */
+/* Fills dst (device or host pointer) with elements [offset, offset + n) of the reference's
+ * generator stream (tests/cross_substrate_identity.rs:589-601): kind 0 = Q16.16 int32
+ * ((i32)u32 >> shift), 1 = int8, 2 = int16.  Element i uses the state after i + 1 steps from
+ * `seed`, so a second operand continues the first by passing offset = the first one's length. */
+int64_t mind_b200_lcg_fill(int64_t dst, int64_t n, int64_t kind, int64_t seed, int64_t offset, int64_t shift);
+/* out[r] = (i32) sum_c mat[r,c] * v[c] with 32-bit wrap; mat has elem_bytes in {1, 2, 4} (signed).
+ * Building block of the exact Freivalds check C.v == A.(B.v) in Z/2^32. */
+int64_t mind_b200_matvec_wrap(int64_t mat, int64_t elem_bytes, int64_t rows, int64_t cols, int64_t v, int64_t out);
+
+/* ---- MindRuntime mirror (src/runtime_interface.rs:26-52) ---------------------------------------
+ * allocate / run_op / synchronize / deallocate over device buffers.  Handles are the
+ * reference's TensorHandle (usize).  dtype codes: 0 = i8, 1 = i16, 2 = i32 (also Q16.16).
+ * run_op names are the intrinsic names without the "__mind_blas_" prefix
+ * ("matmul_mm_i8_v", "matmul_mm_q16_v", "gemv_q16_mt", "matmul_rmajor_i16_v", "matmul_mm_i16", ...);
+ * shapes are taken from the handles.  All return 0 or a negative code. */
+int64_t mind_b200_rt_allocate(int64_t dtype, const int64_t* shape, int64_t rank, int64_t* handle_out);
+int64_t mind_b200_rt_deallocate(int64_t handle);
+int64_t mind_b200_rt_upload(int64_t handle, const void* host_src, int64_t bytes);
+int64_t mind_b200_rt_download(int64_t handle, void* host_dst, int64_t bytes);
+int64_t mind_b200_rt_device_ptr(int64_t handle, int64_t* ptr_out);
+int64_t mind_b200_rt_run_op(const char* op, const int64_t* inputs, int64_t n_inputs,
+                            const int64_t* outputs, int64_t n_outputs);
+int64_t mind_b200_rt_synchronize(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MIND_B200_H */

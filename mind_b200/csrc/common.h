@@ -1,0 +1,112 @@
+// Host-side plumbing shared by every translation unit of libmind_b200:
+// status codes, the thread-local error message, the per-device context (stream,
+// scratch arena, device error word) and the launch counter.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/mind_b200.h"
+
+namespace mb200 {
+
+// Sets the calling thread's error message and returns `code`.
+int64_t fail(int64_t code, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
+void clear_error();
+
+#define MB200_CUDA(expr)                                                                   \
+    do {                                                                                   \
+        cudaError_t _e = (expr);                                                           \
+        if (_e != cudaSuccess)                                                             \
+            return ::mb200::fail(MIND_B200_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,       \
+                                 cudaGetErrorString(_e), __FILE__, __LINE__);              \
+    } while (0)
+
+#define MB200_TRY(expr)            \
+    do {                           \
+        int64_t _s = (expr);       \
+        if (_s != 0) return _s;    \
+    } while (0)
+
+// Grow-only device scratch: one allocation per device, reused by every call on
+// that device (calls on one device are serialised by the context lock).
+struct Arena {
+    char* base = nullptr;
+    size_t cap = 0;
+    size_t used = 0;
+};
+
+struct DeviceCtx {
+    int device = -1;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;  // the stream every launch and copy goes to
+    Arena scratch;                  // operand re-layouts (transposed B, limb planes, padded A)
+    Arena staging;                  // device copies of host-pointer operands
+    int* err_word = nullptr;        // device word a kernel sets when a bounded wait runs out
+    int* err_host = nullptr;        // pinned mirror of err_word
+};
+
+// Context of the CURRENT device (created on first use); nullptr + error set on failure.
+DeviceCtx* current_ctx();
+
+// Bump-allocates `bytes` (1024-byte aligned) from an arena, growing it if needed.
+// Growing frees the old block after a stream sync, so pointers handed out
+// earlier in the same call must be re-derived: reserve the total first.
+int64_t arena_reserve(DeviceCtx* ctx, Arena& a, size_t total_bytes);
+void* arena_take(Arena& a, size_t bytes);
+inline void arena_reset(Arena& a) { a.used = 0; }
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Kernel launch accounting (reported through mind_b200_kernel_launches()).
+void count_launch(int n = 1);
+
+// Checks the launch status of the last kernel and the device error word policy.
+int64_t check_launch(const char* what);
+
+// cuTensorMapEncodeTiled, resolved through the runtime (no link-time libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn();
+
+// ---- kernels' host launchers (device pointers only, asynchronous on ctx->stream) ----
+// int8 GEMM on tensor cores: C[M,N] (i32) = A[M,K] . Bt[N,K]^T, both operands
+// K-contiguous with row pitch `kp` bytes (kp % 16 == 0, bases 16-byte aligned).
+int64_t launch_gemm_i8_tc(DeviceCtx* ctx, const int8_t* a, const int8_t* bt, int32_t* c, int64_t m,
+                          int64_t n, int64_t k, int64_t kp_a, int64_t kp_b);
+// int16 GEMM as four 8-bit limb products on tensor cores; operands are limb planes.
+int64_t launch_gemm_i16_tc(DeviceCtx* ctx, const int8_t* a_hi, const uint8_t* a_lo,
+                           const int8_t* bt_hi, const uint8_t* bt_lo, int32_t* c, int64_t m,
+                           int64_t n, int64_t k, int64_t kp);
+// Re-layout kernels.
+int64_t launch_transpose_i8(DeviceCtx* ctx, const int8_t* b, int8_t* bt, int64_t k, int64_t n,
+                            int64_t kp);
+int64_t launch_pad_rows_i8(DeviceCtx* ctx, const int8_t* a, int8_t* ap, int64_t m, int64_t k,
+                           int64_t kp);
+int64_t launch_split_rows_i16(DeviceCtx* ctx, const int16_t* a, int8_t* hi, uint8_t* lo, int64_t m,
+                              int64_t k, int64_t kp);
+int64_t launch_split_transpose_i16(DeviceCtx* ctx, const int16_t* b, int8_t* bt_hi, uint8_t* bt_lo,
+                                   int64_t k, int64_t n, int64_t kp);
+// CUDA-core kernels.
+int64_t launch_gemm_q16(DeviceCtx* ctx, const int32_t* a, const int32_t* b, int32_t* c, int64_t m,
+                        int64_t k, int64_t n);
+int64_t launch_gemm_i8_simt(DeviceCtx* ctx, const int8_t* a, const int8_t* b, int32_t* c, int64_t m,
+                            int64_t k, int64_t n);
+int64_t launch_gemm_i16_simt(DeviceCtx* ctx, const int16_t* a, const int16_t* b, int32_t* c,
+                             int64_t m, int64_t k, int64_t n);
+int64_t launch_gemv_q16(DeviceCtx* ctx, const int32_t* w, const int32_t* x, int32_t* y,
+                        int64_t rows, int64_t cols);
+int64_t launch_gemv_i16(DeviceCtx* ctx, const int16_t* w, const int16_t* x, int32_t* y,
+                        int64_t rows, int64_t cols);
+int64_t launch_dist_l1_q16(DeviceCtx* ctx, const int32_t* a, const int32_t* b, int32_t* out,
+                           int64_t len);
+int64_t launch_lcg_fill(DeviceCtx* ctx, void* dst, int64_t n, int kind, uint64_t seed,
+                        uint64_t offset, int shift);
+int64_t launch_matvec_wrap(DeviceCtx* ctx, const void* mat, int elem_bytes, int64_t rows,
+                           int64_t cols, const int32_t* v, int32_t* out);
+
+}  // namespace mb200

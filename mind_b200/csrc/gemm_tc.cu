@@ -1,0 +1,424 @@
+// Tensor-core integer GEMM for sm_100a: C[M,N] (s32, wrap) = A[M,K] . Bt[N,K]^T.
+//
+// One persistent, warp-specialised kernel, written against tcgen05 directly:
+//   warp 0     : TMA producer  - cp.async.bulk.tensor tiles (128-byte swizzle) into a
+//                ring of shared-memory stages, completion on a "full" mbarrier;
+//   warp 1     : MMA issuer    - one thread issues tcgen05.mma kind::i8 from shared-
+//                memory descriptors into TMEM accumulators, tcgen05.commit frees the
+//                stage ("empty" mbarrier) and finally publishes the accumulator;
+//   warps 2..5 : epilogue      - tcgen05.ld the accumulator (each warp its 32 TMEM
+//                lanes = 32 output rows), combine, store int32 to global.
+// Tiles are 128 rows of A by BLOCK_N rows of Bt by 128 bytes of K per stage.
+// MODE 0 (int8):  one s8 x s8 product, BLOCK_N = 256, two accumulator stages so the
+//                 epilogue of tile t overlaps the main loop of tile t + 1.
+// MODE 1 (int16): operands arrive as 8-bit limb planes, a = 256*hi + lo with hi signed
+//                 and lo unsigned; four limb products go to three accumulators
+//                 (hi.hi | hi.lo + lo.hi | lo.lo) and the epilogue forms
+//                 (HH << 16) + (MID << 8) + LL with 32-bit wrap, which equals the
+//                 exact sum truncated to 32 bits.  Every partial stays below 2^31 for
+//                 K <= 2^15, and wrap inside an accumulator would be harmless anyway
+//                 (the tensor core does not saturate: descriptor bit 3 is 0).
+// The PAIR = 2 variant runs one tile on a pair of CTAs (a 2-CTA cluster,
+// tcgen05 cta_group::2): 256 rows of A (128 per CTA) by BLOCK_N rows of Bt, of which
+// each CTA stages only its half, which halves the shared-memory traffic per MMA.
+// Out-of-range rows / K tails are zero-filled by TMA; stores are predicated.
+// Every wait is bounded in time: when it runs out the kernel records a code in
+// the device error word, all roles leave their loops, and the kernel exits cleanly.
+#include "common.h"
+#include "ptx.cuh"
+
+namespace mb200 {
+using namespace ptx;
+
+namespace {
+
+constexpr int BLOCK_M = 128;            // rows of A per CTA
+constexpr int BLOCK_K = 128;            // bytes (= 8-bit elements) of K per stage
+constexpr int UMMA_K = 32;              // K of one tcgen05.mma kind::i8
+constexpr int TC_THREADS = 192;
+constexpr int A_TILE_BYTES = BLOCK_M * BLOCK_K;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+constexpr int GROUP_M = 16;             // m-tiles walked together, for L2 reuse
+
+template <int MODE, int PAIR>
+struct Cfg;
+template <>
+struct Cfg<0, 1> {
+    static constexpr int BLOCK_N = 256, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 2, STAGES = 4;
+};
+template <>
+struct Cfg<1, 1> {
+    static constexpr int BLOCK_N = 128, NA = 2, NB = 2, NACC = 3, ACC_STAGES = 1, STAGES = 3;
+};
+template <>
+struct Cfg<0, 2> {
+    static constexpr int BLOCK_N = 256, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 2, STAGES = 6;
+};
+template <>
+struct Cfg<1, 2> {
+    static constexpr int BLOCK_N = 128, NA = 2, NB = 2, NACC = 3, ACC_STAGES = 1, STAGES = 4;
+};
+
+struct TcParams {
+    int32_t* c;
+    int m, n, k;
+    int m_tiles, n_tiles;  // tile grid; an m-tile is PAIR * 128 rows
+    int vec_ok;            // C rows may be stored with 16-byte vectors
+    int* err;
+};
+
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_s,
+                                             int* err_g, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 63u) == 0u) {
+            if (*abort_s) return false;
+            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                *abort_s = 1;
+                atomicCAS(err_g, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& tm, int& tn) {
+    const int per_group = GROUP_M * n_tiles;
+    const int g = tile / per_group;
+    const int r = tile - g * per_group;
+    const int gm0 = g * GROUP_M;
+    const int gsize = min(GROUP_M, m_tiles - gm0);
+    tm = gm0 + r % gsize;
+    tn = r / gsize;
+}
+
+template <int MODE, int PAIR>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
+               const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
+               const TcParams p) {
+    using cfg = Cfg<MODE, PAIR>;
+    constexpr int BLOCK_N = cfg::BLOCK_N;
+    constexpr int B_ROWS = BLOCK_N / PAIR;  // rows of Bt this CTA stages
+    constexpr int B_TILE_BYTES = B_ROWS * BLOCK_K;
+    constexpr int STAGE_BYTES = cfg::NA * A_TILE_BYTES + cfg::NB * B_TILE_BYTES;
+    constexpr int STAGES = cfg::STAGES;
+    constexpr int ACC_STAGES = cfg::ACC_STAGES;
+    constexpr int ACC_COLS = cfg::NACC * BLOCK_N;  // TMEM columns per accumulator stage
+    constexpr int TMEM_COLS = 512;
+    static_assert(ACC_COLS * ACC_STAGES <= TMEM_COLS, "TMEM overflow");
+    constexpr int UMMA_M = BLOCK_M * PAIR;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t tiles0 = (raw + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
+    const uint32_t bars = tiles0 + STAGES * STAGE_BYTES;
+    const uint32_t full0 = bars, empty0 = bars + 8 * STAGES;
+    const uint32_t tfull0 = bars + 16 * STAGES, tempty0 = tfull0 + 8 * ACC_STAGES;
+    const uint32_t tmem_slot = tempty0 + 8 * ACC_STAGES;
+    int* const misc = reinterpret_cast<int*>(smem_raw + (tmem_slot - raw));
+    volatile int* const abort_s = misc + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cta = PAIR == 2 ? cluster_ctarank() : 0u;
+    const bool leader = cta == 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, PAIR);  // one arrive.expect_tx per CTA of the pair
+            mbar_init(empty0 + 8 * s, 1);    // one tcgen05.commit
+        }
+        for (int s = 0; s < ACC_STAGES; ++s) {
+            mbar_init(tfull0 + 8 * s, 1);           // one tcgen05.commit
+            mbar_init(tempty0 + 8 * s, 4 * PAIR);   // one arrive per epilogue warp (of both CTAs)
+        }
+        misc[1] = 0;
+        fence_mbar_init();
+        prefetch_tensormap(&tm_a0);
+        prefetch_tensormap(&tm_b0);
+        if (cfg::NA == 2) prefetch_tensormap(&tm_a1);
+        if (cfg::NB == 2) prefetch_tensormap(&tm_b1);
+    }
+    if (warp == 1) {
+        tmem_alloc<PAIR>(tmem_slot, TMEM_COLS);
+        tmem_relinquish<PAIR>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (PAIR == 2) {
+        cluster_arrive();
+        cluster_wait();
+    }
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(misc);
+
+    const int total_tiles = p.m_tiles * p.n_tiles;
+    const int k_blocks = (p.k + BLOCK_K - 1) / BLOCK_K;
+    const int tile_step = gridDim.x / PAIR;
+    const int tile_first = blockIdx.x / PAIR;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step) {
+                int tm, tn;
+                tile_coords(tile, p.m_tiles, p.n_tiles, tm, tn);
+                const int row_a = (tm * PAIR + (int)cta) * BLOCK_M;
+                const int row_b = tn * BLOCK_N + (int)cta * B_ROWS;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+                    if (!wait_bounded(empty0 + 8 * s, ph ^ 1u, abort_s, p.err, 1)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t dst = tiles0 + s * STAGE_BYTES;
+                    const int kx = kb * BLOCK_K;
+                    if (PAIR == 1) {
+                        const uint32_t bar = full0 + 8 * s;
+                        mbar_arrive_expect_tx(bar, STAGE_BYTES);
+                        tma_load_2d(dst, &tm_a0, bar, kx, row_a);
+                        if (cfg::NA == 2) tma_load_2d(dst + A_TILE_BYTES, &tm_a1, bar, kx, row_a);
+                        const uint32_t db = dst + cfg::NA * A_TILE_BYTES;
+                        tma_load_2d(db, &tm_b0, bar, kx, row_b);
+                        if (cfg::NB == 2) tma_load_2d(db + B_TILE_BYTES, &tm_b1, bar, kx, row_b);
+                    } else {
+                        // Both CTAs signal the LEADER's full barrier: it alone issues MMAs.
+                        const uint32_t bar = mapa(full0 + 8 * s, 0);
+                        mbar_arrive_expect_tx_cluster(full0 + 8 * s, STAGE_BYTES, 0);
+                        tma_load_2d_pair(dst, &tm_a0, bar, kx, row_a);
+                        if (cfg::NA == 2) tma_load_2d_pair(dst + A_TILE_BYTES, &tm_a1, bar, kx, row_a);
+                        const uint32_t db = dst + cfg::NA * A_TILE_BYTES;
+                        tma_load_2d_pair(db, &tm_b0, bar, kx, row_b);
+                        if (cfg::NB == 2) tma_load_2d_pair(db + B_TILE_BYTES, &tm_b1, bar, kx, row_b);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------------- MMA issuer
+        if (lane == 0 && leader) {
+            constexpr uint32_t ID_SS = idesc_i8(UMMA_M, BLOCK_N, true, true);
+            constexpr uint32_t ID_SU = idesc_i8(UMMA_M, BLOCK_N, true, false);
+            constexpr uint32_t ID_US = idesc_i8(UMMA_M, BLOCK_N, false, true);
+            constexpr uint32_t ID_UU = idesc_i8(UMMA_M, BLOCK_N, false, false);
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step, ++tcount) {
+                const uint32_t as = tcount % ACC_STAGES, aph = (tcount / ACC_STAGES) & 1u;
+                if (!wait_bounded(tempty0 + 8 * as, aph ^ 1u, abort_s, p.err, 2)) break;
+                tc_fence_after();
+                const uint32_t d0 = tmem_base + as * ACC_COLS;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+                    if (!wait_bounded(full0 + 8 * s, ph, abort_s, p.err, 3)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = tiles0 + s * STAGE_BYTES;
+                    const uint64_t da0 = smem_desc_k_sw128(sa);
+                    const uint64_t db0 = smem_desc_k_sw128(sa + cfg::NA * A_TILE_BYTES);
+#pragma unroll
+                    for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks) {
+                        const uint32_t acc = (kb | ks) != 0 ? 1u : 0u;
+                        const uint64_t koff = (uint64_t)((ks * UMMA_K) >> 4);
+                        if (MODE == 0) {
+                            mma_i8<PAIR>(d0, da0 + koff, db0 + koff, ID_SS, acc);
+                        } else {
+                            const uint64_t da1 = smem_desc_k_sw128(sa + A_TILE_BYTES) + koff;
+                            const uint64_t db1 =
+                                smem_desc_k_sw128(sa + cfg::NA * A_TILE_BYTES + B_TILE_BYTES) + koff;
+                            mma_i8<PAIR>(d0, da0 + koff, db0 + koff, ID_SS, acc);            // hi.hi
+                            mma_i8<PAIR>(d0 + BLOCK_N, da0 + koff, db1, ID_SU, acc);         // hi.lo
+                            mma_i8<PAIR>(d0 + BLOCK_N, da1, db0 + koff, ID_US, 1u);          // lo.hi
+                            mma_i8<PAIR>(d0 + 2 * BLOCK_N, da1, db1, ID_UU, acc);            // lo.lo
+                        }
+                    }
+                    if (PAIR == 1)
+                        mma_commit(empty0 + 8 * s);
+                    else
+                        mma_commit_pair(empty0 + 8 * s, 3);
+                }
+                if (!ok) break;
+                if (PAIR == 1)
+                    mma_commit(tfull0 + 8 * as);
+                else
+                    mma_commit_pair(tfull0 + 8 * as, 3);
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue
+        const int q = warp & 3;  // TMEM lane quadrant this warp may read
+        uint32_t tcount = 0;
+        for (int tile = tile_first; tile < total_tiles; tile += tile_step, ++tcount) {
+            int tm, tn;
+            tile_coords(tile, p.m_tiles, p.n_tiles, tm, tn);
+            const uint32_t as = tcount % ACC_STAGES, aph = (tcount / ACC_STAGES) & 1u;
+            if (!wait_bounded(tfull0 + 8 * as, aph, abort_s, p.err, 4)) break;
+            tc_fence_after();
+            const int row = (tm * PAIR + (int)cta) * BLOCK_M + q * 32 + lane;
+            const int col_tile = tn * BLOCK_N;
+            const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + as * ACC_COLS;
+            int32_t* const crow = p.c + (size_t)row * (size_t)p.n;
+            for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
+                if (col_tile + c0 >= p.n) break;  // warp-uniform
+                uint32_t v[32];
+                if (MODE == 0) {
+                    tmem_ld32(t0 + c0, v);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t hh[16], mid[16], ll[16];
+                        tmem_ld16(t0 + c0 + 16 * h, hh);
+                        tmem_ld16(t0 + BLOCK_N + c0 + 16 * h, mid);
+                        tmem_ld16(t0 + 2 * BLOCK_N + c0 + 16 * h, ll);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[16 * h + j] = (hh[j] << 16) + (mid[j] << 8) + ll[j];
+                    }
+                }
+                if (row < p.m) {
+                    const int col = col_tile + c0;
+                    if (p.vec_ok && col + 32 <= p.n) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<uint4*>(crow + col + j) =
+                                make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col + j < p.n) crow[col + j] = (int32_t)v[j];
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (PAIR == 1)
+                    mbar_arrive(tempty0 + 8 * as);
+                else
+                    mbar_arrive_cluster(tempty0 + 8 * as, 0);
+            }
+        }
+    }
+
+    // ------------------------------------------------------------------ teardown
+    __syncwarp();
+    if (*abort_s) __nanosleep(200000);  // let copies / MMAs still in flight land before freeing
+    tc_fence_before();
+    __syncthreads();
+    if (PAIR == 2) {
+        cluster_arrive();
+        cluster_wait();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc<PAIR>(tmem_base, TMEM_COLS);
+    }
+}
+
+// 2-D map over a row-major 8-bit matrix [rows][k] with row pitch `pitch` bytes; the
+// box is 128 bytes of K by `box_rows` rows, written to shared memory with the
+// 128-byte swizzle.  Reads past `k` or `rows` return zeros.
+int64_t make_tmap(CUtensorMap* tm, const void* base, int64_t k, int64_t rows, int64_t pitch,
+                  int box_rows) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(MIND_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)pitch};
+    cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                     estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(MIND_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (k=%lld rows=%lld pitch=%lld)",
+                    (int)r, (long long)k, (long long)rows, (long long)pitch);
+    return 0;
+}
+
+int g_pair_mode = 1;  // CTAs per tile: 1, or 2 for the cta_group::2 kernels
+
+template <int MODE, int PAIR>
+int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0, const void* b1,
+                  int32_t* c, int64_t m, int64_t n, int64_t k, int64_t kp_a, int64_t kp_b) {
+    using cfg = Cfg<MODE, PAIR>;
+    constexpr int B_ROWS = cfg::BLOCK_N / PAIR;
+    constexpr int STAGE_BYTES = cfg::NA * A_TILE_BYTES + cfg::NB * B_ROWS * BLOCK_K;
+    constexpr int SMEM = cfg::STAGES * STAGE_BYTES + 1024 + 256;
+    static_assert(SMEM <= 232448, "shared memory budget");
+    if (m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff)
+        return fail(MIND_B200_ERR_TOO_LARGE, "GEMM dimension above 2^31-1");
+    CUtensorMap ta0, ta1, tb0, tb1;
+    MB200_TRY(make_tmap(&ta0, a0, k, m, kp_a, BLOCK_M));
+    MB200_TRY(make_tmap(&tb0, b0, k, n, kp_b, B_ROWS));
+    ta1 = ta0;
+    tb1 = tb0;
+    if (cfg::NA == 2) MB200_TRY(make_tmap(&ta1, a1, k, m, kp_a, BLOCK_M));
+    if (cfg::NB == 2) MB200_TRY(make_tmap(&tb1, b1, k, n, kp_b, B_ROWS));
+    TcParams p;
+    p.c = c;
+    p.m = (int)m;
+    p.n = (int)n;
+    p.k = (int)k;
+    p.m_tiles = (int)((m + BLOCK_M * PAIR - 1) / (BLOCK_M * PAIR));
+    p.n_tiles = (int)((n + cfg::BLOCK_N - 1) / cfg::BLOCK_N);
+    p.vec_ok = (n % 4 == 0) && (reinterpret_cast<uintptr_t>(c) % 16 == 0);
+    p.err = ctx->err_word;
+    const long long total = (long long)p.m_tiles * p.n_tiles;
+    if (total > 0x7fffffff) return fail(MIND_B200_ERR_TOO_LARGE, "too many output tiles");
+    auto kern = gemm_tc_kernel<MODE, PAIR>;
+    static thread_local int attr_dev[4] = {-1, -1, -1, -1};
+    int& done_for = attr_dev[MODE * 2 + (PAIR - 1)];
+    if (done_for != ctx->device) {
+        MB200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+        done_for = ctx->device;
+    }
+    int units = ctx->sm_count / PAIR;  // CTAs (or CTA pairs) resident at once
+    if (total < units) units = (int)total;
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3((unsigned)(units * PAIR), 1, 1);
+    lc.blockDim = dim3(TC_THREADS, 1, 1);
+    lc.dynamicSmemBytes = SMEM;
+    lc.stream = ctx->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = PAIR;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    lc.attrs = at;
+    lc.numAttrs = 1;
+    MB200_CUDA(cudaLaunchKernelEx(&lc, kern, ta0, ta1, tb0, tb1, p));
+    count_launch();
+    return check_launch("gemm_tc_kernel");
+}
+
+}  // namespace
+
+int64_t set_pair_mode(int pair) {
+    if (pair != 1 && pair != 2) return fail(MIND_B200_ERR_INVALID, "CTAs per tile must be 1 or 2");
+    g_pair_mode = pair;
+    return 0;
+}
+
+int64_t launch_gemm_i8_tc(DeviceCtx* ctx, const int8_t* a, const int8_t* bt, int32_t* c, int64_t m,
+                          int64_t n, int64_t k, int64_t kp_a, int64_t kp_b) {
+    if (g_pair_mode == 2)
+        return launch_tc<0, 2>(ctx, a, nullptr, bt, nullptr, c, m, n, k, kp_a, kp_b);
+    return launch_tc<0, 1>(ctx, a, nullptr, bt, nullptr, c, m, n, k, kp_a, kp_b);
+}
+
+int64_t launch_gemm_i16_tc(DeviceCtx* ctx, const int8_t* a_hi, const uint8_t* a_lo,
+                           const int8_t* bt_hi, const uint8_t* bt_lo, int32_t* c, int64_t m,
+                           int64_t n, int64_t k, int64_t kp) {
+    if (g_pair_mode == 2) return launch_tc<1, 2>(ctx, a_hi, a_lo, bt_hi, bt_lo, c, m, n, k, kp, kp);
+    return launch_tc<1, 1>(ctx, a_hi, a_lo, bt_hi, bt_lo, c, m, n, k, kp, kp);
+}
+
+}  // namespace mb200

@@ -1,0 +1,300 @@
+/*
+ * cpu_baseline.c -- threaded, cache-blocked CPU ports of the reference's
+ * deterministic kernels, used ONLY to time a CPU baseline beside the GPU numbers
+ * (and cross-checked against oracle.c in the tests).
+ *
+ * TEST / MEASUREMENT INFRASTRUCTURE ONLY: never linked into the shipped library.
+ *
+ * The reference's kernels for this path exist only as MLIR text that its Rust
+ * compiler prints (src/mlir/lowering.rs) and that LLVM tools compile; neither
+ * toolchain can be run where this is built, so these are PORTS that keep the
+ * reference's structure:
+ *   - int8 GEMM: BLIS-style jc/ic/pc blocking with the reference's block sizes
+ *     (src/mlir/gemm_tuning.rs: I8_MC=1024, I8_KC=512, I8_NC=128), operands
+ *     packed to i16 K-pairs, MR=4 x NR=16 micro-kernel on vpmaddwd
+ *     (src/mlir/lowering.rs:7798 emit_i8_microkernel_avx2, :8371 emit_mm_i8_blocked);
+ *   - Q16.16 GEMM: per row, broadcast A[i,k], 64-bit multiply of a B row
+ *     segment, arithmetic >>16, 64-bit add (src/mlir/lowering.rs:9274-9282, :9433);
+ *   - Q16.16 / int16 GEMV: one reduction per row
+ *     (src/mlir/lowering.rs:9822-9996, :10723);
+ *   - threading: contiguous owner-computes row bands, T = min(ncpu, M, 256),
+ *     band = ceil(M/T) (src/mlir/lowering.rs:10146-10205), no reduction.
+ * Build with -O3 -march=x86-64-v3 (the reference's level, src/target.rs:267-272).
+ */
+#include <pthread.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#include <unistd.h>
+#if defined(__AVX2__)
+#include <immintrin.h>
+#endif
+
+#define BASELINE_EXPORT __attribute__((visibility("default")))
+
+/* ---------------------------- row-band threading -------------------------- */
+typedef void (*band_fn)(void *ctx, int64_t row_start, int64_t row_end);
+typedef struct {
+    band_fn fn;
+    void *ctx;
+    int64_t s, e;
+} band_job;
+
+static void *band_trampoline(void *p) {
+    band_job *j = (band_job *)p;
+    j->fn(j->ctx, j->s, j->e);
+    return NULL;
+}
+
+/* Runs fn over [0, m) split as the reference splits it; returns threads used. */
+static int64_t run_bands(band_fn fn, void *ctx, int64_t m, int64_t threads) {
+    if (m <= 0) return 0;
+    int64_t ncpu = threads > 0 ? threads : sysconf(_SC_NPROCESSORS_ONLN);
+    int64_t upper = m < 256 ? m : 256;
+    int64_t t = ncpu < upper ? ncpu : upper;
+    if (t < 1) t = 1;
+    int64_t band = (m + t - 1) / t;
+    pthread_t tid[256];
+    band_job job[256];
+    int64_t used = 0;
+    for (int64_t i = 0; i < t; ++i) {
+        int64_t s = i * band, e = s + band;
+        if (e > m) e = m;
+        if (s >= e) break;
+        job[used] = (band_job){fn, ctx, s, e};
+        ++used;
+    }
+    for (int64_t i = 1; i < used; ++i) pthread_create(&tid[i], NULL, band_trampoline, &job[i]);
+    band_trampoline(&job[0]);
+    for (int64_t i = 1; i < used; ++i) pthread_join(tid[i], NULL);
+    return used;
+}
+
+BASELINE_EXPORT int64_t baseline_online_cpus(void) { return sysconf(_SC_NPROCESSORS_ONLN); }
+
+/* ------------------------------- int8 GEMM -------------------------------- */
+enum { I8_MC = 1024, I8_KC = 512, I8_NC = 128, I8_MR = 4, I8_NR = 16 };
+
+typedef struct {
+    const int8_t *a, *b;
+    int32_t *c;
+    int64_t m, k, n;
+} gemm_i8_ctx;
+
+/* B block [kc x nc] -> i16 pairs: bp[(p*ncp + j)*2 + h] = B[k0+2p+h][j0+j]. */
+static void pack_b_i8(const int8_t *b, int64_t n, int64_t k0, int64_t kc, int64_t j0, int64_t nc,
+                      int64_t ncp, int16_t *bp) {
+    int64_t kp = (kc + 1) / 2;
+    for (int64_t p = 0; p < kp; ++p)
+        for (int64_t j = 0; j < ncp; ++j)
+            for (int h = 0; h < 2; ++h) {
+                int64_t kk = 2 * p + h;
+                bp[(p * ncp + j) * 2 + h] =
+                    (kk < kc && j < nc) ? (int16_t)b[(k0 + kk) * n + j0 + j] : 0;
+            }
+}
+
+/* A block [mc x kc] -> i16 pairs: ap[(i*kp + p)*2 + h] = A[i0+i][k0+2p+h]. */
+static void pack_a_i8(const int8_t *a, int64_t k, int64_t i0, int64_t mc, int64_t k0, int64_t kc,
+                      int16_t *ap) {
+    int64_t kp = (kc + 1) / 2;
+    for (int64_t i = 0; i < mc; ++i)
+        for (int64_t p = 0; p < kp; ++p)
+            for (int h = 0; h < 2; ++h) {
+                int64_t kk = 2 * p + h;
+                ap[(i * kp + p) * 2 + h] = kk < kc ? (int16_t)a[(i0 + i) * k + k0 + kk] : 0;
+            }
+}
+
+static void micro_i8(const int16_t *ap, const int16_t *bp, int64_t kp, int64_t ncp, int64_t rows,
+                     int64_t cols, int32_t *c, int64_t ldc, int first) {
+#if defined(__AVX2__)
+    __m256i acc[I8_MR][2];
+    for (int r = 0; r < I8_MR; ++r) acc[r][0] = acc[r][1] = _mm256_setzero_si256();
+    for (int64_t p = 0; p < kp; ++p) {
+        __m256i b0 = _mm256_loadu_si256((const __m256i *)(bp + (p * ncp) * 2));
+        __m256i b1 = _mm256_loadu_si256((const __m256i *)(bp + (p * ncp + 8) * 2));
+        for (int r = 0; r < I8_MR; ++r) {
+            int32_t pair;
+            memcpy(&pair, ap + (r * kp + p) * 2, 4);
+            __m256i av = _mm256_set1_epi32(pair);
+            acc[r][0] = _mm256_add_epi32(acc[r][0], _mm256_madd_epi16(av, b0));
+            acc[r][1] = _mm256_add_epi32(acc[r][1], _mm256_madd_epi16(av, b1));
+        }
+    }
+    int32_t tile[I8_MR][I8_NR];
+    for (int r = 0; r < I8_MR; ++r) {
+        _mm256_storeu_si256((__m256i *)&tile[r][0], acc[r][0]);
+        _mm256_storeu_si256((__m256i *)&tile[r][8], acc[r][1]);
+    }
+#else
+    int32_t tile[I8_MR][I8_NR];
+    memset(tile, 0, sizeof tile);
+    for (int64_t p = 0; p < kp; ++p)
+        for (int r = 0; r < I8_MR; ++r)
+            for (int j = 0; j < I8_NR; ++j)
+                tile[r][j] += (int32_t)ap[(r * kp + p) * 2] * bp[(p * ncp + j) * 2] +
+                              (int32_t)ap[(r * kp + p) * 2 + 1] * bp[(p * ncp + j) * 2 + 1];
+#endif
+    for (int64_t r = 0; r < rows; ++r)
+        for (int64_t j = 0; j < cols; ++j) {
+            uint32_t prev = first ? 0u : (uint32_t)c[r * ldc + j];
+            c[r * ldc + j] = (int32_t)(prev + (uint32_t)tile[r][j]);
+        }
+}
+
+static void gemm_i8_band(void *vctx, int64_t rs, int64_t re) {
+    gemm_i8_ctx *g = (gemm_i8_ctx *)vctx;
+    const int64_t k = g->k, n = g->n;
+    if (n <= 0) return;
+    if (k <= 0) {
+        for (int64_t i = rs; i < re; ++i) memset(g->c + i * n, 0, (size_t)n * 4);
+        return;
+    }
+    int16_t *ap = (int16_t *)malloc((size_t)(I8_MC + I8_MR) * (I8_KC + 2) * 2);
+    int16_t *bp = (int16_t *)malloc((size_t)(I8_KC + 2) * (I8_NC + I8_NR) * 2);
+    for (int64_t jc = 0; jc < n; jc += I8_NC) {
+        int64_t nc = n - jc < I8_NC ? n - jc : I8_NC;
+        int64_t ncp = (nc + I8_NR - 1) / I8_NR * I8_NR;
+        for (int64_t ic = rs; ic < re; ic += I8_MC) {
+            int64_t mc = re - ic < I8_MC ? re - ic : I8_MC;
+            int64_t mcp = (mc + I8_MR - 1) / I8_MR * I8_MR;
+            for (int64_t pc = 0; pc < k; pc += I8_KC) {
+                int64_t kc = k - pc < I8_KC ? k - pc : I8_KC;
+                int64_t kp = (kc + 1) / 2;
+                pack_b_i8(g->b, n, pc, kc, jc, nc, ncp, bp);
+                pack_a_i8(g->a, k, ic, mc, pc, kc, ap);
+                if (mcp > mc) memset(ap + mc * kp * 2, 0, (size_t)(mcp - mc) * kp * 4);
+                for (int64_t jr = 0; jr < nc; jr += I8_NR)
+                    for (int64_t ir = 0; ir < mc; ir += I8_MR) {
+                        int64_t rows = mc - ir < I8_MR ? mc - ir : I8_MR;
+                        int64_t cols = nc - jr < I8_NR ? nc - jr : I8_NR;
+                        micro_i8(ap + ir * kp * 2, bp + jr * 2, kp, ncp, rows, cols,
+                                 g->c + (ic + ir) * n + jc + jr, n, pc == 0);
+                    }
+            }
+        }
+    }
+    free(ap);
+    free(bp);
+}
+
+/* C = A.B for int8 operands; returns the number of threads used. */
+BASELINE_EXPORT int64_t baseline_gemm_i8_mt(const int8_t *a, const int8_t *b, int32_t *c, int64_t m,
+                                            int64_t k, int64_t n, int64_t threads) {
+    gemm_i8_ctx g = {a, b, c, m, k, n};
+    return run_bands(gemm_i8_band, &g, m, threads);
+}
+
+/* ------------------------------ Q16.16 GEMM ------------------------------- */
+typedef struct {
+    const int32_t *a, *b;
+    int32_t *c;
+    int64_t m, k, n;
+} gemm_q16_ctx;
+
+enum { Q16_NC = 128 };
+
+static void gemm_q16_band(void *vctx, int64_t rs, int64_t re) {
+    gemm_q16_ctx *g = (gemm_q16_ctx *)vctx;
+    const int64_t k = g->k, n = g->n;
+    int64_t acc[Q16_NC];
+    for (int64_t i = rs; i < re; ++i)
+        for (int64_t jc = 0; jc < n; jc += Q16_NC) {
+            int64_t nc = n - jc < Q16_NC ? n - jc : Q16_NC;
+            for (int64_t j = 0; j < nc; ++j) acc[j] = 0;
+            for (int64_t kk = 0; kk < k; ++kk) {
+                const int64_t av = g->a[i * k + kk];
+                const int32_t *brow = g->b + kk * n + jc;
+                for (int64_t j = 0; j < nc; ++j) acc[j] += (av * (int64_t)brow[j]) >> 16;
+            }
+            for (int64_t j = 0; j < nc; ++j) g->c[i * n + jc + j] = (int32_t)acc[j];
+        }
+}
+
+BASELINE_EXPORT int64_t baseline_gemm_q16_mt(const int32_t *a, const int32_t *b, int32_t *c,
+                                             int64_t m, int64_t k, int64_t n, int64_t threads) {
+    gemm_q16_ctx g = {a, b, c, m, k, n};
+    return run_bands(gemm_q16_band, &g, m, threads);
+}
+
+/* ------------------------------ int16 GEMM -------------------------------- */
+typedef struct {
+    const int16_t *a, *b;
+    int32_t *c;
+    int64_t m, k, n;
+} gemm_i16_ctx;
+
+static void gemm_i16_band(void *vctx, int64_t rs, int64_t re) {
+    gemm_i16_ctx *g = (gemm_i16_ctx *)vctx;
+    const int64_t k = g->k, n = g->n;
+    uint32_t acc[Q16_NC];
+    for (int64_t i = rs; i < re; ++i)
+        for (int64_t jc = 0; jc < n; jc += Q16_NC) {
+            int64_t nc = n - jc < Q16_NC ? n - jc : Q16_NC;
+            for (int64_t j = 0; j < nc; ++j) acc[j] = 0;
+            for (int64_t kk = 0; kk < k; ++kk) {
+                const int32_t av = g->a[i * k + kk];
+                const int16_t *brow = g->b + kk * n + jc;
+                for (int64_t j = 0; j < nc; ++j) acc[j] += (uint32_t)(av * (int32_t)brow[j]);
+            }
+            for (int64_t j = 0; j < nc; ++j) g->c[i * n + jc + j] = (int32_t)acc[j];
+        }
+}
+
+BASELINE_EXPORT int64_t baseline_gemm_i16_mt(const int16_t *a, const int16_t *b, int32_t *c,
+                                             int64_t m, int64_t k, int64_t n, int64_t threads) {
+    gemm_i16_ctx g = {a, b, c, m, k, n};
+    return run_bands(gemm_i16_band, &g, m, threads);
+}
+
+/* --------------------------------- GEMV ----------------------------------- */
+typedef struct {
+    const int32_t *w, *x;
+    int32_t *y;
+    int64_t cols;
+} gemv_q16_ctx;
+
+static void gemv_q16_band(void *vctx, int64_t rs, int64_t re) {
+    gemv_q16_ctx *g = (gemv_q16_ctx *)vctx;
+    for (int64_t r = rs; r < re; ++r) {
+        const int32_t *row = g->w + r * g->cols;
+        int64_t lane[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        int64_t i = 0;
+        for (; i + 8 <= g->cols; i += 8)
+            for (int l = 0; l < 8; ++l) lane[l] += ((int64_t)row[i + l] * (int64_t)g->x[i + l]) >> 16;
+        int64_t acc = 0;
+        for (int l = 0; l < 8; ++l) acc += lane[l];
+        for (; i < g->cols; ++i) acc += ((int64_t)row[i] * (int64_t)g->x[i]) >> 16;
+        g->y[r] = (int32_t)acc;
+    }
+}
+
+BASELINE_EXPORT int64_t baseline_gemv_q16_mt(const int32_t *w, const int32_t *x, int32_t *y,
+                                             int64_t rows, int64_t cols, int64_t threads) {
+    gemv_q16_ctx g = {w, x, y, cols};
+    return run_bands(gemv_q16_band, &g, rows, threads);
+}
+
+typedef struct {
+    const int16_t *w, *x;
+    int32_t *y;
+    int64_t cols;
+} gemv_i16_ctx;
+
+static void gemv_i16_band(void *vctx, int64_t rs, int64_t re) {
+    gemv_i16_ctx *g = (gemv_i16_ctx *)vctx;
+    for (int64_t r = rs; r < re; ++r) {
+        const int16_t *row = g->w + r * g->cols;
+        uint32_t acc = 0;
+        for (int64_t i = 0; i < g->cols; ++i) acc += (uint32_t)((int32_t)row[i] * (int32_t)g->x[i]);
+        g->y[r] = (int32_t)acc;
+    }
+}
+
+BASELINE_EXPORT int64_t baseline_gemv_i16_mt(const int16_t *w, const int16_t *x, int32_t *y,
+                                             int64_t rows, int64_t cols, int64_t threads) {
+    gemv_i16_ctx g = {w, x, y, cols};
+    return run_bands(gemv_i16_band, &g, rows, threads);
+}
