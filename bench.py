@@ -1,0 +1,388 @@
+#!/usr/bin/env python
+"""Benchmark of MIND's deterministic integer BLAS on B200 through the C ABI.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload gemm_i8|gemm_i16|gemm_q16|gemv_q16]
+  python bench.py --impl reference ...      # the CPU implementation timed on the host cores
+
+A step is one call of the intrinsic over one set of seeded synthetic operands (the
+reference's LCG, generated on the device).  The default workload is the 16384^3 int8 GEMM,
+row-sharded over the N ranks (one process per GPU, B replicated, no collective), so the
+total work is fixed as N grows.  One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+KIND_Q16, KIND_I8, KIND_I16 = 0, 1, 2
+L2_BYTES = 126 * 1024 * 1024
+
+WORKLOADS = {
+    # name: intrinsic, shape, element kind, generator shift, seed (the reference bench's per-shape rule)
+    "gemm_i8": dict(fn="matmul_mm_i8_v", m=16384, k=16384, n=16384, kind=KIND_I8, shift=0,
+                    seed=0xDEADBEEF00000000 ^ 16384, metric="bit-exact int8 GEMM throughput",
+                    unit="TOP/s", dtype="s8 x s8 -> s32", bound="tensor"),
+    "gemm_i16": dict(fn="matmul_mm_i16", m=4096, k=4096, n=4096, kind=KIND_I16, shift=0,
+                     seed=0xDEADBEEF00000000 ^ 4096, metric="bit-exact int16 GEMM throughput",
+                     unit="TOP/s", dtype="s16 x s16 -> s32 (four 8-bit limb products)", bound="tensor"),
+    "gemm_q16": dict(fn="matmul_mm_q16_v", m=1024, k=1024, n=1024, kind=KIND_Q16, shift=13,
+                     seed=0xDEADBEEF00000000 ^ 1024, metric="bit-exact Q16.16 GEMM throughput",
+                     unit="Gop/s", dtype="q16.16 (s32, two 32-bit multiply-adds per product)", bound="int32-alu"),
+    "gemv_q16": dict(fn="gemv_q16_mt", m=16384, k=16384, n=1, kind=KIND_Q16, shift=15,
+                     seed=0xDEADBEEF00000000 ^ ((16384 << 20) ^ 16384), metric="bit-exact Q16.16 GEMV bandwidth",
+                     unit="GB/s", dtype="q16.16 (s32)", bound="hbm"),
+}
+ELEM_BYTES = {KIND_Q16: 4, KIND_I8: 1, KIND_I16: 2}
+
+
+def work_units(w, m):
+    """Algorithmic work of one call over m rows, in the workload's unit numerator."""
+    if w["unit"] == "GB/s":
+        return 4.0 * m * w["k"] + 4.0 * w["k"] + 4.0 * m  # matrix once + vector + output, bytes
+    return 2.0 * m * w["n"] * w["k"]                       # ops = 2 MKN
+
+
+def unit_scale(w):
+    return {"TOP/s": 1e12, "Gop/s": 1e9, "GB/s": 1e9}[w["unit"]]
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f), "measured"
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1])); power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "power_w_max": max(power) if power else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ----------------------------------------------------------------- CPU baseline
+def cpu_call(w, a, b, rows, threads=0):
+    """One call of the CPU implementation over `rows` rows of the workload's shape."""
+    import oracle as O
+    k, n = w["k"], w["n"]
+    if w["fn"] == "matmul_mm_i8_v":
+        return O.baseline_gemm_i8(a, b, rows, k, n, threads)
+    if w["fn"] == "matmul_mm_i16":
+        return O.baseline_gemm_i16(a, b, rows, k, n, threads)
+    if w["fn"] == "matmul_mm_q16_v":
+        return O.baseline_gemm_q16(a, b, rows, k, n, threads)
+    return O.baseline_gemv_q16(a, b, rows, k, threads)
+
+
+def cpu_inputs(w, rows):
+    import oracle as O
+    g = O.Lcg(w["seed"])
+    k, n = w["k"], w["n"]
+    draw = {KIND_I8: g.i8, KIND_I16: g.i16, KIND_Q16: lambda c: g.q16(c, w["shift"])}[w["kind"]]
+    a = draw(rows * k)
+    # B follows the WHOLE A in the stream; a fresh generator with its own seed stands in
+    # for it here (the CPU timing does not depend on the values).
+    g2 = O.Lcg(w["seed"] ^ 0x5555)
+    draw2 = {KIND_I8: g2.i8, KIND_I16: g2.i16, KIND_Q16: lambda c: g2.q16(c, w["shift"])}[w["kind"]]
+    b = draw2(k * n)
+    return a, b
+
+
+def cpu_sample_rows(w, target_s):
+    """Rows of the workload whose CPU time is about target_s (time is linear in rows:
+    owner-computes row bands), found from one short calibration call."""
+    import oracle as O
+    cores = O.online_cpus()
+    rows0 = min(w["m"], max(4, 8 * min(cores, 256)))
+    a, b = cpu_inputs(w, rows0)
+    cpu_call(w, a, b, rows0)  # warm the thread stacks and caches
+    t0 = time.perf_counter()
+    cpu_call(w, a, b, rows0)
+    dt = max(time.perf_counter() - t0, 1e-4)
+    rows = int(rows0 * target_s / dt)
+    quantum = 4 * min(cores, 256)
+    rows = max(quantum, rows // quantum * quantum)
+    return min(rows, w["m"]), cores
+
+
+def cpu_baseline(w, target_s=15.0):
+    rows, cores = cpu_sample_rows(w, target_s)
+    a, b = cpu_inputs(w, rows)
+    t0 = time.perf_counter()
+    _, used = cpu_call(w, a, b, rows)
+    dt = time.perf_counter() - t0
+    return {"value": work_units(w, rows) / dt / unit_scale(w), "unit": w["unit"], "cores": used,
+            "kind": "port",
+            "sample": f"rows 0..{rows} of {w['m']} (all of K and N), {dt:.2f} s; row bands are independent, so time is linear in rows",
+            "host_cpus": cores}
+
+
+def run_reference(args, w):
+    """The CPU implementation of the path (threaded port of the reference's kernels,
+    oracle/cpu_baseline.c) on the host cores; each step is a bounded row sample."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    per_step = min(10.0, max(0.5, 100.0 / max(1, args.steps + args.warmup)))
+    rows, cores = cpu_sample_rows(w, per_step)
+    a, b = cpu_inputs(w, rows)
+    used = 0
+    for _ in range(args.warmup):
+        cpu_call(w, a, b, rows)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        _, used = cpu_call(w, a, b, rows)
+    dt = time.perf_counter() - t0
+    value = work_units(w, rows) * args.steps / dt / unit_scale(w)
+    sample = f"rows 0..{rows} of {w['m']} (all of K and N) per step; row bands are independent, so time is linear in rows"
+    line = {"impl": "reference", "metric": w["metric"], "value": value, "unit": w["unit"],
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": f"{args.workload} {w['m']}x{w['k']}x{w['n']}", "sample": sample},
+            "cpu_baseline": {"value": value, "unit": w["unit"], "cores": used, "kind": "port",
+                             "sample": sample, "host_cpus": cores},
+            "e2e": {"value": value, "unit": w["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------- GPU arm
+def run_mine(args, w):
+    import torch
+    import torch.distributed as dist
+
+    from mind_b200 import blas
+    from mind_b200.shard import row_band
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if blas.device_count() == 0:
+        raise SystemExit("libmind_b200 found no sm_100 device; there is no fallback to time")
+    stream = torch.cuda.current_stream()
+    blas.set_stream(stream.cuda_stream)
+    blas.set_gemm_path(args.path)
+
+    m, k, n, kind = w["m"], w["k"], w["n"], w["kind"]
+    es = ELEM_BYTES[kind]
+    r0, r1 = row_band(m, world, rank)
+    rows = r1 - r0
+    tdt = {KIND_Q16: torch.int32, KIND_I8: torch.int8, KIND_I16: torch.int16}[kind]
+    # This rank's band of A, all of B (replicated), this rank's band of C.
+    a = torch.empty(max(rows * k, 1), dtype=tdt, device="cuda")
+    b = torch.empty(k * n, dtype=tdt, device="cuda")
+    c = torch.empty(max(rows * n, 1), dtype=torch.int32, device="cuda")
+    blas.lcg_fill(a, rows * k, kind, w["seed"], r0 * k, w["shift"])
+    blas.lcg_fill(b, k * n, kind, w["seed"], m * k, w["shift"])
+    fn = getattr(blas, w["fn"])
+
+    def step(pa, pb, pc):
+        if w["fn"] == "gemv_q16_mt":
+            fn(pa, pb, pc, rows, k)
+        else:
+            fn(pa, pb, pc, rows, k, n)
+
+    # Byte-identity gate before any timing (the reference's benches do the same): two rows
+    # at each end of this rank's band against the CPU oracle.
+    step(a, b, c)
+    blas.synchronize()
+    if rows >= 2 and not args.no_check:
+        import oracle as O
+        bh = b.cpu().numpy()
+        for s in (0, rows - 2):
+            ah = a[s * k:(s + 2) * k].cpu().numpy()
+            got = c[s * n:(s + 2) * n].cpu().numpy()
+            want = {"matmul_mm_i8_v": O.gemm_i8, "matmul_mm_i16": O.gemm_i16, "matmul_mm_q16_v": O.gemm_q16}.get(w["fn"])
+            want = want(ah, bh, 2, k, n) if want else O.gemv_q16(ah, bh, 2, k)
+            if not np.array_equal(got, want):
+                raise SystemExit(f"rank {rank}: output differs from the oracle in rows {r0 + s}..{r0 + s + 2}; not timing a wrong kernel")
+
+    in_bytes = (rows * k + k * n) * es
+    flush = None
+    if in_bytes <= 2 * L2_BYTES:  # operands could sit in L2 between steps: evict them
+        flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device="cuda")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        if flush is not None:
+            flush.fill_(1)
+        step(a, b, c)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = blas.kernel_launches()
+    blas.profile(True)
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for e0, e1 in evs:
+        if flush is not None:
+            flush.fill_(1)
+        e0.record(stream)
+        step(a, b, c)
+        e1.record(stream)
+    barrier()
+    launches = blas.kernel_launches() - launches0
+    n_main, main_ms = blas.profile_read()
+    blas.profile(False)
+    clocks = sampler.stop() if rank == 0 else None
+    ms = sum(e0.elapsed_time(e1) for e0, e1 in evs)
+    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+
+    # End to end: the same call with HOST (pinned) operands, so every step copies this rank's
+    # A band and B to the device and C back, inside the timed region.
+    e2e_steps = max(1, min(args.steps, 3))
+    ha = torch.empty(a.numel(), dtype=tdt).pin_memory(); ha.copy_(a)
+    hb = torch.empty(b.numel(), dtype=tdt).pin_memory(); hb.copy_(b)
+    hc = torch.empty(c.numel(), dtype=torch.int32).pin_memory()
+    step(ha, hb, hc)  # warm-up (sizes the staging buffers)
+    barrier()
+    x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    x0.record(stream)
+    for _ in range(e2e_steps):
+        step(ha, hb, hc)  # synchronous: returns when C is back in host memory
+    x1.record(stream)
+    torch.cuda.synchronize()
+    e2e_s = x0.elapsed_time(x1) * 1e-3
+    t = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_s = float(t.item())
+    if not torch.equal(hc[: rows * n], c[: rows * n].cpu()):
+        raise SystemExit(f"rank {rank}: host-pointer call and device-pointer call disagree")
+
+    if rank == 0:
+        peaks, peak_src = measured_peaks()
+        scale = unit_scale(w)
+        total_work = work_units(w, m)  # whole job: every rank's rows
+        value = total_work * args.steps / (ms_total * 1e-3) / scale
+        per_launch = work_units(w, rows)
+        achieved = per_launch * n_main / (main_ms * 1e-3) / scale if n_main and main_ms > 0 else None
+        if w["bound"] == "hbm":
+            peak, peak_note = peaks["hbm_gbs"], f"{peak_src} STREAM-style copy"
+        elif w["bound"] == "tensor":
+            # no int8 figure is measured on this pool: the int8 tensor rate is twice bf16
+            base = peaks["bf16_tflops_sustained"] if ms_total / args.steps > 500 else peaks["bf16_tflops"]
+            peak, peak_note = 2.0 * base, f"2 x {peak_src} cuBLAS bf16 ({'sustained' if base == peaks['bf16_tflops_sustained'] else 'burst'})"
+            if w["fn"] == "matmul_mm_i16":
+                peak, peak_note = peak / 4.0, peak_note + " / 4 limb products"
+        else:
+            peak, peak_note = None, "no measured INT32 multiply-add peak on this pool"
+        roofline = {"bound": w["bound"], "achieved": achieved, "peak": peak, "unit": w["unit"],
+                    "frac": (achieved / peak) if achieved and peak else None, "traffic": None,
+                    "kernel": "gemm_tc_kernel" if w["bound"] == "tensor" else ("rows_warp_kernel" if w["bound"] == "hbm" else "gemm_simt_kernel"),
+                    "kernel_ms": main_ms / n_main if n_main else None, "peak_source": peak_note}
+        line = {"metric": w["metric"], "value": value, "unit": w["unit"], "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": w["dtype"], "data": "synthetic",
+                "config": {"workload": f"{args.workload} {m}x{k}x{n}" if n > 1 else f"{args.workload} {m}x{k}",
+                           "sharding": f"{world} row band(s) of {-(-m // world)} rows, B replicated, no collective",
+                           "l2": "operands larger than L2" if flush is None else "L2 flushed between steps",
+                           "gemm_path": args.path, "seed": hex(w["seed"])},
+                "roofline": roofline,
+                "e2e": {"value": total_work * e2e_steps / e2e_s / scale, "unit": w["unit"],
+                        "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": rows * n * 4,
+                        "steps": e2e_steps},
+                "gpu_launches": launches, "clocks": clocks}
+        line["cpu_baseline"] = cpu_baseline(w) if world == 1 and not args.no_cpu else None
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="mine", choices=["mine", "reference"])
+    ap.add_argument("--workload", default="gemm_i8", choices=sorted(WORKLOADS))
+    ap.add_argument("--path", type=int, default=0, help="0: one CTA per tile, 2: CTA pairs, 1: CUDA cores")
+    ap.add_argument("--size", type=int, default=0, help="override M = K (= N) for quick runs")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-check", action="store_true", help="skip the oracle gate before timing")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    w = dict(WORKLOADS[args.workload])
+    if args.size:
+        w["m"] = w["k"] = args.size
+        if w["n"] > 1:
+            w["n"] = args.size
+    if args.impl == "reference":
+        run_reference(args, w)
+    else:
+        run_mine(args, w)
+
+
+if __name__ == "__main__":
+    main()

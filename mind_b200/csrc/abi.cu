@@ -1,0 +1,410 @@
+// extern "C" entry points of libmind_b200: argument checks, host / device pointer
+// classification, staging of host operands, operand re-layout, kernel dispatch.
+#include <mutex>
+#include <vector>
+
+#include "common.h"
+
+namespace mb200 {
+namespace {
+
+std::mutex g_call_mutex;  // calls are serialised, like the reference's MT dispatch lock
+int g_gemm_path = 0;      // 0 = tensor cores, 1 = CUDA-core cross-check kernels
+
+// One operand of a call: where the caller keeps it and where the kernels see it.
+struct Operand {
+    void* user = nullptr;
+    size_t bytes = 0;
+    bool output = false;
+    bool host = false;
+    void* dev = nullptr;
+};
+
+// Classifies each operand, gives host operands a device copy in the staging arena,
+// uploads inputs before the kernels and downloads outputs after them.
+class Call {
+public:
+    explicit Call(DeviceCtx* ctx) : ctx_(ctx) {}
+
+    int add(const void* p, size_t bytes, bool output) {
+        Operand o;
+        o.user = const_cast<void*>(p);
+        o.bytes = bytes;
+        o.output = output;
+        ops_.push_back(o);
+        return (int)ops_.size() - 1;
+    }
+
+    int64_t begin() {
+        size_t staged = 0;
+        for (auto& o : ops_) {
+            if (o.bytes == 0) continue;
+            cudaPointerAttributes at;
+            cudaError_t e = cudaPointerGetAttributes(&at, o.user);
+            if (e != cudaSuccess) {
+                cudaGetLastError();
+                o.host = true;
+            } else if (at.type == cudaMemoryTypeDevice) {
+                if (at.device != ctx_->device)
+                    return fail(MIND_B200_ERR_INVALID,
+                                "operand lives on device %d but the current device is %d", at.device,
+                                ctx_->device);
+                o.host = false;
+            } else {
+                o.host = at.type != cudaMemoryTypeManaged;
+            }
+            if (o.host) {
+                staged += align_up(o.bytes, 1024);
+                any_host_ = true;
+            }
+        }
+        if (any_host_) MB200_TRY(arena_reserve(ctx_, ctx_->staging, staged + 1024));
+        for (auto& o : ops_) {
+            if (o.bytes == 0) continue;
+            if (!o.host) {
+                o.dev = o.user;
+                continue;
+            }
+            o.dev = arena_take(ctx_->staging, o.bytes);
+            if (!o.dev) return fail(MIND_B200_ERR_CUDA, "staging arena exhausted");
+            if (!o.output)
+                MB200_CUDA(cudaMemcpyAsync(o.dev, o.user, o.bytes, cudaMemcpyHostToDevice, ctx_->stream));
+        }
+        return 0;
+    }
+
+    template <typename T>
+    T* dev(int i) const { return static_cast<T*>(ops_[i].dev); }
+
+    // Downloads outputs; with any host operand, also waits and reports kernel time-outs.
+    // `waits_inside` says a kernel with bounded waits ran, whose error word must be fetched.
+    int64_t end(bool waits_inside = false) {
+        for (auto& o : ops_)
+            if (o.host && o.output && o.bytes)
+                MB200_CUDA(cudaMemcpyAsync(o.user, o.dev, o.bytes, cudaMemcpyDeviceToHost, ctx_->stream));
+        if (waits_inside)
+            MB200_CUDA(cudaMemcpyAsync(ctx_->err_host, ctx_->err_word, sizeof(int),
+                                       cudaMemcpyDeviceToHost, ctx_->stream));
+        if (any_host_) {
+            MB200_CUDA(cudaStreamSynchronize(ctx_->stream));
+            return check_err_word(ctx_);
+        }
+        return 0;
+    }
+
+    static int64_t check_err_word(DeviceCtx* ctx) {
+        const int code = *ctx->err_host;
+        if (code == 0) return 0;
+        *ctx->err_host = 0;
+        cudaMemsetAsync(ctx->err_word, 0, sizeof(int), ctx->stream);
+        return fail(MIND_B200_ERR_TIMEOUT,
+                    "a bounded wait inside the GEMM kernel ran out (role code %d); the output is invalid",
+                    code);
+    }
+
+private:
+    DeviceCtx* ctx_;
+    std::vector<Operand> ops_;
+    bool any_host_ = false;
+};
+
+int64_t check_dims(int64_t m, int64_t k, int64_t n) {
+    if (m < 0 || k < 0 || n < 0) return fail(MIND_B200_ERR_INVALID, "negative dimension");
+    return 0;
+}
+
+// ------------------------------------------------------------------ GEMMs
+int64_t gemm_i8(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n) {
+    clear_error();
+    MB200_TRY(check_dims(m, k, n));
+    if (m == 0 || n == 0) return 0;
+    if (!c || (k > 0 && (!a || !b))) return fail(MIND_B200_ERR_INVALID, "null operand");
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return MIND_B200_ERR_NO_DEVICE;
+    std::lock_guard<std::mutex> lock(g_call_mutex);
+    Call call(ctx);
+    const int ia = call.add((void*)a, (size_t)m * k, false);
+    const int ib = call.add((void*)b, (size_t)k * n, false);
+    const int ic = call.add((void*)c, (size_t)m * n * 4, true);
+    MB200_TRY(call.begin());
+    if (k == 0) {
+        MB200_CUDA(cudaMemsetAsync(call.dev<void>(ic), 0, (size_t)m * n * 4, ctx->stream));
+    } else if (g_gemm_path == 1) {
+        MB200_TRY(launch_gemm_i8_simt(ctx, call.dev<int8_t>(ia), call.dev<int8_t>(ib), call.dev<int32_t>(ic), m, k, n));
+    } else {
+        const int64_t kp = (int64_t)align_up((size_t)k, 16);
+        const int8_t* da = call.dev<int8_t>(ia);
+        const bool a_direct = kp == k && reinterpret_cast<uintptr_t>(da) % 16 == 0;
+        const size_t bt_bytes = (size_t)n * kp, ap_bytes = a_direct ? 0 : (size_t)m * kp;
+        MB200_TRY(arena_reserve(ctx, ctx->scratch, align_up(bt_bytes, 1024) + align_up(ap_bytes, 1024) + 2048));
+        int8_t* bt = static_cast<int8_t*>(arena_take(ctx->scratch, bt_bytes));
+        MB200_TRY(launch_transpose_i8(ctx, call.dev<int8_t>(ib), bt, k, n, kp));
+        if (!a_direct) {
+            int8_t* ap = static_cast<int8_t*>(arena_take(ctx->scratch, ap_bytes));
+            MB200_TRY(launch_pad_rows_i8(ctx, da, ap, m, k, kp));
+            da = ap;
+        }
+        MB200_TRY(launch_gemm_i8_tc(ctx, da, bt, call.dev<int32_t>(ic), m, n, k, kp, kp));
+    }
+    return call.end(true);
+}
+
+int64_t gemm_i16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n) {
+    clear_error();
+    MB200_TRY(check_dims(m, k, n));
+    if (m == 0 || n == 0) return 0;
+    if (!c || (k > 0 && (!a || !b))) return fail(MIND_B200_ERR_INVALID, "null operand");
+    if ((a | b) & 1) return fail(MIND_B200_ERR_INVALID, "int16 operand is not 2-byte aligned");
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return MIND_B200_ERR_NO_DEVICE;
+    std::lock_guard<std::mutex> lock(g_call_mutex);
+    Call call(ctx);
+    const int ia = call.add((void*)a, (size_t)m * k * 2, false);
+    const int ib = call.add((void*)b, (size_t)k * n * 2, false);
+    const int ic = call.add((void*)c, (size_t)m * n * 4, true);
+    MB200_TRY(call.begin());
+    if (k == 0) {
+        MB200_CUDA(cudaMemsetAsync(call.dev<void>(ic), 0, (size_t)m * n * 4, ctx->stream));
+    } else if (g_gemm_path == 1) {
+        MB200_TRY(launch_gemm_i16_simt(ctx, call.dev<int16_t>(ia), call.dev<int16_t>(ib), call.dev<int32_t>(ic), m, k, n));
+    } else {
+        const int64_t kp = (int64_t)align_up((size_t)k, 16);
+        const size_t a_plane = align_up((size_t)m * kp, 1024), b_plane = align_up((size_t)n * kp, 1024);
+        MB200_TRY(arena_reserve(ctx, ctx->scratch, 2 * a_plane + 2 * b_plane + 4096));
+        int8_t* a_hi = static_cast<int8_t*>(arena_take(ctx->scratch, a_plane));
+        uint8_t* a_lo = static_cast<uint8_t*>(arena_take(ctx->scratch, a_plane));
+        int8_t* b_hi = static_cast<int8_t*>(arena_take(ctx->scratch, b_plane));
+        uint8_t* b_lo = static_cast<uint8_t*>(arena_take(ctx->scratch, b_plane));
+        MB200_TRY(launch_split_rows_i16(ctx, call.dev<int16_t>(ia), a_hi, a_lo, m, k, kp));
+        MB200_TRY(launch_split_transpose_i16(ctx, call.dev<int16_t>(ib), b_hi, b_lo, k, n, kp));
+        MB200_TRY(launch_gemm_i16_tc(ctx, a_hi, a_lo, b_hi, b_lo, call.dev<int32_t>(ic), m, n, k, kp));
+    }
+    return call.end(true);
+}
+
+// b_transposed: b is N x K (the identity gate's composition) instead of K x N.
+int64_t gemm_q16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n, bool b_transposed) {
+    clear_error();
+    MB200_TRY(check_dims(m, k, n));
+    if (m == 0 || n == 0) return 0;
+    if (!c || (k > 0 && (!a || !b))) return fail(MIND_B200_ERR_INVALID, "null operand");
+    if ((a | b | c) & 3) return fail(MIND_B200_ERR_INVALID, "int32 operand is not 4-byte aligned");
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return MIND_B200_ERR_NO_DEVICE;
+    std::lock_guard<std::mutex> lock(g_call_mutex);
+    Call call(ctx);
+    const int ia = call.add((void*)a, (size_t)m * k * 4, false);
+    const int ib = call.add((void*)b, (size_t)k * n * 4, false);
+    const int ic = call.add((void*)c, (size_t)m * n * 4, true);
+    MB200_TRY(call.begin());
+    if (k == 0) {
+        MB200_CUDA(cudaMemsetAsync(call.dev<void>(ic), 0, (size_t)m * n * 4, ctx->stream));
+    } else {
+        const int32_t* db = call.dev<int32_t>(ib);
+        if (b_transposed) {
+            MB200_TRY(arena_reserve(ctx, ctx->scratch, (size_t)k * n * 4 + 2048));
+            int32_t* bkn = static_cast<int32_t*>(arena_take(ctx->scratch, (size_t)k * n * 4));
+            MB200_TRY(launch_transpose_i32(ctx, db, bkn, n, k));
+            db = bkn;
+        }
+        MB200_TRY(launch_gemm_q16(ctx, call.dev<int32_t>(ia), db, call.dev<int32_t>(ic), m, k, n));
+    }
+    return call.end();
+}
+
+// ------------------------------------------------------------ row reductions
+// kind: 0 = Q16.16 matrix x vector, 1 = int16 matrix x vector.
+int64_t gemv(int kind, int64_t w, int64_t x, int64_t y, int64_t rows, int64_t cols) {
+    clear_error();
+    if (rows < 0 || cols < 0) return fail(MIND_B200_ERR_INVALID, "negative dimension");
+    if (rows == 0) return 0;
+    if (!y || (cols > 0 && (!w || !x))) return fail(MIND_B200_ERR_INVALID, "null operand");
+    const int es = kind == 0 ? 4 : 2;
+    if (((w | x) & (es - 1)) || (y & 3)) return fail(MIND_B200_ERR_INVALID, "misaligned operand");
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return MIND_B200_ERR_NO_DEVICE;
+    std::lock_guard<std::mutex> lock(g_call_mutex);
+    Call call(ctx);
+    const int iw = call.add((void*)w, (size_t)rows * cols * es, false);
+    const int ix = call.add((void*)x, (size_t)cols * es, false);
+    const int iy = call.add((void*)y, (size_t)rows * 4, true);
+    MB200_TRY(call.begin());
+    if (kind == 0)
+        MB200_TRY(launch_gemv_q16(ctx, call.dev<int32_t>(iw), call.dev<int32_t>(ix), call.dev<int32_t>(iy), rows, cols));
+    else
+        MB200_TRY(launch_gemv_i16(ctx, call.dev<int16_t>(iw), call.dev<int16_t>(ix), call.dev<int32_t>(iy), rows, cols));
+    return call.end();
+}
+
+// kind: 0 = Q16.16 dot, 1 = int16 dot, 2 = Q16.16 L1 distance.  Returns the value;
+// failures leave a message and return 0 (the reference's dot returns 0 on bad input).
+int64_t dot(int kind, int64_t a, int64_t b, int64_t len) {
+    clear_error();
+    if (len <= 0 || !a || !b) return 0;
+    const int es = kind == 1 ? 2 : 4;
+    if ((a | b) & (es - 1)) {
+        fail(MIND_B200_ERR_INVALID, "misaligned operand");
+        return 0;
+    }
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return 0;
+    std::lock_guard<std::mutex> lock(g_call_mutex);
+    int32_t result = 0;
+    Call call(ctx);
+    const int ia = call.add((void*)a, (size_t)len * es, false);
+    const int ib = call.add((void*)b, (size_t)len * es, false);
+    const int ir = call.add(&result, 4, true);  // a host operand: the call is synchronous
+    if (call.begin() != 0) return 0;
+    int64_t st;
+    if (kind == 0)
+        st = launch_gemv_q16(ctx, call.dev<int32_t>(ia), call.dev<int32_t>(ib), call.dev<int32_t>(ir), 1, len);
+    else if (kind == 1)
+        st = launch_gemv_i16(ctx, call.dev<int16_t>(ia), call.dev<int16_t>(ib), call.dev<int32_t>(ir), 1, len);
+    else
+        st = launch_dist_l1_q16(ctx, call.dev<int32_t>(ia), call.dev<int32_t>(ib), call.dev<int32_t>(ir), len);
+    if (st != 0 || call.end() != 0) return 0;
+    return (int64_t)result;
+}
+
+}  // namespace
+}  // namespace mb200
+
+using namespace mb200;
+
+extern "C" {
+
+int64_t __mind_blas_matmul_mm_i8_v(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n) { return gemm_i8(a, b, c, m, k, n); }
+int64_t __mind_blas_matmul_mm_i8_mt_v(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n) { return gemm_i8(a, b, c, m, k, n); }
+int64_t __mind_blas_matmul_mm_q16_v(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n) { return gemm_q16(a, b, c, m, k, n, false); }
+int64_t __mind_blas_matmul_mm_q16_mt_v(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n) { return gemm_q16(a, b, c, m, k, n, false); }
+int64_t __mind_b200_matmul_mm_i16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n) { return gemm_i16(a, b, c, m, k, n); }
+int64_t __mind_blas_gemv_q16_mt(int64_t w, int64_t x, int64_t y, int64_t m, int64_t k) { return gemv(0, w, x, y, m, k); }
+int64_t __mind_blas_matmul_rmajor_q16_v(int64_t w, int64_t x, int64_t y, int64_t rows, int64_t cols) { return gemv(0, w, x, y, rows, cols); }
+int64_t __mind_blas_matmul_rmajor_i16_v(int64_t w, int64_t x, int64_t y, int64_t rows, int64_t cols) { return gemv(1, w, x, y, rows, cols); }
+int64_t __mind_blas_dot_q16_v(int64_t a, int64_t b, int64_t len) { return dot(0, a, b, len); }
+int64_t __mind_blas_dot_i16_v(int64_t a, int64_t b, int64_t len) { return dot(1, a, b, len); }
+int64_t __mind_blas_dot_l1_q16_v(int64_t a, int64_t b, int64_t len) { return dot(2, a, b, len); }
+
+int64_t dotq(int64_t a, int64_t b, int64_t n) { return dot(0, a, b, n); }
+int64_t dotl1q(int64_t a, int64_t b, int64_t n) { return dot(2, a, b, n); }
+int64_t doti16(int64_t a, int64_t b, int64_t n) { return dot(1, a, b, n); }
+int64_t mmq(int64_t w, int64_t x, int64_t y, int64_t rows, int64_t cols) { return gemv(0, w, x, y, rows, cols); }
+int64_t mmi16(int64_t w, int64_t x, int64_t y, int64_t rows, int64_t cols) { return gemv(1, w, x, y, rows, cols); }
+int64_t gemvq(int64_t w, int64_t x, int64_t y, int64_t m, int64_t k) { return gemv(0, w, x, y, m, k); }
+int64_t gemmq(int64_t a, int64_t bt, int64_t c, int64_t m, int64_t k, int64_t n) { return gemm_q16(a, bt, c, m, k, n, true); }
+int64_t gemmq_kn(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n) { return gemm_q16(a, b, c, m, k, n, false); }
+int64_t gemmqmm(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n) { return gemm_q16(a, b, c, m, k, n, false); }
+int64_t gemmi8(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n) { return gemm_i8(a, b, c, m, k, n); }
+int64_t gemmi8mt(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n) { return gemm_i8(a, b, c, m, k, n); }
+
+const char* mind_b200_last_error(void) { return last_error_cstr(); }
+
+int64_t mind_b200_set_stream(int64_t cuda_stream) {
+    clear_error();
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return MIND_B200_ERR_NO_DEVICE;
+    std::lock_guard<std::mutex> lock(g_call_mutex);
+    ctx->stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+    return 0;
+}
+
+int64_t mind_b200_synchronize(void) {
+    clear_error();
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return MIND_B200_ERR_NO_DEVICE;
+    std::lock_guard<std::mutex> lock(g_call_mutex);
+    MB200_CUDA(cudaStreamSynchronize(ctx->stream));
+    return Call::check_err_word(ctx);
+}
+
+int64_t mind_b200_device_count(void) { return usable_device_count(); }
+int64_t mind_b200_kernel_launches(void) { return launches(); }
+
+int64_t mind_b200_reserve(int64_t scratch_bytes, int64_t staging_bytes) {
+    clear_error();
+    if (scratch_bytes < 0 || staging_bytes < 0) return fail(MIND_B200_ERR_INVALID, "negative size");
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return MIND_B200_ERR_NO_DEVICE;
+    std::lock_guard<std::mutex> lock(g_call_mutex);
+    MB200_TRY(arena_reserve(ctx, ctx->scratch, (size_t)scratch_bytes));
+    MB200_TRY(arena_reserve(ctx, ctx->staging, (size_t)staging_bytes));
+    return 0;
+}
+
+int64_t mind_b200_set_gemm_path(int64_t path) {
+    clear_error();
+    std::lock_guard<std::mutex> lock(g_call_mutex);
+    if (path == 0 || path == 1) {
+        g_gemm_path = (int)path;
+        return set_pair_mode(1);
+    }
+    if (path == 2) {  // tensor cores, one tile per CTA pair
+        g_gemm_path = 0;
+        return set_pair_mode(2);
+    }
+    return fail(MIND_B200_ERR_INVALID, "gemm path must be 0 (tensor cores), 1 (CUDA cores) or 2 (tensor cores, CTA pairs)");
+}
+
+int64_t mind_b200_profile(int64_t enable) {
+    clear_error();
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return MIND_B200_ERR_NO_DEVICE;
+    std::lock_guard<std::mutex> lock(g_call_mutex);
+    ctx->profile = enable != 0;
+    ctx->prof_count = 0;
+    return 0;
+}
+
+int64_t mind_b200_profile_read(int64_t* launches_out, double* total_ms_out) {
+    clear_error();
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return MIND_B200_ERR_NO_DEVICE;
+    std::lock_guard<std::mutex> lock(g_call_mutex);
+    MB200_CUDA(cudaStreamSynchronize(ctx->stream));
+    double total = 0.0;
+    for (int i = 0; i < ctx->prof_count; ++i) {
+        float ms = 0.f;
+        MB200_CUDA(cudaEventElapsedTime(&ms, ctx->prof_ev[2 * i], ctx->prof_ev[2 * i + 1]));
+        total += ms;
+    }
+    if (launches_out) *launches_out = ctx->prof_count;
+    if (total_ms_out) *total_ms_out = total;
+    ctx->prof_count = 0;
+    return 0;
+}
+
+int64_t mind_b200_lcg_fill(int64_t dst, int64_t n, int64_t kind, int64_t seed, int64_t offset, int64_t shift) {
+    clear_error();
+    if (n < 0 || kind < 0 || kind > 2 || shift < 0 || shift > 31) return fail(MIND_B200_ERR_INVALID, "bad argument");
+    if (n == 0) return 0;
+    if (!dst) return fail(MIND_B200_ERR_INVALID, "null destination");
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return MIND_B200_ERR_NO_DEVICE;
+    std::lock_guard<std::mutex> lock(g_call_mutex);
+    const size_t es = kind == 0 ? 4 : (kind == 1 ? 1 : 2);
+    Call call(ctx);
+    const int id = call.add((void*)dst, (size_t)n * es, true);
+    MB200_TRY(call.begin());
+    MB200_TRY(launch_lcg_fill(ctx, call.dev<void>(id), n, (int)kind, (uint64_t)seed, (uint64_t)offset, (int)shift));
+    return call.end();
+}
+
+int64_t mind_b200_matvec_wrap(int64_t mat, int64_t elem_bytes, int64_t rows, int64_t cols, int64_t v, int64_t out) {
+    clear_error();
+    if (rows < 0 || cols < 0) return fail(MIND_B200_ERR_INVALID, "negative dimension");
+    if (rows == 0) return 0;
+    if (!out || (cols > 0 && (!mat || !v))) return fail(MIND_B200_ERR_INVALID, "null operand");
+    if (elem_bytes != 1 && elem_bytes != 2 && elem_bytes != 4) return fail(MIND_B200_ERR_INVALID, "elem_bytes must be 1, 2 or 4");
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return MIND_B200_ERR_NO_DEVICE;
+    std::lock_guard<std::mutex> lock(g_call_mutex);
+    Call call(ctx);
+    const int im = call.add((void*)mat, (size_t)rows * cols * elem_bytes, false);
+    const int iv = call.add((void*)v, (size_t)cols * 4, false);
+    const int io = call.add((void*)out, (size_t)rows * 4, true);
+    MB200_TRY(call.begin());
+    MB200_TRY(launch_matvec_wrap(ctx, call.dev<void>(im), (int)elem_bytes, rows, cols, call.dev<int32_t>(iv), call.dev<int32_t>(io)));
+    return call.end();
+}
+
+}  // extern "C"

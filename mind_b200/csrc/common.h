@@ -16,6 +16,10 @@ namespace mb200 {
 // Sets the calling thread's error message and returns `code`.
 int64_t fail(int64_t code, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
 void clear_error();
+const char* last_error_cstr();
+long long launches();
+int usable_device_count();
+int64_t set_pair_mode(int pair);
 
 #define MB200_CUDA(expr)                                                                   \
     do {                                                                                   \
@@ -47,7 +51,16 @@ struct DeviceCtx {
     Arena staging;                  // device copies of host-pointer operands
     int* err_word = nullptr;        // device word a kernel sets when a bounded wait runs out
     int* err_host = nullptr;        // pinned mirror of err_word
+    // Optional timing of the main kernel of each call (CUDA events on `stream`).
+    static constexpr int PROF_RING = 512;
+    bool profile = false;
+    int prof_count = 0;
+    cudaEvent_t prof_ev[2 * PROF_RING] = {};
 };
+
+// Bracket the dominant kernel of a call; no-ops unless profiling is on.
+void prof_begin(DeviceCtx* ctx);
+void prof_end(DeviceCtx* ctx);
 
 // Context of the CURRENT device (created on first use); nullptr + error set on failure.
 DeviceCtx* current_ctx();
@@ -85,6 +98,8 @@ int64_t launch_gemm_i16_tc(DeviceCtx* ctx, const int8_t* a_hi, const uint8_t* a_
 // Re-layout kernels.
 int64_t launch_transpose_i8(DeviceCtx* ctx, const int8_t* b, int8_t* bt, int64_t k, int64_t n,
                             int64_t kp);
+int64_t launch_transpose_i32(DeviceCtx* ctx, const int32_t* src, int32_t* dst, int64_t rows,
+                             int64_t cols);
 int64_t launch_pad_rows_i8(DeviceCtx* ctx, const int8_t* a, int8_t* ap, int64_t m, int64_t k,
                            int64_t kp);
 int64_t launch_split_rows_i16(DeviceCtx* ctx, const int16_t* a, int8_t* hi, uint8_t* lo, int64_t m,

@@ -394,7 +394,20 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     at[0].val.clusterDim.z = 1;
     lc.attrs = at;
     lc.numAttrs = 1;
+    if (PAIR == 2) {
+        // Not every SM need be pairable; a pair that is not resident would only start
+        // after another one ends, so size the persistent grid to what fits at once.
+        int fit = 0;
+        if (cudaOccupancyMaxActiveClusters(&fit, kern, &lc) == cudaSuccess && fit > 0 && fit < units) {
+            units = fit;
+            lc.gridDim = dim3((unsigned)(units * PAIR), 1, 1);
+        } else {
+            cudaGetLastError();
+        }
+    }
+    prof_begin(ctx);
     MB200_CUDA(cudaLaunchKernelEx(&lc, kern, ta0, ta1, tb0, tb1, p));
+    prof_end(ctx);
     count_launch();
     return check_launch("gemm_tc_kernel");
 }

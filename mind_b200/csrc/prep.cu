@@ -1,0 +1,175 @@
+// Operand re-layout kernels (pure data movement) that put the caller's row-major
+// operands into the K-contiguous, 16-byte-pitched form the TMA tiles need:
+//   - B (K x N, N contiguous) -> Bt (N x Kp, K contiguous): byte transpose;
+//   - A with an unaligned base or K % 16 != 0 -> padded copy (M x Kp);
+//   - int16 operands -> signed-high / unsigned-low 8-bit limb planes
+//     (a = 256 * hi + lo, hi = a >> 8, lo = a & 255), B transposed on the way.
+// Kp is K rounded up to 16; pad bytes are never read (the tensor map's extent is K).
+#include "common.h"
+
+namespace mb200 {
+namespace {
+
+constexpr int TT = 64;  // transpose tile edge, elements
+
+// grid (ceil(N/64), ceil(K/64)), 256 threads. in: [K][N]; out: [N][kp].
+__global__ void transpose_i8_kernel(const int8_t* __restrict__ b, int8_t* __restrict__ bt, int k,
+                                    int n, int64_t kp) {
+    __shared__ int8_t tile[TT][TT + 4];
+    const int n0 = blockIdx.x * TT, k0 = blockIdx.y * TT;
+    for (int e = threadIdx.x; e < TT * TT; e += blockDim.x) {
+        const int r = e / TT, c = e % TT;  // r: k, c: n (n contiguous in global)
+        const int kk = k0 + r, nn = n0 + c;
+        tile[r][c] = (kk < k && nn < n) ? b[(size_t)kk * n + nn] : (int8_t)0;
+    }
+    __syncthreads();
+    // each thread writes 4 consecutive k of one n as one 32-bit word
+    for (int e = threadIdx.x; e < TT * (TT / 4); e += blockDim.x) {
+        const int r = e / (TT / 4), c4 = (e % (TT / 4)) * 4;  // r: n, c4: k
+        const int nn = n0 + r, kk = k0 + c4;
+        if (nn < n && kk < kp) {
+            const uint32_t w = (uint32_t)(uint8_t)tile[c4][r] | ((uint32_t)(uint8_t)tile[c4 + 1][r] << 8) |
+                               ((uint32_t)(uint8_t)tile[c4 + 2][r] << 16) |
+                               ((uint32_t)(uint8_t)tile[c4 + 3][r] << 24);
+            *reinterpret_cast<uint32_t*>(bt + (size_t)nn * kp + kk) = w;
+        }
+    }
+}
+
+// in: [K][N] int16; out: hi / lo planes [N][kp].
+__global__ void split_transpose_i16_kernel(const int16_t* __restrict__ b, int8_t* __restrict__ bt_hi,
+                                           uint8_t* __restrict__ bt_lo, int k, int n, int64_t kp) {
+    __shared__ int16_t tile[TT][TT + 2];
+    const int n0 = blockIdx.x * TT, k0 = blockIdx.y * TT;
+    for (int e = threadIdx.x; e < TT * TT; e += blockDim.x) {
+        const int r = e / TT, c = e % TT;
+        const int kk = k0 + r, nn = n0 + c;
+        tile[r][c] = (kk < k && nn < n) ? b[(size_t)kk * n + nn] : (int16_t)0;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < TT * (TT / 4); e += blockDim.x) {
+        const int r = e / (TT / 4), c4 = (e % (TT / 4)) * 4;
+        const int nn = n0 + r, kk = k0 + c4;
+        if (nn < n && kk < kp) {
+            uint32_t hi = 0, lo = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int v = tile[c4 + j][r];
+                hi |= (uint32_t)((v >> 8) & 0xff) << (8 * j);
+                lo |= (uint32_t)(v & 0xff) << (8 * j);
+            }
+            *reinterpret_cast<uint32_t*>(bt_hi + (size_t)nn * kp + kk) = hi;
+            *reinterpret_cast<uint32_t*>(bt_lo + (size_t)nn * kp + kk) = lo;
+        }
+    }
+}
+
+// src [rows][cols] int32 -> dst [cols][rows]; grid (ceil(cols/32), ceil(rows/32)), block (32, 8).
+__global__ void transpose_i32_kernel(const int32_t* __restrict__ src, int32_t* __restrict__ dst,
+                                     int64_t rows, int64_t cols) {
+    __shared__ int32_t tile[32][33];
+    const int64_t c0 = (int64_t)blockIdx.x * 32, r0 = (int64_t)blockIdx.y * 32;
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const int64_t r = r0 + j, c = c0 + threadIdx.x;
+        if (r < rows && c < cols) tile[j][threadIdx.x] = src[r * cols + c];
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const int64_t c = c0 + j, r = r0 + threadIdx.x;
+        if (r < rows && c < cols) dst[c * rows + r] = tile[threadIdx.x][j];
+    }
+}
+
+// Row copy into a kp-pitched buffer; grid-stride over rows, threads over bytes.
+__global__ void pad_rows_i8_kernel(const int8_t* __restrict__ a, int8_t* __restrict__ ap, int64_t m,
+                                   int64_t k, int64_t kp) {
+    for (int64_t r = blockIdx.x; r < m; r += gridDim.x)
+        for (int64_t c = threadIdx.x; c < kp; c += blockDim.x)
+            ap[r * kp + c] = c < k ? a[r * k + c] : (int8_t)0;
+}
+
+__global__ void split_rows_i16_kernel(const int16_t* __restrict__ a, int8_t* __restrict__ hi,
+                                      uint8_t* __restrict__ lo, int64_t m, int64_t k, int64_t kp) {
+    for (int64_t r = blockIdx.x; r < m; r += gridDim.x)
+        for (int64_t c = threadIdx.x; c < kp; c += blockDim.x) {
+            const int v = c < k ? (int)a[r * k + c] : 0;
+            hi[r * kp + c] = (int8_t)(v >> 8);
+            lo[r * kp + c] = (uint8_t)(v & 0xff);
+        }
+}
+
+// 8 int16 per thread (one 16-byte load, two 8-byte stores); needs k % 8 == 0,
+// kp == k and a 16-byte aligned base.
+__global__ void split_rows_i16_vec_kernel(const uint4* __restrict__ a, uint2* __restrict__ hi,
+                                          uint2* __restrict__ lo, int64_t n8) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n8;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const uint4 v = a[i];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t h[2], l[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint32_t w0 = w[2 * j], w1 = w[2 * j + 1];
+            l[j] = (w0 & 0xff) | ((w0 >> 8) & 0xff00) | ((w1 & 0xff) << 16) | ((w1 << 8) & 0xff000000u);
+            h[j] = ((w0 >> 8) & 0xff) | ((w0 >> 16) & 0xff00) | ((w1 << 8) & 0xff0000) | (w1 & 0xff000000u);
+        }
+        hi[i] = make_uint2(h[0], h[1]);
+        lo[i] = make_uint2(l[0], l[1]);
+    }
+}
+
+}  // namespace
+
+int64_t launch_transpose_i8(DeviceCtx* ctx, const int8_t* b, int8_t* bt, int64_t k, int64_t n,
+                            int64_t kp) {
+    dim3 grid((unsigned)((n + TT - 1) / TT), (unsigned)((kp + TT - 1) / TT));
+    if (grid.y > 65535) return fail(MIND_B200_ERR_TOO_LARGE, "K above 4194240 is not supported");
+    transpose_i8_kernel<<<grid, 256, 0, ctx->stream>>>(b, bt, (int)k, (int)n, kp);
+    count_launch();
+    return check_launch("transpose_i8_kernel");
+}
+
+int64_t launch_split_transpose_i16(DeviceCtx* ctx, const int16_t* b, int8_t* bt_hi, uint8_t* bt_lo,
+                                   int64_t k, int64_t n, int64_t kp) {
+    dim3 grid((unsigned)((n + TT - 1) / TT), (unsigned)((kp + TT - 1) / TT));
+    if (grid.y > 65535) return fail(MIND_B200_ERR_TOO_LARGE, "K above 4194240 is not supported");
+    split_transpose_i16_kernel<<<grid, 256, 0, ctx->stream>>>(b, bt_hi, bt_lo, (int)k, (int)n, kp);
+    count_launch();
+    return check_launch("split_transpose_i16_kernel");
+}
+
+int64_t launch_transpose_i32(DeviceCtx* ctx, const int32_t* src, int32_t* dst, int64_t rows,
+                             int64_t cols) {
+    dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32));
+    if (grid.y > 65535) return fail(MIND_B200_ERR_TOO_LARGE, "more than 2097120 rows to transpose");
+    transpose_i32_kernel<<<grid, dim3(32, 8), 0, ctx->stream>>>(src, dst, rows, cols);
+    count_launch();
+    return check_launch("transpose_i32_kernel");
+}
+
+int64_t launch_pad_rows_i8(DeviceCtx* ctx, const int8_t* a, int8_t* ap, int64_t m, int64_t k,
+                           int64_t kp) {
+    unsigned grid = (unsigned)(m < 148 * 16 ? m : 148 * 16);
+    pad_rows_i8_kernel<<<grid, 256, 0, ctx->stream>>>(a, ap, m, k, kp);
+    count_launch();
+    return check_launch("pad_rows_i8_kernel");
+}
+
+int64_t launch_split_rows_i16(DeviceCtx* ctx, const int16_t* a, int8_t* hi, uint8_t* lo, int64_t m,
+                              int64_t k, int64_t kp) {
+    if (kp == k && k % 8 == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0) {
+        const int64_t n8 = m * k / 8;
+        int64_t blocks = (n8 + 255) / 256;
+        if (blocks > 148 * 32) blocks = 148 * 32;
+        split_rows_i16_vec_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(
+            reinterpret_cast<const uint4*>(a), reinterpret_cast<uint2*>(hi),
+            reinterpret_cast<uint2*>(lo), n8);
+    } else {
+        unsigned grid = (unsigned)(m < 148 * 16 ? m : 148 * 16);
+        split_rows_i16_kernel<<<grid, 256, 0, ctx->stream>>>(a, hi, lo, m, k, kp);
+    }
+    count_launch();
+    return check_launch("split_rows_i16_kernel");
+}
+
+}  // namespace mb200

@@ -1,0 +1,104 @@
+// Device-side seeded input generator (the reference's LCG with jump-ahead) and
+// the wrap-around matrix x vector used for exact large-shape checks.
+#include "common.h"
+
+namespace mb200 {
+namespace {
+
+constexpr uint64_t LCG_A = 1664525ull, LCG_C = 1013904223ull;
+constexpr int LCG_CHUNK = 16;  // consecutive elements per thread
+
+// State after `steps` steps from s0: the affine map x -> a*x + c raised to `steps`.
+__device__ __forceinline__ uint64_t lcg_jump(uint64_t s0, uint64_t steps) {
+    uint64_t a = 1, c = 0, ca = LCG_A, cc = LCG_C;
+    while (steps) {
+        if (steps & 1) {
+            a = ca * a;
+            c = ca * c + cc;
+        }
+        cc = (ca + 1) * cc;
+        ca = ca * ca;
+        steps >>= 1;
+    }
+    return a * s0 + c;
+}
+
+template <int KIND>
+__global__ void lcg_fill_kernel(void* __restrict__ dst, int64_t n, uint64_t seed, uint64_t offset,
+                                int shift) {
+    const int64_t chunks = (n + LCG_CHUNK - 1) / LCG_CHUNK;
+    for (int64_t ch = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; ch < chunks;
+         ch += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t i0 = ch * LCG_CHUNK;
+        uint64_t s = lcg_jump(seed, offset + (uint64_t)i0);
+        const int64_t i1 = i0 + LCG_CHUNK < n ? i0 + LCG_CHUNK : n;
+        for (int64_t i = i0; i < i1; ++i) {
+            s = s * LCG_A + LCG_C;
+            const uint32_t u = (uint32_t)(s >> 16);
+            if (KIND == 0)
+                static_cast<int32_t*>(dst)[i] = (int32_t)u >> shift;
+            else if (KIND == 1)
+                static_cast<int8_t*>(dst)[i] = (int8_t)(u >> 16);
+            else
+                static_cast<int16_t*>(dst)[i] = (int16_t)(u >> 16);
+        }
+    }
+}
+
+// out[r] = sum_c mat[r,c] * v[c] mod 2^32; one warp per row.
+template <typename T>
+__global__ void matvec_wrap_kernel(const T* __restrict__ mat, int64_t rows, int64_t cols,
+                                   const int32_t* __restrict__ v, int32_t* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t r = warp; r < rows; r += nwarps) {
+        const T* row = mat + r * cols;
+        uint32_t acc = 0;
+        for (int64_t c = lane; c < cols; c += 32) acc += (uint32_t)(int32_t)row[c] * (uint32_t)v[c];
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) out[r] = (int32_t)acc;
+    }
+}
+
+}  // namespace
+
+int64_t launch_lcg_fill(DeviceCtx* ctx, void* dst, int64_t n, int kind, uint64_t seed,
+                        uint64_t offset, int shift) {
+    if (n <= 0) return 0;
+    const int64_t chunks = (n + LCG_CHUNK - 1) / LCG_CHUNK;
+    int64_t blocks = (chunks + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (kind == 0)
+        lcg_fill_kernel<0><<<(unsigned)blocks, 256, 0, ctx->stream>>>(dst, n, seed, offset, shift);
+    else if (kind == 1)
+        lcg_fill_kernel<1><<<(unsigned)blocks, 256, 0, ctx->stream>>>(dst, n, seed, offset, shift);
+    else if (kind == 2)
+        lcg_fill_kernel<2><<<(unsigned)blocks, 256, 0, ctx->stream>>>(dst, n, seed, offset, shift);
+    else
+        return fail(MIND_B200_ERR_INVALID, "lcg_fill: kind must be 0 (q16), 1 (i8) or 2 (i16)");
+    count_launch();
+    return check_launch("lcg_fill_kernel");
+}
+
+int64_t launch_matvec_wrap(DeviceCtx* ctx, const void* mat, int elem_bytes, int64_t rows,
+                           int64_t cols, const int32_t* v, int32_t* out) {
+    if (rows <= 0) return 0;
+    int64_t blocks = (rows + 7) / 8;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (elem_bytes == 1)
+        matvec_wrap_kernel<int8_t><<<(unsigned)blocks, 256, 0, ctx->stream>>>(
+            static_cast<const int8_t*>(mat), rows, cols, v, out);
+    else if (elem_bytes == 2)
+        matvec_wrap_kernel<int16_t><<<(unsigned)blocks, 256, 0, ctx->stream>>>(
+            static_cast<const int16_t*>(mat), rows, cols, v, out);
+    else if (elem_bytes == 4)
+        matvec_wrap_kernel<int32_t><<<(unsigned)blocks, 256, 0, ctx->stream>>>(
+            static_cast<const int32_t*>(mat), rows, cols, v, out);
+    else
+        return fail(MIND_B200_ERR_INVALID, "matvec_wrap: elem_bytes must be 1, 2 or 4");
+    count_launch();
+    return check_launch("matvec_wrap_kernel");
+}
+
+}  // namespace mb200

@@ -1,0 +1,228 @@
+"""Device-resident operands, the on-device input generator, the benchmark
+configurations at full size (checked through size-independent properties where the
+O(N^3) oracle is too slow), determinism across repeats, and the runtime mirror."""
+import ctypes as C
+import json
+import os
+
+import numpy as np
+import pytest
+
+import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SELF = json.load(open(os.path.join(HERE, "golden", "oracle_hashes.json")))
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(autouse=True)
+def _stream(gpu):
+    torch.cuda.set_device(0)
+    gpu.set_stream(torch.cuda.current_stream().cuda_stream)
+    gpu.set_gemm_path(0)
+    yield
+    gpu.set_gemm_path(0)
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def lcg_dev(gpu, n, kind, seed, offset=0, shift=12):
+    dt = {0: torch.int32, 1: torch.int8, 2: torch.int16}[kind]
+    t = torch.empty(n, dtype=dt, device="cuda")
+    gpu.lcg_fill(t, n, kind, seed, offset, shift)
+    return t
+
+
+def test_device_generator_matches_host(gpu):
+    seed = 0xDEADBEEF00000000 ^ 12345
+    n = 100003
+    g = O.Lcg(seed)
+    a8, b16, c32 = g.i8(n), g.i16(n), g.q16(n, 13)
+    assert np.array_equal(lcg_dev(gpu, n, 1, seed).cpu().numpy(), a8)
+    assert np.array_equal(lcg_dev(gpu, n, 2, seed, offset=n).cpu().numpy(), b16)
+    assert np.array_equal(lcg_dev(gpu, n, 0, seed, offset=2 * n, shift=13).cpu().numpy(), c32)
+    host = np.empty(77, dtype=np.int8)  # host destination goes through staging
+    gpu.lcg_fill(host, 77, 1, seed)
+    assert np.array_equal(host, a8[:77])
+
+
+def test_device_pointers_all_kernels(gpu):
+    g = O.Lcg(5)
+    m, k, n = 200, 320, 136
+    a, b = g.i8(m * k), g.i8(k * n)
+    for path in (0, 2, 1):
+        gpu.set_gemm_path(path)
+        c = torch.full((m * n,), -1, dtype=torch.int32, device="cuda")
+        gpu.matmul_mm_i8_v(dev(a), dev(b), c, m, k, n)
+        gpu.synchronize()
+        assert np.array_equal(c.cpu().numpy(), O.gemm_i8(a, b, m, k, n)), path
+    a, b = g.i16(m * k), g.i16(k * n)
+    for path in (0, 2, 1):
+        gpu.set_gemm_path(path)
+        c = torch.full((m * n,), -1, dtype=torch.int32, device="cuda")
+        gpu.matmul_mm_i16(dev(a), dev(b), c, m, k, n)
+        gpu.synchronize()
+        assert np.array_equal(c.cpu().numpy(), O.gemm_i16(a, b, m, k, n)), path
+    a, b = g.q16(m * k), g.q16(k * n)
+    c = torch.full((m * n,), -1, dtype=torch.int32, device="cuda")
+    gpu.matmul_mm_q16_v(dev(a), dev(b), c, m, k, n)
+    y = torch.full((m,), -1, dtype=torch.int32, device="cuda")
+    gpu.gemv_q16_mt(dev(a), dev(b[:k]), y, m, k)
+    gpu.synchronize()
+    assert np.array_equal(c.cpu().numpy(), O.gemm_q16(a, b, m, k, n))
+    assert np.array_equal(y.cpu().numpy(), O.gemv_q16(a, b[:k], m, k))
+    # mixed: host A, device B, host C
+    ch = np.empty(m * n, dtype=np.int32)
+    gpu.matmul_mm_q16_v(a, dev(b), ch, m, k, n)
+    assert np.array_equal(ch, O.gemm_q16(a, b, m, k, n))
+
+
+def test_config1_int8_256(gpu):
+    e = SELF["gemm-i8-256x256x256"]
+    a = lcg_dev(gpu, 256 * 256, 1, e["seed"])
+    b = lcg_dev(gpu, 256 * 256, 1, e["seed"], offset=256 * 256)
+    hashes = set()
+    for path in (0, 2, 1):
+        gpu.set_gemm_path(path)
+        for _ in range(16):  # the reference's same-process repeat gate uses 16 fresh buffers
+            c = torch.empty(256 * 256, dtype=torch.int32, device="cuda")
+            gpu.matmul_mm_i8_v(a, b, c, 256, 256, 256)
+            hashes.add(O.canonical_hash_i32(c.cpu().numpy()))
+    assert hashes == {e["sha256"]}
+
+
+def test_config2_q16_1024(gpu):
+    e = SELF["gemm-q16-1024x1024x1024-shift13"]
+    n = 1024
+    a = lcg_dev(gpu, n * n, 0, e["seed"], shift=13)
+    b = lcg_dev(gpu, n * n, 0, e["seed"], offset=n * n, shift=13)
+    c = torch.empty(n * n, dtype=torch.int32, device="cuda")
+    gpu.matmul_mm_q16_v(a, b, c, n, n, n)
+    assert O.canonical_hash_i32(c.cpu().numpy()) == e["sha256"]
+
+
+def freivalds(gpu, a, b, c, m, k, n, elem_bytes, rounds=4):
+    """Exact check in Z/2^32: C.v == A.(B.v) for random int32 vectors v."""
+    gen = torch.Generator(device="cuda").manual_seed(1234)
+    for _ in range(rounds):
+        v = torch.randint(-2**31, 2**31 - 1, (n,), dtype=torch.int32, device="cuda", generator=gen)
+        bv = torch.empty(k, dtype=torch.int32, device="cuda")
+        abv = torch.empty(m, dtype=torch.int32, device="cuda")
+        cv = torch.empty(m, dtype=torch.int32, device="cuda")
+        gpu.matvec_wrap(b, elem_bytes, k, n, v, bv)
+        gpu.matvec_wrap(a, elem_bytes, m, k, bv, abv)
+        gpu.matvec_wrap(c, 4, m, n, v, cv)
+        gpu.synchronize()
+        if not torch.equal(abv, cv):
+            return False
+    return True
+
+
+def test_matvec_wrap_helper(gpu):
+    g = O.Lcg(3)
+    m, k = 37, 91
+    a = g.i16(m * k)
+    v = g.q16(k, 0)
+    out = np.empty(m, dtype=np.int32)
+    gpu.matvec_wrap(a, 2, m, k, v, out)
+    want = (a.reshape(m, k).astype(np.int64) @ v.astype(np.int64)).astype(np.int32)
+    assert np.array_equal(out, want)
+
+
+@pytest.mark.parametrize("path", [0, 2])
+def test_config3_i16_4096(gpu, path):
+    gpu.set_gemm_path(path)
+    n = 4096
+    seed = 0xDEADBEEF00000000 ^ 4096
+    a = lcg_dev(gpu, n * n, 2, seed)
+    b = lcg_dev(gpu, n * n, 2, seed, offset=n * n)
+    c = torch.empty(n * n, dtype=torch.int32, device="cuda")
+    gpu.matmul_mm_i16(a, b, c, n, n, n)
+    gpu.synchronize()
+    assert freivalds(gpu, a, b, c, n, n, n, 2)
+    # sampled row bands against the CPU oracle: first, last, and one in the middle
+    ah, bh, ch = a.cpu().numpy(), b.cpu().numpy(), c.cpu().numpy().reshape(n, n)
+    for r0 in (0, 2047, n - 2):
+        want = O.gemm_i16(ah[r0 * n:(r0 + 2) * n], bh, 2, n, n).reshape(2, n)
+        assert np.array_equal(ch[r0:r0 + 2], want)
+    # and the whole matrix against the independent CUDA-core kernel
+    gpu.set_gemm_path(1)
+    c2 = torch.empty(n * n, dtype=torch.int32, device="cuda")
+    gpu.matmul_mm_i16(a, b, c2, n, n, n)
+    gpu.synchronize()
+    assert torch.equal(c, c2)
+
+
+def test_config4_gemv_16384(gpu):
+    n = 16384
+    seed = 0xDEADBEEF00000000 ^ ((n << 20) ^ n)
+    w = lcg_dev(gpu, n * n, 0, seed, shift=15)
+    x = lcg_dev(gpu, n, 0, seed, offset=n * n, shift=15)
+    y = torch.empty(n, dtype=torch.int32, device="cuda")
+    gpu.gemv_q16_mt(w, x, y, n, n)
+    gpu.synchronize()
+    want, _ = O.baseline_gemv_q16(w.cpu().numpy(), x.cpu().numpy(), n, n)
+    assert np.array_equal(y.cpu().numpy(), want)
+    # 256 stability re-runs, as the reference's MT bench does (benches/det_gemv_q16_mt.rs:71)
+    for _ in range(256):
+        y2 = torch.empty(n, dtype=torch.int32, device="cuda")
+        gpu.gemv_q16_mt(w, x, y2, n, n)
+        assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("path", [0, 2])
+def test_config5_int8_16384(gpu, path):
+    gpu.set_gemm_path(path)
+    n = 16384
+    seed = 0xDEADBEEF00000000 ^ 16384
+    a = lcg_dev(gpu, n * n, 1, seed)
+    b = lcg_dev(gpu, n * n, 1, seed, offset=n * n)
+    c = torch.empty(n * n, dtype=torch.int32, device="cuda")
+    gpu.matmul_mm_i8_v(a, b, c, n, n, n)
+    gpu.synchronize()
+    assert freivalds(gpu, a, b, c, n, n, n, 1)
+    ah, bh = a[: 2 * n].cpu().numpy(), b.cpu().numpy()
+    assert np.array_equal(c[: 2 * n].cpu().numpy(), O.gemm_i8(ah, bh, 2, n, n))
+    ah = a[(n - 2) * n:].cpu().numpy()
+    assert np.array_equal(c[(n - 2) * n:].cpu().numpy(), O.gemm_i8(ah, bh, 2, n, n))
+    # a row-sharded run (2 bands, as 2 GPUs would split it) gives the same bytes
+    c2 = torch.empty(n * n, dtype=torch.int32, device="cuda")
+    half = n // 2
+    gpu.matmul_mm_i8_v(a[: half * n], b, c2[: half * n], half, n, n)
+    gpu.matmul_mm_i8_v(a[half * n:], b, c2[half * n:], half, n, n)
+    gpu.synchronize()
+    assert torch.equal(c, c2)
+
+
+def test_runtime_mirror(gpu):
+    """allocate / run_op / synchronize / deallocate (src/runtime_interface.rs:26-52)."""
+    import mind_b200
+    L = mind_b200.lib()
+    m, k, n = 48, 80, 32
+    g = O.Lcg(21)
+    a, b = g.i8(m * k), g.i8(k * n)
+
+    def alloc(dtype, *shape):
+        h = C.c_int64(0)
+        arr = (C.c_int64 * len(shape))(*shape)
+        assert L.mind_b200_rt_allocate(dtype, arr, len(shape), C.byref(h)) == 0
+        return h.value
+
+    ha, hb, hc = alloc(0, m, k), alloc(0, k, n), alloc(2, m, n)
+    assert L.mind_b200_rt_upload(ha, a.ctypes.data, a.nbytes) == 0
+    assert L.mind_b200_rt_upload(hb, b.ctypes.data, b.nbytes) == 0
+    ins, outs = (C.c_int64 * 2)(ha, hb), (C.c_int64 * 1)(hc)
+    assert L.mind_b200_rt_run_op(b"matmul_mm_i8_v", ins, 2, outs, 1) == 0
+    assert L.mind_b200_rt_synchronize() == 0
+    c = np.empty(m * n, dtype=np.int32)
+    assert L.mind_b200_rt_download(hc, c.ctypes.data, c.nbytes) == 0
+    assert np.array_equal(c, O.gemm_i8(a, b, m, k, n))
+    assert L.mind_b200_rt_run_op(b"no_such_op", ins, 2, outs, 1) == mind_b200.ERR_INVALID
+    assert b"unknown op" in L.mind_b200_last_error()
+    for h in (ha, hb, hc):
+        assert L.mind_b200_rt_deallocate(h) == 0
+    assert L.mind_b200_rt_deallocate(ha) == mind_b200.ERR_INVALID

@@ -1,0 +1,260 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI, on a real B200.
+
+Integer work: every comparison is bit-exact (np.array_equal / sha256 equality)."""
+import json
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF = json.load(open(os.path.join(HERE, "golden", "reference_hashes.json")))
+SELF = json.load(open(os.path.join(HERE, "golden", "oracle_hashes.json")))
+SEED = 0xDEADBEEF
+
+
+def ref_hash(w):
+    return next(iter(REF[w]["hashes"].values()))
+
+
+# Tile edges of the GPU kernels (128 / 256 rows, 128-byte K slabs, 16-byte pitches).
+GEMM_SHAPES = [
+    (1, 1, 1), (1, 16, 1), (7, 15, 7), (63, 17, 65), (64, 64, 64), (65, 31, 63),
+    (127, 32, 129), (128, 128, 256), (129, 33, 255), (255, 127, 257), (256, 129, 128),
+    (257, 130, 1), (1, 511, 257), (130, 513, 70), (128, 1, 256), (300, 256, 520),
+    (5, 0, 9), (384, 1024, 512), (100, 2048, 36),
+]
+PATHS = [0, 2, 1]  # tensor cores (1 CTA per tile), tensor cores (CTA pairs), CUDA cores
+
+
+@pytest.fixture(autouse=True)
+def _default_path(gpu):
+    gpu.set_gemm_path(0)
+    yield
+    gpu.set_gemm_path(0)
+
+
+# --------------------------------------------------------------- golden vectors
+def test_golden_gemm_i8_all_paths(gpu):
+    g = O.Lcg(SEED)
+    a, b = g.i8(64 * 64), g.i8(64 * 64)
+    for path in PATHS:
+        gpu.set_gemm_path(path)
+        for fn in (gpu.matmul_mm_i8_v, gpu.matmul_mm_i8_mt_v):
+            c = np.full(64 * 64, -1, dtype=np.int32)
+            assert fn(a, b, c, 64, 64, 64) == 0
+            assert O.canonical_hash_i32(c) == ref_hash("gemm-i8-64x64x64"), path
+
+
+def test_golden_gemm_q16(gpu):
+    g = O.Lcg(SEED)
+    a, b = g.q16(64 * 64), g.q16(64 * 64)
+    for fn in (gpu.matmul_mm_q16_v, gpu.matmul_mm_q16_mt_v):
+        c = np.full(64 * 64, -1, dtype=np.int32)
+        fn(a, b, c, 64, 64, 64)
+        assert O.canonical_hash_i32(c) == ref_hash("gemm-q16-fused-64x64x64")
+    bt = np.ascontiguousarray(b.reshape(64, 64).T).reshape(-1)
+    c = np.full(64 * 64, -1, dtype=np.int32)
+    gpu.gemmq_bt(a, bt, c, 64, 64, 64)
+    assert O.canonical_hash_i32(c) == ref_hash("gemm-q16-64x64x64")
+
+
+def test_golden_gemv_and_dots(gpu):
+    g = O.Lcg(SEED)
+    w, x = g.q16(256 * 256), g.q16(256)
+    for fn in (gpu.gemv_q16_mt, gpu.matmul_rmajor_q16_v):
+        y = np.full(256, -1, dtype=np.int32)
+        fn(w, x, y, 256, 256)
+        assert O.canonical_hash_i32(y) == ref_hash("gemv-q16-256x256")
+    g = O.Lcg(SEED)
+    w, x = g.i16(256 * 256), g.i16(256)
+    y = np.full(256, -1, dtype=np.int32)
+    gpu.matmul_rmajor_i16_v(w, x, y, 256, 256)
+    assert O.canonical_hash_i32(y) == ref_hash("gemv-i16-256x256")
+    g = O.Lcg(SEED)
+    a, b = g.q16(65536), g.q16(65536)
+    assert O.canonical_hash_i64_scalar(gpu.dot_q16_v(a, b, 65536)) == ref_hash("dot-l2-q16")
+    assert O.canonical_hash_i64_scalar(gpu.dot_l1_q16_v(a, b, 65536)) == ref_hash("dot-l1-q16")
+    g = O.Lcg(SEED)
+    a, b = g.i16(4096), g.i16(4096)
+    assert O.canonical_hash_i64_scalar(gpu.dot_i16_v(a, b, 4096)) == ref_hash("dot-i16-4096")
+
+
+def test_reference_xnode_driver_runs_unmodified(gpu):
+    """The reference's own C driver (compiled from its sources) against this library."""
+    if not os.path.exists(O.REF_DRIVER_PATH):
+        pytest.skip("oracle/_ref/xnode_driver was not built (no reference checkout at build time)")
+    import mind_b200
+    r = subprocess.run([O.REF_DRIVER_PATH, mind_b200.LIB_PATH, "b200"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "all canaries MATCH" in r.stdout
+    out = dict(line.split()[:2] for line in r.stdout.splitlines() if line.startswith("  "))
+    for w in ("dot-l2-q16", "dot-l1-q16", "gemv-q16-256x256", "gemv-i16-256x256",
+              "gemm-q16-64x64x64", "gemm-i8-64x64x64"):
+        assert out[w] == ref_hash(w), w
+
+
+# ------------------------------------------------------------------ edge shapes
+@pytest.mark.parametrize("path", PATHS)
+def test_gemm_i8_shapes(gpu, path):
+    gpu.set_gemm_path(path)
+    for (m, k, n) in GEMM_SHAPES:
+        g = O.Lcg(0xDEADBEEF00000000 ^ (m * 1000003 + k * 1009 + n))
+        a, b = g.i8(m * k), g.i8(k * n)
+        c = np.full(m * n + 8, 0x5A5A5A5A, dtype=np.int32)  # canary after the output
+        gpu.matmul_mm_i8_v(a, b, c, m, k, n)
+        assert np.array_equal(c[: m * n], O.gemm_i8(a, b, m, k, n)), (path, m, k, n)
+        assert np.all(c[m * n :] == 0x5A5A5A5A), (path, m, k, n)
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_gemm_i16_shapes(gpu, path):
+    gpu.set_gemm_path(path)
+    for (m, k, n) in GEMM_SHAPES:
+        g = O.Lcg(0xDEADBEEF00000000 ^ (m * 1000003 + k * 1009 + n + 1))
+        a, b = g.i16(m * k), g.i16(k * n)  # full range: sums wrap for k >= 2
+        c = np.full(m * n + 8, 0x5A5A5A5A, dtype=np.int32)
+        gpu.matmul_mm_i16(a, b, c, m, k, n)
+        assert np.array_equal(c[: m * n], O.gemm_i16(a, b, m, k, n)), (path, m, k, n)
+        assert np.all(c[m * n :] == 0x5A5A5A5A)
+
+
+def test_gemm_q16_shapes(gpu):
+    for (m, k, n) in GEMM_SHAPES:
+        for shift in (12, 0):  # the reference's range, and full range (wrap past 2^31)
+            g = O.Lcg(0xDEADBEEF00000000 ^ (m * 1000003 + k * 1009 + n + 2))
+            a, b = g.q16(m * k, shift), g.q16(k * n, shift)
+            c = np.full(m * n + 8, 0x5A5A5A5A, dtype=np.int32)
+            gpu.matmul_mm_q16_v(a, b, c, m, k, n)
+            assert np.array_equal(c[: m * n], O.gemm_q16(a, b, m, k, n)), (m, k, n, shift)
+            assert np.all(c[m * n :] == 0x5A5A5A5A)
+
+
+def test_q16_extreme_values(gpu):
+    """INT_MIN / INT_MAX / -1 / 0x7FFF8000...: the hi/lo split must be exact everywhere."""
+    specials = np.array([-2**31, 2**31 - 1, -1, 0, 1, 0x7FFF8000, 0x7FFF7FFF, -0x8000, 0x8000,
+                         0x7FFF, -0x7FFF, 0xFFFF, -0x10000, 0x10000, -0x7FFF8000, 65535 * 32768],
+                        dtype=np.int64).astype(np.int32)
+    k = specials.size
+    a = np.ascontiguousarray(np.tile(specials, (k, 1)))            # every special in every row
+    b = np.ascontiguousarray(np.stack([np.roll(specials, s) for s in range(k)], axis=1))
+    c = np.empty(k * k, dtype=np.int32)
+    gpu.matmul_mm_q16_v(a.reshape(-1), b.reshape(-1), c, k, k, k)
+    assert np.array_equal(c, O.gemm_q16(a.reshape(-1), b.reshape(-1), k, k, k))
+    for r in range(k):
+        x = np.ascontiguousarray(np.roll(specials, r))
+        y = np.empty(1, dtype=np.int32)
+        gpu.gemv_q16_mt(specials, x, y, 1, k)
+        assert int(y[0]) == O.dot_q16(specials, x)
+        assert gpu.dot_q16_v(specials, x, k) == O.dot_q16(specials, x)
+        assert gpu.dot_l1_q16_v(specials, x, k) == O.dot_l1_q16(specials, x)
+
+
+def test_wrap_fixture_and_overflowing_i8(gpu):
+    e = SELF["gemm-q16-64x64x64-shift0-wrap"]
+    g = O.Lcg(e["seed"])
+    a, b = g.q16(64 * 64, 0), g.q16(64 * 64, 0)
+    c = np.empty(64 * 64, dtype=np.int32)
+    gpu.matmul_mm_q16_v(a, b, c, 64, 64, 64)
+    assert O.canonical_hash_i32(c) == e["sha256"]
+    # int8: all -128 x -128 with K = 2^17 + 256 sums to 2^31 + 2^22: i32 wraps
+    m, k, n = 128, (1 << 17) + 256, 16
+    a = np.full(m * k, -128, dtype=np.int8)
+    b = np.full(k * n, -128, dtype=np.int8)
+    for path in (0, 2):
+        gpu.set_gemm_path(path)
+        c = np.empty(m * n, dtype=np.int32)
+        gpu.matmul_mm_i8_v(a, b, c, m, k, n)
+        want = np.int64(16384) * k
+        assert np.all(c.astype(np.int64) == ((want + 2**31) % 2**32) - 2**31)
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 1), (2, 3), (4, 4), (8, 16), (16, 9), (3, 65), (512, 130),
+                                       (256, 130), (11922, 384), (5, 0), (3, 4096), (1, 65537), (700, 2048)])
+def test_gemv_shapes(gpu, rows, cols):
+    g = O.Lcg(0xDEADBEEF00000000 ^ ((rows << 20) ^ cols))
+    w, x = g.q16(rows * cols), g.q16(cols)
+    y = np.full(rows + 4, 0x5A5A5A5A, dtype=np.int32)
+    gpu.gemv_q16_mt(w, x, y, rows, cols)
+    assert np.array_equal(y[:rows], O.gemv_q16(w, x, rows, cols))
+    assert np.all(y[rows:] == 0x5A5A5A5A)
+    w, x = g.i16(rows * cols), g.i16(cols)
+    y = np.full(rows + 4, 0x5A5A5A5A, dtype=np.int32)
+    gpu.matmul_rmajor_i16_v(w, x, y, rows, cols)
+    assert np.array_equal(y[:rows], O.gemv_i16(w, x, rows, cols))
+    assert np.all(y[rows:] == 0x5A5A5A5A)
+
+
+def test_gemv_fixture_512x130(gpu):
+    e = SELF["gemv-q16-512x130"]
+    g = O.Lcg(e["seed"])
+    w, x = g.q16(512 * 130), g.q16(130)
+    y = np.empty(512, dtype=np.int32)
+    gpu.gemv_q16_mt(w, x, y, 512, 130)
+    assert O.canonical_hash_i32(y) == e["sha256"]
+
+
+@pytest.mark.parametrize("n", [1, 2, 7, 8, 9, 15, 16, 17, 31, 32, 33, 1024, 4096, 65537])
+def test_dot_lengths(gpu, n):
+    """Lengths of the reference's smoke test (tests/blas_vec_q16_smoke.rs:96)."""
+    g = O.Lcg(0x1234 + n)
+    a, b = g.q16(n, 0), g.q16(n, 0)
+    assert gpu.dot_q16_v(a, b, n) == O.dot_q16(a, b)
+    assert gpu.dot_l1_q16_v(a, b, n) == O.dot_l1_q16(a, b)
+    a, b = g.i16(n), g.i16(n)
+    assert gpu.dot_i16_v(a, b, n) == O.dot_i16(a, b)
+
+
+def test_matmul_row_equals_dot(gpu):
+    """tests/blas_vec_q16_smoke.rs:577-624: each matmul row equals the dot of that row."""
+    g = O.Lcg(7)
+    rows, cols = 9, 133
+    w, x = g.q16(rows * cols), g.q16(cols)
+    y = np.empty(rows, dtype=np.int32)
+    gpu.matmul_rmajor_q16_v(w, x, y, rows, cols)
+    for r in range(rows):
+        assert int(y[r]) == gpu.dot_q16_v(np.ascontiguousarray(w[r * cols:(r + 1) * cols]), x, cols)
+
+
+def test_unaligned_operands(gpu):
+    """Any element-aligned address is legal input (the reference loads with alignment 1/2/4)."""
+    m, k, n = 70, 48, 36
+    g = O.Lcg(11)
+    for path in PATHS:
+        gpu.set_gemm_path(path)
+        abuf, bbuf = g.i8(m * k + 3), g.i8(k * n + 5)
+        a, b = abuf[3:], bbuf[5:]
+        cbuf = np.zeros(m * n + 1, dtype=np.int32)
+        gpu.matmul_mm_i8_v(a.ctypes.data, b.ctypes.data, cbuf[1:].ctypes.data, m, k, n)
+        assert np.array_equal(cbuf[1:], O.gemm_i8(a.copy(), b.copy(), m, k, n))
+        abuf, bbuf = g.i16(m * k + 1), g.i16(k * n + 3)
+        a, b = abuf[1:], bbuf[3:]
+        gpu.matmul_mm_i16(a.ctypes.data, b.ctypes.data, cbuf[1:].ctypes.data, m, k, n)
+        assert np.array_equal(cbuf[1:], O.gemm_i16(a.copy(), b.copy(), m, k, n))
+    abuf, bbuf = g.q16(m * k + 1), g.q16(k * n + 3)
+    a, b = abuf[1:], bbuf[3:]
+    cbuf = np.zeros(m * n + 1, dtype=np.int32)
+    gpu.matmul_mm_q16_v(a.ctypes.data, b.ctypes.data, cbuf[1:].ctypes.data, m, k, n)
+    assert np.array_equal(cbuf[1:], O.gemm_q16(a.copy(), b.copy(), m, k, n))
+    wbuf, xbuf = g.q16(m * k + 1), g.q16(k + 1)
+    y = np.zeros(m + 1, dtype=np.int32)
+    gpu.gemv_q16_mt(wbuf[1:].ctypes.data, xbuf[1:].ctypes.data, y[1:].ctypes.data, m, k)
+    assert np.array_equal(y[1:], O.gemv_q16(wbuf[1:].copy(), xbuf[1:].copy(), m, k))
+
+
+def test_errors_do_not_abort(gpu):
+    import mind_b200
+    a = np.zeros(16, dtype=np.int8)
+    c = np.zeros(16, dtype=np.int32)
+    with pytest.raises(mind_b200.MindB200Error) as e:
+        gpu.matmul_mm_i8_v(0, a, c, 4, 4, 4)
+    assert e.value.code == mind_b200.ERR_INVALID
+    with pytest.raises(mind_b200.MindB200Error):
+        gpu.matmul_mm_q16_v(a.ctypes.data + 1, a, c, 2, 2, 2)  # misaligned int32
+    gpu.matmul_mm_i8_v(a, a, c, 4, 4, 4)  # and the library still works afterwards
+    assert np.all(c == 0)
