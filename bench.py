@@ -75,12 +75,19 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.proc, self.lines = index, None, []
+        self.t_begin, self.t_end = 0.0, float("inf")
+
+    def mark_begin(self):
+        self.t_begin = time.perf_counter()
+
+    def mark_end(self):
+        self.t_end = time.perf_counter()
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50", "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:
@@ -88,7 +95,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
 
     def stop(self):
         if not self.proc:
@@ -100,7 +107,11 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons, power = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        inside = [l for (t, l) in self.lines if self.t_begin <= t <= self.t_end + 0.05]
+        window = "timed region"
+        if not inside:  # region shorter than one sampling period: fall back to the whole run
+            inside, window = [l for (_, l) in self.lines], "whole run (timed region shorter than a sample)"
+        for line in inside:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 7:
                 continue
@@ -113,7 +124,7 @@ class ClockSampler:
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None,
                 "sm_max_mhz": max(mx) if mx else None, "power_w_max": max(power) if power else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "window": window, "reasons": sorted(reasons)}
 
 
 # ----------------------------------------------------------------- CPU baseline
@@ -268,14 +279,15 @@ def run_mine(args, w):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()  # nvidia-smi takes a moment to come up: start it before the warm-up
     for _ in range(args.warmup):
         if flush is not None:
             flush.fill_(1)
         step(a, b, c)
     barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    sampler.mark_begin()
     launches0 = blas.kernel_launches()
     blas.profile(True)
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
@@ -286,6 +298,7 @@ def run_mine(args, w):
         step(a, b, c)
         e1.record(stream)
     barrier()
+    sampler.mark_end()
     launches = blas.kernel_launches() - launches0
     n_main, main_ms = blas.profile_read()
     blas.profile(False)
@@ -362,11 +375,11 @@ def run_mine(args, w):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="mine", choices=["mine", "reference"])
     ap.add_argument("--workload", default="gemm_i8", choices=sorted(WORKLOADS))
-    ap.add_argument("--path", type=int, default=0, help="0: one CTA per tile, 2: CTA pairs, 1: CUDA cores")
+    ap.add_argument("--path", type=int, default=0, help="0: auto, 2: CTA pairs, 3: one CTA per tile, 1: CUDA cores")
     ap.add_argument("--size", type=int, default=0, help="override M = K (= N) for quick runs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-check", action="store_true", help="skip the oracle gate before timing")

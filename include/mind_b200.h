@@ -121,9 +121,10 @@ int64_t mind_b200_kernel_launches(void);
 /* Pre-sizes the current device's scratch (operand re-layouts) and staging (host operands)
  * buffers so that later calls allocate nothing. */
 int64_t mind_b200_reserve(int64_t scratch_bytes, int64_t staging_bytes);
-/* Which kernel the int8 / int16 GEMMs use: 0 = tensor cores (tcgen05), one CTA per
- * output tile (default); 2 = tensor cores, one tile per pair of CTAs (cta_group::2);
- * 1 = the independent CUDA-core kernel kept as an on-device cross-check. */
+/* Which kernel the int8 / int16 GEMMs use: 0 = tensor cores (tcgen05), the library picks
+ * between its two kernels per call (default); 2 = tensor cores, one output tile per pair of
+ * CTAs (cta_group::2); 3 = tensor cores, one CTA per tile; 1 = the independent CUDA-core
+ * kernel kept as an on-device cross-check.  All four give identical bytes. */
 int64_t mind_b200_set_gemm_path(int64_t path);
 /* Kernel timing for measurements: while enabled, the dominant kernel of every call (the
  * GEMM / GEMV kernel itself, not the operand re-layout) is bracketed by CUDA events on the

@@ -334,15 +334,13 @@ int64_t mind_b200_reserve(int64_t scratch_bytes, int64_t staging_bytes) {
 int64_t mind_b200_set_gemm_path(int64_t path) {
     clear_error();
     std::lock_guard<std::mutex> lock(g_call_mutex);
-    if (path == 0 || path == 1) {
-        g_gemm_path = (int)path;
-        return set_pair_mode(1);
+    switch (path) {
+        case 0: g_gemm_path = 0; return set_pair_mode(0);  // tensor cores, kernel picked per call
+        case 1: g_gemm_path = 1; return set_pair_mode(0);  // CUDA cores
+        case 2: g_gemm_path = 0; return set_pair_mode(2);  // tensor cores, CTA pairs
+        case 3: g_gemm_path = 0; return set_pair_mode(1);  // tensor cores, one CTA per tile
     }
-    if (path == 2) {  // tensor cores, one tile per CTA pair
-        g_gemm_path = 0;
-        return set_pair_mode(2);
-    }
-    return fail(MIND_B200_ERR_INVALID, "gemm path must be 0 (tensor cores), 1 (CUDA cores) or 2 (tensor cores, CTA pairs)");
+    return fail(MIND_B200_ERR_INVALID, "gemm path must be 0 (auto), 1 (CUDA cores), 2 (CTA pairs) or 3 (single CTA)");
 }
 
 int64_t mind_b200_profile(int64_t enable) {

@@ -24,6 +24,9 @@
 // Out-of-range rows / K tails are zero-filled by TMA; stores are predicated.
 // Every wait is bounded in time: when it runs out the kernel records a code in
 // the device error word, all roles leave their loops, and the kernel exits cleanly.
+#include <stdio.h>
+#include <stdlib.h>
+
 #include "common.h"
 #include "ptx.cuh"
 
@@ -128,7 +131,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full0 + 8 * s, PAIR);  // one arrive.expect_tx per CTA of the pair
+            mbar_init(full0 + 8 * s, 1);     // one arrive.expect_tx (by the leader, for both CTAs' bytes)
             mbar_init(empty0 + 8 * s, 1);    // one tcgen05.commit
         }
         for (int s = 0; s < ACC_STAGES; ++s) {
@@ -187,9 +190,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                         tma_load_2d(db, &tm_b0, bar, kx, row_b);
                         if (cfg::NB == 2) tma_load_2d(db + B_TILE_BYTES, &tm_b1, bar, kx, row_b);
                     } else {
-                        // Both CTAs signal the LEADER's full barrier: it alone issues MMAs.
+                        // Both CTAs' copies complete on the LEADER's full barrier (it alone issues
+                        // MMAs).  Only the leader arrives, expecting the bytes of both; the peer's
+                        // bytes may land first, which a transaction count allows.  No remote
+                        // arrive: its release fence would drain the copies in flight every stage.
                         const uint32_t bar = mapa(full0 + 8 * s, 0);
-                        mbar_arrive_expect_tx_cluster(full0 + 8 * s, STAGE_BYTES, 0);
+                        if (leader) mbar_arrive_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
                         tma_load_2d_pair(dst, &tm_a0, bar, kx, row_a);
                         if (cfg::NA == 2) tma_load_2d_pair(dst + A_TILE_BYTES, &tm_a1, bar, kx, row_a);
                         const uint32_t db = dst + cfg::NA * A_TILE_BYTES;
@@ -343,7 +349,7 @@ int64_t make_tmap(CUtensorMap* tm, const void* base, int64_t k, int64_t rows, in
     return 0;
 }
 
-int g_pair_mode = 1;  // CTAs per tile: 1, or 2 for the cta_group::2 kernels
+int g_pair_mode = 0;  // CTAs per tile: 1, 2 (cta_group::2 kernels), or 0 = pick per call
 
 template <int MODE, int PAIR>
 int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0, const void* b1,
@@ -398,7 +404,11 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
         // Not every SM need be pairable; a pair that is not resident would only start
         // after another one ends, so size the persistent grid to what fits at once.
         int fit = 0;
-        if (cudaOccupancyMaxActiveClusters(&fit, kern, &lc) == cudaSuccess && fit > 0 && fit < units) {
+        cudaError_t oe = cudaOccupancyMaxActiveClusters(&fit, kern, &lc);
+        if (getenv("MIND_B200_DEBUG"))
+            fprintf(stderr, "[mind_b200] pair launch: units=%d fit=%d (%s)\n", units, fit,
+                    cudaGetErrorString(oe));
+        if (oe == cudaSuccess && fit > 0 && fit < units) {
             units = fit;
             lc.gridDim = dim3((unsigned)(units * PAIR), 1, 1);
         } else {
@@ -415,21 +425,25 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
 }  // namespace
 
 int64_t set_pair_mode(int pair) {
-    if (pair != 1 && pair != 2) return fail(MIND_B200_ERR_INVALID, "CTAs per tile must be 1 or 2");
+    if (pair < 0 || pair > 2) return fail(MIND_B200_ERR_INVALID, "CTAs per tile must be 0 (auto), 1 or 2");
     g_pair_mode = pair;
     return 0;
 }
 
 int64_t launch_gemm_i8_tc(DeviceCtx* ctx, const int8_t* a, const int8_t* bt, int32_t* c, int64_t m,
                           int64_t n, int64_t k, int64_t kp_a, int64_t kp_b) {
-    if (g_pair_mode == 2)
-        return launch_tc<0, 2>(ctx, a, nullptr, bt, nullptr, c, m, n, k, kp_a, kp_b);
+    // Measured on B200: the CTA-pair kernel is the faster int8 kernel whenever an output
+    // tile of 256 rows is not mostly padding.
+    const bool pair = g_pair_mode == 2 || (g_pair_mode == 0 && m > 128);
+    if (pair) return launch_tc<0, 2>(ctx, a, nullptr, bt, nullptr, c, m, n, k, kp_a, kp_b);
     return launch_tc<0, 1>(ctx, a, nullptr, bt, nullptr, c, m, n, k, kp_a, kp_b);
 }
 
 int64_t launch_gemm_i16_tc(DeviceCtx* ctx, const int8_t* a_hi, const uint8_t* a_lo,
                            const int8_t* bt_hi, const uint8_t* bt_lo, int32_t* c, int64_t m,
                            int64_t n, int64_t k, int64_t kp) {
+    // Measured on B200: with three accumulators per tile the single-CTA kernel is as fast
+    // or faster than the pair kernel at every size tried, so auto keeps one CTA per tile.
     if (g_pair_mode == 2) return launch_tc<1, 2>(ctx, a_hi, a_lo, bt_hi, bt_lo, c, m, n, k, kp, kp);
     return launch_tc<1, 1>(ctx, a_hi, a_lo, bt_hi, bt_lo, c, m, n, k, kp, kp);
 }

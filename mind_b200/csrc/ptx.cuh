@@ -46,12 +46,14 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
-// Arrive on the barrier at the same offset in CTA `cta` of this cluster.
+// Arrive on the barrier at the same offset in CTA `cta` of this cluster.  Relaxed: the
+// arrival orders nothing but itself (callers fence tcgen05 traffic explicitly), so it
+// does not wait for this thread's global stores to drain.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta) {
     asm volatile(
         "{\n\t.reg .b32 r;\n\t"
         "mapa.shared::cluster.u32 r, %0, %1;\n\t"
-        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [r];\n\t}" ::"r"(bar),
+        "mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [r];\n\t}" ::"r"(bar),
         "r"(cta)
         : "memory");
 }
