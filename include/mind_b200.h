@@ -87,6 +87,31 @@ int64_t __mind_blas_dot_i16_v(int64_t a, int64_t b, int64_t len);
  * un-transposed K x N B, the layout of its int8 and Q16.16 GEMMs.  New symbol name. */
 int64_t __mind_b200_matmul_mm_i16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n);
 
+/* ---- int8 GEMM that allocates nothing -----------------------------------------------------------
+ * This entry point has no counterpart in the reference.  It is for hosts that cannot call
+ * cudaMalloc when they need the product: a serving loop or stream callback where an allocation
+ * (and the device synchronisation it may bring) is not allowed, or a process whose GPU memory is
+ * wholly owned by another allocator.  Same rule, same kernels and same bytes as
+ * __mind_blas_matmul_mm_i8_v, but the transposed B (and the padded A, when K % 16 != 0 or A is
+ * not 16-byte aligned) live in a fixed array inside the library image instead of a buffer grown
+ * with cudaMalloc, and no per-device context is created.  It calls no cudaMalloc, cudaFree,
+ * cudaMallocHost or other allocating routine.
+ *   - a, b, c must be DEVICE pointers of the current device (host operands would need staging
+ *     memory); cuda_stream is the stream to run on (0 = legacy default stream).
+ *   - limit: N*ceil16(K) + (M*ceil16(K) if A needs padding), each rounded up to 256 bytes, must
+ *     not exceed MIND_B200_STATIC_SCRATCH_BYTES, else MIND_B200_ERR_TOO_LARGE.  Every GPU that
+ *     loads the library holds that array until the process exits.
+ *   - the call waits for its own work and then returns (it reports a kernel time-out itself).
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress);
+ *     make that first call before starting any stream capture on that device.
+ *   - all calls share the one array, which keeps the previous call's contents (each call
+ *     rewrites what it reads and zeroes its error word first).  Two calls overlapping on the
+ *     GPU would race on it; inside one process a lock and the final wait rule that out, and
+ *     every process has its own copy of the array. */
+#define MIND_B200_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
+int64_t mind_b200_matmul_mm_i8_static(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n,
+                                      int64_t cuda_stream);
+
 /* ---- names of the reference's identity-gate library -----------------------------------------
  * The gate compiles a MIND source whose public functions wrap the intrinsics
  * (tests/cross_substrate_identity.rs:69-144) and its drivers dlsym these names

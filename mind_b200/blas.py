@@ -89,6 +89,22 @@ def dot_i16_v(a, b, n):
     return _dot("__mind_blas_dot_i16_v", a, b, n)
 
 
+STATIC_SCRATCH_BYTES = 8 * 1024 * 1024
+
+
+def matmul_mm_i8_static(a, b, c, m, k, n, stream: int = 0):
+    """int8 GEMM for callers that may not allocate GPU memory (device operands only).
+
+    Same bytes as ``matmul_mm_i8_v``; the re-laid-out operands live in a fixed 8 MiB array
+    inside the library instead of a cudaMalloc'ed buffer, so larger shapes are refused with
+    ``ERR_TOO_LARGE``.  Synchronous.  See ``mind_b200_matmul_mm_i8_static`` in the header.
+    """
+    import ctypes as C
+    f = lib().mind_b200_matmul_mm_i8_static
+    f.argtypes, f.restype = [C.c_int64] * 7, C.c_int64
+    return check(f(addr(a), addr(b), addr(c), m, k, n, int(stream)))
+
+
 def gemmq_bt(a, bt, c, m, k, n):
     """The identity gate's ``gemmq``: B is passed transposed (N x K)."""
     return _call6("gemmq", a, bt, c, m, k, n)
