@@ -148,8 +148,10 @@ int64_t mind_b200_kernel_launches(void);
 int64_t mind_b200_reserve(int64_t scratch_bytes, int64_t staging_bytes);
 /* Which kernel the int8 / int16 GEMMs use: 0 = tensor cores (tcgen05), the library picks
  * between its two kernels per call (default); 2 = tensor cores, one output tile per pair of
- * CTAs (cta_group::2); 3 = tensor cores, one CTA per tile; 1 = the independent CUDA-core
- * kernel kept as an on-device cross-check.  All four give identical bytes. */
+ * CTAs (cta_group::2); 3 = tensor cores, one CTA per tile; 4 / 5 = as 2 / 3 but B is always
+ * transposed into scratch first (otherwise B is read in place whenever its pitch and base are
+ * 16-byte aligned); 1 = the independent CUDA-core kernel kept as an on-device cross-check.
+ * Every path gives identical bytes. */
 int64_t mind_b200_set_gemm_path(int64_t path);
 /* Kernel timing for measurements: while enabled, the dominant kernel of every call (the
  * GEMM / GEMV kernel itself, not the operand re-layout) is bracketed by CUDA events on the

@@ -10,6 +10,7 @@ namespace {
 
 std::mutex g_call_mutex;  // calls are serialised, like the reference's MT dispatch lock
 int g_gemm_path = 0;      // 0 = tensor cores, 1 = CUDA-core cross-check kernels
+bool g_force_transpose = false;  // tensor cores: always re-lay B out K-contiguous (testing)
 
 // One operand of a call: where the caller keeps it and where the kernels see it.
 struct Operand {
@@ -135,16 +136,23 @@ int64_t gemm_i8(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n
         const int64_t kp = (int64_t)align_up((size_t)k, 16);
         const int8_t* da = call.dev<int8_t>(ia);
         const bool a_direct = kp == k && reinterpret_cast<uintptr_t>(da) % 16 == 0;
-        const size_t bt_bytes = (size_t)n * kp, ap_bytes = a_direct ? 0 : (size_t)m * kp;
+        // B is read in place (N-contiguous tiles) when TMA can address it: 16-byte pitch and
+        // base.  Otherwise it is transposed into K-contiguous scratch first.
+        const int8_t* db = call.dev<int8_t>(ib);
+        const bool b_direct = !g_force_transpose && n % 16 == 0 && reinterpret_cast<uintptr_t>(db) % 16 == 0;
+        const size_t bt_bytes = b_direct ? 0 : (size_t)n * kp, ap_bytes = a_direct ? 0 : (size_t)m * kp;
         MB200_TRY(arena_reserve(ctx, ctx->scratch, align_up(bt_bytes, 1024) + align_up(ap_bytes, 1024) + 2048));
-        int8_t* bt = static_cast<int8_t*>(arena_take(ctx->scratch, bt_bytes));
-        MB200_TRY(launch_transpose_i8(ctx, call.dev<int8_t>(ib), bt, k, n, kp));
+        int8_t* bt = b_direct ? nullptr : static_cast<int8_t*>(arena_take(ctx->scratch, bt_bytes));
+        if (!b_direct) MB200_TRY(launch_transpose_i8(ctx, db, bt, k, n, kp));
         if (!a_direct) {
             int8_t* ap = static_cast<int8_t*>(arena_take(ctx->scratch, ap_bytes));
             MB200_TRY(launch_pad_rows_i8(ctx, da, ap, m, k, kp));
             da = ap;
         }
-        MB200_TRY(launch_gemm_i8_tc(ctx, da, bt, call.dev<int32_t>(ic), m, n, k, kp, kp));
+        if (b_direct)
+            MB200_TRY(launch_gemm_i8_tc_bmn(ctx, da, db, call.dev<int32_t>(ic), m, n, k, kp, n));
+        else
+            MB200_TRY(launch_gemm_i8_tc(ctx, da, bt, call.dev<int32_t>(ic), m, n, k, kp, kp));
     }
     return call.end(true);
 }
@@ -169,15 +177,25 @@ int64_t gemm_i16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t 
         MB200_TRY(launch_gemm_i16_simt(ctx, call.dev<int16_t>(ia), call.dev<int16_t>(ib), call.dev<int32_t>(ic), m, k, n));
     } else {
         const int64_t kp = (int64_t)align_up((size_t)k, 16);
-        const size_t a_plane = align_up((size_t)m * kp, 1024), b_plane = align_up((size_t)n * kp, 1024);
+        const int64_t np = (int64_t)align_up((size_t)n, 16);
+        // B's limb planes keep B's own orientation ([K][np], N contiguous) unless the CTA-pair
+        // kernel is forced, whose B tiles must be K-contiguous.
+        const bool b_transposed = g_force_transpose || tc_pair_forced();
+        const size_t a_plane = align_up((size_t)m * kp, 1024);
+        const size_t b_plane = align_up(b_transposed ? (size_t)n * kp : (size_t)k * np, 1024);
         MB200_TRY(arena_reserve(ctx, ctx->scratch, 2 * a_plane + 2 * b_plane + 4096));
         int8_t* a_hi = static_cast<int8_t*>(arena_take(ctx->scratch, a_plane));
         uint8_t* a_lo = static_cast<uint8_t*>(arena_take(ctx->scratch, a_plane));
         int8_t* b_hi = static_cast<int8_t*>(arena_take(ctx->scratch, b_plane));
         uint8_t* b_lo = static_cast<uint8_t*>(arena_take(ctx->scratch, b_plane));
         MB200_TRY(launch_split_rows_i16(ctx, call.dev<int16_t>(ia), a_hi, a_lo, m, k, kp));
-        MB200_TRY(launch_split_transpose_i16(ctx, call.dev<int16_t>(ib), b_hi, b_lo, k, n, kp));
-        MB200_TRY(launch_gemm_i16_tc(ctx, a_hi, a_lo, b_hi, b_lo, call.dev<int32_t>(ic), m, n, k, kp));
+        if (b_transposed) {
+            MB200_TRY(launch_split_transpose_i16(ctx, call.dev<int16_t>(ib), b_hi, b_lo, k, n, kp));
+            MB200_TRY(launch_gemm_i16_tc(ctx, a_hi, a_lo, b_hi, b_lo, call.dev<int32_t>(ic), m, n, k, kp));
+        } else {
+            MB200_TRY(launch_split_rows_i16(ctx, call.dev<int16_t>(ib), b_hi, b_lo, k, n, np));
+            MB200_TRY(launch_gemm_i16_tc_bmn(ctx, a_hi, a_lo, b_hi, b_lo, call.dev<int32_t>(ic), m, n, k, kp, np));
+        }
     }
     return call.end(true);
 }
@@ -334,13 +352,14 @@ int64_t mind_b200_reserve(int64_t scratch_bytes, int64_t staging_bytes) {
 int64_t mind_b200_set_gemm_path(int64_t path) {
     clear_error();
     std::lock_guard<std::mutex> lock(g_call_mutex);
+    g_force_transpose = path == 4 || path == 5;
     switch (path) {
         case 0: g_gemm_path = 0; return set_pair_mode(0);  // tensor cores, kernel picked per call
         case 1: g_gemm_path = 1; return set_pair_mode(0);  // CUDA cores
-        case 2: g_gemm_path = 0; return set_pair_mode(2);  // tensor cores, CTA pairs
-        case 3: g_gemm_path = 0; return set_pair_mode(1);  // tensor cores, one CTA per tile
+        case 2: case 4: g_gemm_path = 0; return set_pair_mode(2);  // tensor cores, CTA pairs
+        case 3: case 5: g_gemm_path = 0; return set_pair_mode(1);  // tensor cores, one CTA per tile
     }
-    return fail(MIND_B200_ERR_INVALID, "gemm path must be 0 (auto), 1 (CUDA cores), 2 (CTA pairs) or 3 (single CTA)");
+    return fail(MIND_B200_ERR_INVALID, "gemm path must be 0 (auto), 1 (CUDA cores), 2 / 3 (CTA pairs / single CTA) or 4 / 5 (the same with B transposed first)");
 }
 
 int64_t mind_b200_profile(int64_t enable) {

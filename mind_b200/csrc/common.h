@@ -95,6 +95,14 @@ int64_t launch_gemm_i8_tc(DeviceCtx* ctx, const int8_t* a, const int8_t* bt, int
 int64_t launch_gemm_i16_tc(DeviceCtx* ctx, const int8_t* a_hi, const uint8_t* a_lo,
                            const int8_t* bt_hi, const uint8_t* bt_lo, int32_t* c, int64_t m,
                            int64_t n, int64_t k, int64_t kp);
+// Same products with B used as the caller has it (B[K][N], row pitch `pitch_b` bytes,
+// pitch_b % 16 == 0, base 16-byte aligned): no transpose pass.
+int64_t launch_gemm_i8_tc_bmn(DeviceCtx* ctx, const int8_t* a, const int8_t* b, int32_t* c, int64_t m,
+                              int64_t n, int64_t k, int64_t kp_a, int64_t pitch_b);
+int64_t launch_gemm_i16_tc_bmn(DeviceCtx* ctx, const int8_t* a_hi, const uint8_t* a_lo,
+                               const int8_t* b_hi, const uint8_t* b_lo, int32_t* c, int64_t m,
+                               int64_t n, int64_t k, int64_t kp_a, int64_t pitch_b);
+bool tc_pair_forced();
 // Re-layout kernels.
 int64_t launch_transpose_i8(DeviceCtx* ctx, const int8_t* b, int8_t* bt, int64_t k, int64_t n,
                             int64_t kp);

@@ -98,15 +98,20 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
     tn = r / gsize;
 }
 
-template <int MODE, int PAIR>
+// BMN = false: B is given transposed (Bt[N][K], K contiguous).  BMN = true: B is used as the
+// caller has it (B[K][N], N contiguous = "MN-major"); its tiles are TMA boxes of 128 bytes of N
+// by 128 rows of K, and the MMA reads them through an MN-major descriptor - no transpose pass.
+template <int MODE, int PAIR, bool BMN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
                const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
                const TcParams p) {
     using cfg = Cfg<MODE, PAIR>;
     constexpr int BLOCK_N = cfg::BLOCK_N;
-    constexpr int B_ROWS = BLOCK_N / PAIR;  // rows of Bt this CTA stages
+    constexpr int B_ROWS = BLOCK_N / PAIR;  // columns of the output (rows of Bt) this CTA stages
     constexpr int B_TILE_BYTES = B_ROWS * BLOCK_K;
+    static_assert(!BMN || B_ROWS % 128 == 0, "an MN-major B tile is made of 128-column boxes");
+    constexpr int B_BOX_BYTES = 128 * BLOCK_K;  // one MN-major box: 128 columns x 128 rows of K
     constexpr int STAGE_BYTES = cfg::NA * A_TILE_BYTES + cfg::NB * B_TILE_BYTES;
     constexpr int STAGES = cfg::STAGES;
     constexpr int ACC_STAGES = cfg::ACC_STAGES;
@@ -187,8 +192,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                         tma_load_2d(dst, &tm_a0, bar, kx, row_a);
                         if (cfg::NA == 2) tma_load_2d(dst + A_TILE_BYTES, &tm_a1, bar, kx, row_a);
                         const uint32_t db = dst + cfg::NA * A_TILE_BYTES;
-                        tma_load_2d(db, &tm_b0, bar, kx, row_b);
-                        if (cfg::NB == 2) tma_load_2d(db + B_TILE_BYTES, &tm_b1, bar, kx, row_b);
+                        if (!BMN) {
+                            tma_load_2d(db, &tm_b0, bar, kx, row_b);
+                            if (cfg::NB == 2) tma_load_2d(db + B_TILE_BYTES, &tm_b1, bar, kx, row_b);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < B_ROWS / 128; ++j) {
+                                tma_load_2d(db + j * B_BOX_BYTES, &tm_b0, bar, row_b + 128 * j, kx);
+                                if (cfg::NB == 2)
+                                    tma_load_2d(db + B_TILE_BYTES + j * B_BOX_BYTES, &tm_b1, bar, row_b + 128 * j, kx);
+                            }
+                        }
+                    } else if (BMN) {
+                        const uint32_t bar = mapa(full0 + 8 * s, 0);
+                        if (leader) mbar_arrive_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
+                        tma_load_2d_pair(dst, &tm_a0, bar, kx, row_a);
+                        if (cfg::NA == 2) tma_load_2d_pair(dst + A_TILE_BYTES, &tm_a1, bar, kx, row_a);
+                        const uint32_t db = dst + cfg::NA * A_TILE_BYTES;
+#pragma unroll
+                        for (int j = 0; j < B_ROWS / 128; ++j) {
+                            tma_load_2d_pair(db + j * B_BOX_BYTES, &tm_b0, bar, row_b + 128 * j, kx);
+                            if (cfg::NB == 2)
+                                tma_load_2d_pair(db + B_TILE_BYTES + j * B_BOX_BYTES, &tm_b1, bar, row_b + 128 * j, kx);
+                        }
                     } else {
                         // Both CTAs' copies complete on the LEADER's full barrier (it alone issues
                         // MMAs).  Only the leader arrives, expecting the bytes of both; the peer's
@@ -208,10 +234,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
     } else if (warp == 1) {
         // -------------------------------------------------------------- MMA issuer
         if (lane == 0 && leader) {
-            constexpr uint32_t ID_SS = idesc_i8(UMMA_M, BLOCK_N, true, true);
-            constexpr uint32_t ID_SU = idesc_i8(UMMA_M, BLOCK_N, true, false);
-            constexpr uint32_t ID_US = idesc_i8(UMMA_M, BLOCK_N, false, true);
-            constexpr uint32_t ID_UU = idesc_i8(UMMA_M, BLOCK_N, false, false);
+            constexpr uint32_t ID_SS = idesc_i8(UMMA_M, BLOCK_N, true, true, BMN);
+            constexpr uint32_t ID_SU = idesc_i8(UMMA_M, BLOCK_N, true, false, BMN);
+            constexpr uint32_t ID_US = idesc_i8(UMMA_M, BLOCK_N, false, true, BMN);
+            constexpr uint32_t ID_UU = idesc_i8(UMMA_M, BLOCK_N, false, false, BMN);
+            // Descriptor step per MMA (32 of K): 32 bytes along a K-major row, or 32 K-rows of
+            // 128 bytes in an MN-major tile; in units of 16 bytes.
+            constexpr uint64_t B_KSTEP = BMN ? (UMMA_K * 128) >> 4 : UMMA_K >> 4;
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step, ++tcount) {
@@ -227,21 +256,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                     }
                     tc_fence_after();
                     const uint32_t sa = tiles0 + s * STAGE_BYTES;
+                    const uint32_t sb = sa + cfg::NA * A_TILE_BYTES;
                     const uint64_t da0 = smem_desc_k_sw128(sa);
-                    const uint64_t db0 = smem_desc_k_sw128(sa + cfg::NA * A_TILE_BYTES);
+                    const uint64_t db0 = BMN ? smem_desc_mn_sw128(sb, B_BOX_BYTES) : smem_desc_k_sw128(sb);
 #pragma unroll
                     for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks) {
                         const uint32_t acc = (kb | ks) != 0 ? 1u : 0u;
                         const uint64_t koff = (uint64_t)((ks * UMMA_K) >> 4);
+                        const uint64_t kb_off = (uint64_t)ks * B_KSTEP;
                         if (MODE == 0) {
-                            mma_i8<PAIR>(d0, da0 + koff, db0 + koff, ID_SS, acc);
+                            mma_i8<PAIR>(d0, da0 + koff, db0 + kb_off, ID_SS, acc);
                         } else {
                             const uint64_t da1 = smem_desc_k_sw128(sa + A_TILE_BYTES) + koff;
-                            const uint64_t db1 =
-                                smem_desc_k_sw128(sa + cfg::NA * A_TILE_BYTES + B_TILE_BYTES) + koff;
-                            mma_i8<PAIR>(d0, da0 + koff, db0 + koff, ID_SS, acc);            // hi.hi
+                            const uint64_t db1 = (BMN ? smem_desc_mn_sw128(sb + B_TILE_BYTES, B_BOX_BYTES)
+                                                      : smem_desc_k_sw128(sb + B_TILE_BYTES)) + kb_off;
+                            mma_i8<PAIR>(d0, da0 + koff, db0 + kb_off, ID_SS, acc);          // hi.hi
                             mma_i8<PAIR>(d0 + BLOCK_N, da0 + koff, db1, ID_SU, acc);         // hi.lo
-                            mma_i8<PAIR>(d0 + BLOCK_N, da1, db0 + koff, ID_US, 1u);          // lo.hi
+                            mma_i8<PAIR>(d0 + BLOCK_N, da1, db0 + kb_off, ID_US, 1u);        // lo.hi
                             mma_i8<PAIR>(d0 + 2 * BLOCK_N, da1, db1, ID_UU, acc);            // lo.lo
                         }
                     }
@@ -351,7 +382,9 @@ int64_t make_tmap(CUtensorMap* tm, const void* base, int64_t k, int64_t rows, in
 
 int g_pair_mode = 0;  // CTAs per tile: 1, 2 (cta_group::2 kernels), or 0 = pick per call
 
-template <int MODE, int PAIR>
+// kp_b: row pitch of the B operand(s) in bytes: of Bt[N][K] rows (BMN = false) or of
+// B[K][N] rows (BMN = true).
+template <int MODE, int PAIR, bool BMN>
 int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0, const void* b1,
                   int32_t* c, int64_t m, int64_t n, int64_t k, int64_t kp_a, int64_t kp_b) {
     using cfg = Cfg<MODE, PAIR>;
@@ -363,11 +396,19 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
         return fail(MIND_B200_ERR_TOO_LARGE, "GEMM dimension above 2^31-1");
     CUtensorMap ta0, ta1, tb0, tb1;
     MB200_TRY(make_tmap(&ta0, a0, k, m, kp_a, BLOCK_M));
-    MB200_TRY(make_tmap(&tb0, b0, k, n, kp_b, B_ROWS));
+    if (BMN)
+        MB200_TRY(make_tmap(&tb0, b0, n, k, kp_b, BLOCK_K));  // boxes of 128 columns x 128 rows of K
+    else
+        MB200_TRY(make_tmap(&tb0, b0, k, n, kp_b, B_ROWS));
     ta1 = ta0;
     tb1 = tb0;
     if (cfg::NA == 2) MB200_TRY(make_tmap(&ta1, a1, k, m, kp_a, BLOCK_M));
-    if (cfg::NB == 2) MB200_TRY(make_tmap(&tb1, b1, k, n, kp_b, B_ROWS));
+    if (cfg::NB == 2) {
+        if (BMN)
+            MB200_TRY(make_tmap(&tb1, b1, n, k, kp_b, BLOCK_K));
+        else
+            MB200_TRY(make_tmap(&tb1, b1, k, n, kp_b, B_ROWS));
+    }
     TcParams p;
     p.c = c;
     p.m = (int)m;
@@ -379,9 +420,8 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     p.err = ctx->err_word;
     const long long total = (long long)p.m_tiles * p.n_tiles;
     if (total > 0x7fffffff) return fail(MIND_B200_ERR_TOO_LARGE, "too many output tiles");
-    auto kern = gemm_tc_kernel<MODE, PAIR>;
-    static thread_local int attr_dev[4] = {-1, -1, -1, -1};
-    int& done_for = attr_dev[MODE * 2 + (PAIR - 1)];
+    auto kern = gemm_tc_kernel<MODE, PAIR, BMN>;
+    static thread_local int done_for = -1;  // one per template instance
     if (done_for != ctx->device) {
         MB200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
         done_for = ctx->device;
@@ -435,8 +475,24 @@ int64_t launch_gemm_i8_tc(DeviceCtx* ctx, const int8_t* a, const int8_t* bt, int
     // Measured on B200: the CTA-pair kernel is the faster int8 kernel whenever an output
     // tile of 256 rows is not mostly padding.
     const bool pair = g_pair_mode == 2 || (g_pair_mode == 0 && m > 128);
-    if (pair) return launch_tc<0, 2>(ctx, a, nullptr, bt, nullptr, c, m, n, k, kp_a, kp_b);
-    return launch_tc<0, 1>(ctx, a, nullptr, bt, nullptr, c, m, n, k, kp_a, kp_b);
+    if (pair) return launch_tc<0, 2, false>(ctx, a, nullptr, bt, nullptr, c, m, n, k, kp_a, kp_b);
+    return launch_tc<0, 1, false>(ctx, a, nullptr, bt, nullptr, c, m, n, k, kp_a, kp_b);
+}
+
+int64_t launch_gemm_i8_tc_bmn(DeviceCtx* ctx, const int8_t* a, const int8_t* b, int32_t* c, int64_t m,
+                              int64_t n, int64_t k, int64_t kp_a, int64_t pitch_b) {
+    const bool pair = g_pair_mode == 2 || (g_pair_mode == 0 && m > 128);
+    if (pair) return launch_tc<0, 2, true>(ctx, a, nullptr, b, nullptr, c, m, n, k, kp_a, pitch_b);
+    return launch_tc<0, 1, true>(ctx, a, nullptr, b, nullptr, c, m, n, k, kp_a, pitch_b);
+}
+
+bool tc_pair_forced() { return g_pair_mode == 2; }
+
+// One CTA per tile only: a pair would give each CTA 64 columns of B, half a swizzle atom.
+int64_t launch_gemm_i16_tc_bmn(DeviceCtx* ctx, const int8_t* a_hi, const uint8_t* a_lo,
+                               const int8_t* b_hi, const uint8_t* b_lo, int32_t* c, int64_t m,
+                               int64_t n, int64_t k, int64_t kp_a, int64_t pitch_b) {
+    return launch_tc<1, 1, true>(ctx, a_hi, a_lo, b_hi, b_lo, c, m, n, k, kp_a, pitch_b);
 }
 
 int64_t launch_gemm_i16_tc(DeviceCtx* ctx, const int8_t* a_hi, const uint8_t* a_lo,
@@ -444,8 +500,8 @@ int64_t launch_gemm_i16_tc(DeviceCtx* ctx, const int8_t* a_hi, const uint8_t* a_
                            int64_t n, int64_t k, int64_t kp) {
     // Measured on B200: with three accumulators per tile the single-CTA kernel is as fast
     // or faster than the pair kernel at every size tried, so auto keeps one CTA per tile.
-    if (g_pair_mode == 2) return launch_tc<1, 2>(ctx, a_hi, a_lo, bt_hi, bt_lo, c, m, n, k, kp, kp);
-    return launch_tc<1, 1>(ctx, a_hi, a_lo, bt_hi, bt_lo, c, m, n, k, kp, kp);
+    if (g_pair_mode == 2) return launch_tc<1, 2, false>(ctx, a_hi, a_lo, bt_hi, bt_lo, c, m, n, k, kp, kp);
+    return launch_tc<1, 1, false>(ctx, a_hi, a_lo, bt_hi, bt_lo, c, m, n, k, kp, kp);
 }
 
 }  // namespace mb200

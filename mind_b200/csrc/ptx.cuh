@@ -231,12 +231,28 @@ __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t smem_addr) {
     return d;
 }
 
-// Instruction descriptor of tcgen05.mma kind::i8: s32 accumulator, both
-// operands K-major, no saturation.  a_signed / b_signed pick s8 or u8.
-__host__ __device__ constexpr uint32_t idesc_i8(int m, int n, bool a_signed, bool b_signed) {
+// Shared-memory matrix descriptor for an MN-major operand tile (N contiguous): rows of
+// K, each 128 bytes of N, stored with the 128-byte swizzle (a TMA box of {128 bytes of N,
+// rows of K}).  Groups of 8 K-rows are 1024 bytes apart; the next 128 columns of N start
+// `n_atom_stride` bytes further on.
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t smem_addr, uint32_t n_atom_stride) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((n_atom_stride >> 4) & 0x3FFFu) << 16;  // leading offset: next N atom
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;                       // stride offset: next 8 K-rows
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+// Instruction descriptor of tcgen05.mma kind::i8: s32 accumulator, A K-major, B K-major
+// or (b_mn) MN-major, no saturation.  a_signed / b_signed pick s8 or u8.
+__host__ __device__ constexpr uint32_t idesc_i8(int m, int n, bool a_signed, bool b_signed,
+                                                bool b_mn = false) {
     return (2u << 4)                          // accumulator format: S32
            | ((a_signed ? 1u : 0u) << 7)      // A: 1 = signed 8-bit, 0 = unsigned
            | ((b_signed ? 1u : 0u) << 10)     // B
+           | ((b_mn ? 1u : 0u) << 16)         // B major: 0 = K, 1 = MN
            | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 

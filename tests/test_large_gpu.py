@@ -54,14 +54,14 @@ def test_device_pointers_all_kernels(gpu):
     g = O.Lcg(5)
     m, k, n = 200, 320, 136
     a, b = g.i8(m * k), g.i8(k * n)
-    for path in (3, 2, 1, 0):
+    for path in (3, 2, 1, 0, 4, 5):
         gpu.set_gemm_path(path)
         c = torch.full((m * n,), -1, dtype=torch.int32, device="cuda")
         gpu.matmul_mm_i8_v(dev(a), dev(b), c, m, k, n)
         gpu.synchronize()
         assert np.array_equal(c.cpu().numpy(), O.gemm_i8(a, b, m, k, n)), path
     a, b = g.i16(m * k), g.i16(k * n)
-    for path in (3, 2, 1, 0):
+    for path in (3, 2, 1, 0, 4, 5):
         gpu.set_gemm_path(path)
         c = torch.full((m * n,), -1, dtype=torch.int32, device="cuda")
         gpu.matmul_mm_i16(dev(a), dev(b), c, m, k, n)
@@ -86,7 +86,7 @@ def test_config1_int8_256(gpu):
     a = lcg_dev(gpu, 256 * 256, 1, e["seed"])
     b = lcg_dev(gpu, 256 * 256, 1, e["seed"], offset=256 * 256)
     hashes = set()
-    for path in (3, 2, 1, 0):
+    for path in (3, 2, 1, 0, 4, 5):
         gpu.set_gemm_path(path)
         for _ in range(16):  # the reference's same-process repeat gate uses 16 fresh buffers
             c = torch.empty(256 * 256, dtype=torch.int32, device="cuda")
@@ -133,7 +133,7 @@ def test_matvec_wrap_helper(gpu):
     assert np.array_equal(out, want)
 
 
-@pytest.mark.parametrize("path", [3, 2])
+@pytest.mark.parametrize("path", [3, 2, 5])
 def test_config3_i16_4096(gpu, path):
     gpu.set_gemm_path(path)
     n = 4096
@@ -174,7 +174,7 @@ def test_config4_gemv_16384(gpu):
         assert torch.equal(y, y2)
 
 
-@pytest.mark.parametrize("path", [3, 2])
+@pytest.mark.parametrize("path", [3, 2, 4])
 def test_config5_int8_16384(gpu, path):
     gpu.set_gemm_path(path)
     n = 16384

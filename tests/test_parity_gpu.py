@@ -29,7 +29,7 @@ GEMM_SHAPES = [
     (257, 130, 1), (1, 511, 257), (130, 513, 70), (128, 1, 256), (300, 256, 520),
     (5, 0, 9), (384, 1024, 512), (100, 2048, 36),
 ]
-PATHS = [3, 2, 1, 0]  # tensor cores (1 CTA per tile), tensor cores (CTA pairs), CUDA cores, auto
+PATHS = [3, 2, 1, 0, 4, 5]  # single CTA, CTA pairs, CUDA cores, auto, pairs / single with B transposed first
 
 
 @pytest.fixture(autouse=True)
@@ -166,7 +166,7 @@ def test_wrap_fixture_and_overflowing_i8(gpu):
     m, k, n = 128, (1 << 17) + 256, 16
     a = np.full(m * k, -128, dtype=np.int8)
     b = np.full(k * n, -128, dtype=np.int8)
-    for path in (3, 2):
+    for path in (3, 2, 4, 5):
         gpu.set_gemm_path(path)
         c = np.empty(m * n, dtype=np.int32)
         gpu.matmul_mm_i8_v(a, b, c, m, k, n)
