@@ -114,6 +114,145 @@ int64_t check_dims(int64_t m, int64_t k, int64_t n) {
     return 0;
 }
 
+// ---------------------------------------------- host-operand pipeline (int8 GEMM)
+// With A and / or C in host memory a large GEMM is cut into row bands (independent,
+// like the reference's thread bands) so that the upload of band i+1, the product of
+// band i and the download of band i-1 overlap: copies run on two side streams, the
+// kernels on the library's stream, A and C bands are double-buffered in staging.
+struct Pipe {
+    cudaStream_t in = nullptr, out = nullptr;
+    cudaEvent_t start = nullptr, in_done[2] = {}, gemm_done[2] = {}, out_done[2] = {};
+    bool ready = false;
+};
+Pipe g_pipe[64];
+
+int64_t pipe_for(DeviceCtx* ctx, Pipe** out) {
+    Pipe& p = g_pipe[ctx->device];
+    if (!p.ready) {
+        MB200_CUDA(cudaStreamCreateWithFlags(&p.in, cudaStreamNonBlocking));
+        MB200_CUDA(cudaStreamCreateWithFlags(&p.out, cudaStreamNonBlocking));
+        MB200_CUDA(cudaEventCreateWithFlags(&p.start, cudaEventDisableTiming));
+        for (int i = 0; i < 2; ++i) {
+            MB200_CUDA(cudaEventCreateWithFlags(&p.in_done[i], cudaEventDisableTiming));
+            MB200_CUDA(cudaEventCreateWithFlags(&p.gemm_done[i], cudaEventDisableTiming));
+            MB200_CUDA(cudaEventCreateWithFlags(&p.out_done[i], cudaEventDisableTiming));
+        }
+        p.ready = true;
+    }
+    *out = &p;
+    return 0;
+}
+
+// 1 = host, 0 = device of ctx, negative = error.
+int64_t pointer_is_host(DeviceCtx* ctx, const void* p) {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+        cudaGetLastError();
+        return 1;
+    }
+    if (at.type == cudaMemoryTypeDevice) {
+        if (at.device != ctx->device)
+            return fail(MIND_B200_ERR_INVALID, "operand lives on device %d but the current device is %d",
+                        at.device, ctx->device);
+        return 0;
+    }
+    return at.type != cudaMemoryTypeManaged;
+}
+
+constexpr int64_t PIPE_MIN_ROWS = 1024;  // below this one band is as good as several
+
+int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const int8_t* b, bool b_host,
+                          int32_t* c, bool c_host, int64_t m, int64_t k, int64_t n) {
+    Pipe* pp = nullptr;
+    MB200_TRY(pipe_for(ctx, &pp));
+    Pipe& P = *pp;
+    const int64_t kp = (int64_t)align_up((size_t)k, 16);
+    int64_t band = (int64_t)align_up((size_t)((m + 7) / 8), 256);
+    const int64_t bands = (m + band - 1) / band;
+
+    // staging: B, two A bands (pitch kp), two C bands
+    const size_t sb = b_host ? align_up((size_t)k * n, 1024) : 0;
+    const size_t sa = a_host ? align_up((size_t)band * kp, 1024) : 0;
+    const size_t sc = c_host ? align_up((size_t)band * n * 4, 1024) : 0;
+    MB200_TRY(arena_reserve(ctx, ctx->staging, sb + 2 * sa + 2 * sc + 8192));
+    const int8_t* db = b;
+    if (b_host) {
+        int8_t* t = static_cast<int8_t*>(arena_take(ctx->staging, sb));
+        MB200_CUDA(cudaMemcpyAsync(t, b, (size_t)k * n, cudaMemcpyHostToDevice, ctx->stream));
+        db = t;
+    }
+    int8_t* a_slot[2] = {nullptr, nullptr};
+    int32_t* c_slot[2] = {nullptr, nullptr};
+    for (int s = 0; s < 2; ++s) {
+        if (a_host) a_slot[s] = static_cast<int8_t*>(arena_take(ctx->staging, sa));
+        if (c_host) c_slot[s] = static_cast<int32_t*>(arena_take(ctx->staging, sc));
+    }
+
+    // scratch: transposed B and / or padded device A, laid out once for all bands
+    const bool b_direct = !g_force_transpose && n % 16 == 0 && reinterpret_cast<uintptr_t>(db) % 16 == 0;
+    const bool a_dev_direct = a_host || (kp == k && reinterpret_cast<uintptr_t>(a) % 16 == 0);
+    const size_t bt_bytes = b_direct ? 0 : (size_t)n * kp, ap_bytes = a_dev_direct ? 0 : (size_t)m * kp;
+    MB200_TRY(arena_reserve(ctx, ctx->scratch, align_up(bt_bytes, 1024) + align_up(ap_bytes, 1024) + 2048));
+    int8_t* bt = nullptr;
+    if (!b_direct) {
+        bt = static_cast<int8_t*>(arena_take(ctx->scratch, bt_bytes));
+        MB200_TRY(launch_transpose_i8(ctx, db, bt, k, n, kp));
+    }
+    const int8_t* a_dev = a;
+    int64_t a_pitch = k;
+    if (!a_host && !a_dev_direct) {
+        int8_t* ap = static_cast<int8_t*>(arena_take(ctx->scratch, ap_bytes));
+        MB200_TRY(launch_pad_rows_i8(ctx, a, ap, m, k, kp));
+        a_dev = ap;
+        a_pitch = kp;
+    }
+
+    // side streams start after everything already queued on the library's stream
+    MB200_CUDA(cudaEventRecord(P.start, ctx->stream));
+    MB200_CUDA(cudaStreamWaitEvent(P.in, P.start, 0));
+    MB200_CUDA(cudaStreamWaitEvent(P.out, P.start, 0));
+    for (int64_t i = 0; i < bands; ++i) {
+        const int s = (int)(i & 1);
+        const int64_t r0 = i * band, rows = (m - r0 < band) ? m - r0 : band;
+        const int8_t* a_band;
+        int64_t pitch;
+        if (a_host) {
+            if (i >= 2) MB200_CUDA(cudaStreamWaitEvent(P.in, P.gemm_done[s], 0));  // slot free again
+            const int8_t* src = a + (size_t)r0 * k;
+            if (kp == k)
+                MB200_CUDA(cudaMemcpyAsync(a_slot[s], src, (size_t)rows * k, cudaMemcpyHostToDevice, P.in));
+            else  // pad to a 16-byte pitch on the way: the pad bytes are never read
+                MB200_CUDA(cudaMemcpy2DAsync(a_slot[s], (size_t)kp, src, (size_t)k, (size_t)k, (size_t)rows,
+                                             cudaMemcpyHostToDevice, P.in));
+            MB200_CUDA(cudaEventRecord(P.in_done[s], P.in));
+            MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.in_done[s], 0));
+            a_band = a_slot[s];
+            pitch = kp;
+        } else {
+            a_band = a_dev + (size_t)r0 * a_pitch;
+            pitch = a_pitch;
+        }
+        int32_t* c_band = c_host ? c_slot[s] : c + (size_t)r0 * n;
+        if (c_host && i >= 2) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.out_done[s], 0));
+        if (b_direct)
+            MB200_TRY(launch_gemm_i8_tc_bmn(ctx, a_band, db, c_band, rows, n, k, pitch, n));
+        else
+            MB200_TRY(launch_gemm_i8_tc(ctx, a_band, bt, c_band, rows, n, k, pitch, kp));
+        MB200_CUDA(cudaEventRecord(P.gemm_done[s], ctx->stream));
+        if (c_host) {
+            MB200_CUDA(cudaStreamWaitEvent(P.out, P.gemm_done[s], 0));
+            MB200_CUDA(cudaMemcpyAsync(c + (size_t)r0 * n, c_slot[s], (size_t)rows * n * 4,
+                                       cudaMemcpyDeviceToHost, P.out));
+            MB200_CUDA(cudaEventRecord(P.out_done[s], P.out));
+        }
+    }
+    if (c_host)
+        for (int s = 0; s < 2 && s < bands; ++s) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.out_done[s], 0));
+    MB200_CUDA(cudaMemcpyAsync(ctx->err_host, ctx->err_word, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    MB200_CUDA(cudaStreamSynchronize(ctx->stream));
+    return Call::check_err_word(ctx);
+}
+
 // ------------------------------------------------------------------ GEMMs
 int64_t gemm_i8(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n) {
     clear_error();
@@ -123,6 +262,14 @@ int64_t gemm_i8(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return MIND_B200_ERR_NO_DEVICE;
     std::lock_guard<std::mutex> lock(g_call_mutex);
+    if (k > 0 && g_gemm_path != 1 && m >= PIPE_MIN_ROWS) {
+        const int64_t ah = pointer_is_host(ctx, (void*)a), bh = pointer_is_host(ctx, (void*)b),
+                      ch = pointer_is_host(ctx, (void*)c);
+        if (ah < 0 || bh < 0 || ch < 0) return MIND_B200_ERR_INVALID;
+        if (ah || ch)
+            return gemm_i8_pipelined(ctx, (const int8_t*)a, ah != 0, (const int8_t*)b, bh != 0, (int32_t*)c,
+                                     ch != 0, m, k, n);
+    }
     Call call(ctx);
     const int ia = call.add((void*)a, (size_t)m * k, false);
     const int ib = call.add((void*)b, (size_t)k * n, false);

@@ -112,6 +112,30 @@ def test_gemm_i8_shapes(gpu, path):
         assert np.all(c[m * n :] == 0x5A5A5A5A), (path, m, k, n)
 
 
+@pytest.mark.parametrize("path", [0, 2, 3, 4])
+def test_gemm_i8_host_operand_pipeline(gpu, path):
+    """M >= 1024 with host A and / or C: row bands are uploaded, multiplied and downloaded
+    in overlap.  Ragged last band, K % 16 != 0 (padded on upload), N % 16 != 0."""
+    import torch
+    gpu.set_gemm_path(path)
+    for (m, k, n) in [(1024, 64, 48), (2500, 100, 36), (1300, 256, 512), (4097, 33, 257), (8192, 512, 128)]:
+        g = O.Lcg(0xDEADBEEF00000000 ^ (m * 7 + k * 3 + n))
+        a, b = g.i8(m * k), g.i8(k * n)
+        want = O.gemm_i8(a, b, m, k, n)
+        c = np.full(m * n + 8, 0x5A5A5A5A, dtype=np.int32)
+        gpu.matmul_mm_i8_v(a, b, c, m, k, n)  # all host
+        assert np.array_equal(c[: m * n], want), (path, m, k, n)
+        assert np.all(c[m * n:] == 0x5A5A5A5A)
+        ad, bd = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+        c2 = np.zeros(m * n, dtype=np.int32)
+        gpu.matmul_mm_i8_v(ad, bd, c2, m, k, n)  # device A and B, host C
+        assert np.array_equal(c2, want), (path, m, k, n)
+        cd = torch.zeros(m * n, dtype=torch.int32, device="cuda")
+        gpu.matmul_mm_i8_v(a, bd, cd, m, k, n)  # host A, device C
+        gpu.synchronize()
+        assert np.array_equal(cd.cpu().numpy(), want), (path, m, k, n)
+
+
 @pytest.mark.parametrize("path", PATHS)
 def test_gemm_i16_shapes(gpu, path):
     gpu.set_gemm_path(path)
