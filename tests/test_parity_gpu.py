@@ -148,8 +148,11 @@ def test_gemm_i16_shapes(gpu, path):
         assert np.all(c[m * n :] == 0x5A5A5A5A)
 
 
-def test_gemm_q16_shapes(gpu):
-    for (m, k, n) in GEMM_SHAPES:
+@pytest.mark.parametrize("path", [0, 1])  # 0: FP64-pipe kernel where shapes allow; 1: all-integer kernel
+def test_gemm_q16_shapes(gpu, path):
+    gpu.set_gemm_path(path)
+    # the last shape crosses the 4096-step fold of the FP64 accumulators twice
+    for (m, k, n) in GEMM_SHAPES + [(256, 64, 128), (1024, 1024, 64), (260, 132, 516), (70, 8200, 68)]:
         for shift in (12, 0):  # the reference's range, and full range (wrap past 2^31)
             g = O.Lcg(0xDEADBEEF00000000 ^ (m * 1000003 + k * 1009 + n + 2))
             a, b = g.q16(m * k, shift), g.q16(k * n, shift)
