@@ -160,7 +160,7 @@ def cpu_sample_rows(w, target_s):
     owner-computes row bands), found from one short calibration call."""
     import oracle as O
     cores = O.online_cpus()
-    rows0 = min(w["m"], max(4, 8 * min(cores, 256)))
+    rows0 = min(w["m"], max(4, 64 * min(cores, 256)))  # enough rows per thread to amortise packing B
     a, b = cpu_inputs(w, rows0)
     cpu_call(w, a, b, rows0)  # warm the thread stacks and caches
     t0 = time.perf_counter()
@@ -214,6 +214,51 @@ def run_reference(args, w):
 
 
 # ------------------------------------------------------------------- GPU arm
+def quick_workload(name, blas, torch, stream, steps=30):
+    """Device-resident timing of one of the other benchmark configurations on this GPU."""
+    w = WORKLOADS[name]
+    m, k, n, kind = w["m"], w["k"], w["n"], w["kind"]
+    tdt = {KIND_Q16: torch.int32, KIND_I8: torch.int8, KIND_I16: torch.int16}[kind]
+    a = torch.empty(m * k, dtype=tdt, device="cuda")
+    b = torch.empty(k * n, dtype=tdt, device="cuda")
+    c = torch.empty(m * n, dtype=torch.int32, device="cuda")
+    blas.lcg_fill(a, m * k, kind, w["seed"], 0, w["shift"])
+    blas.lcg_fill(b, k * n, kind, w["seed"], m * k, w["shift"])
+    fn = getattr(blas, w["fn"])
+    call = (lambda: fn(a, b, c, m, k)) if w["fn"] == "gemv_q16_mt" else (lambda: fn(a, b, c, m, k, n))
+    flush = None
+    if (m * k + k * n) * ELEM_BYTES[kind] <= 2 * L2_BYTES:
+        flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device="cuda")
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    blas.profile(True)
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for e0, e1 in evs:
+        if flush is not None:
+            flush.fill_(1)
+        e0.record(stream)
+        call()
+        e1.record(stream)
+    torch.cuda.synchronize()
+    n_main, main_ms = blas.profile_read()
+    blas.profile(False)
+    ms = sum(e0.elapsed_time(e1) for e0, e1 in evs) / steps
+    scale = unit_scale(w)
+    out = {"workload": f"{name} {m}x{k}x{n}" if n > 1 else f"{name} {m}x{k}", "metric": w["metric"],
+           "value": work_units(w, m) / (ms * 1e-3) / scale, "unit": w["unit"], "ms_per_step": ms, "steps": steps,
+           "kernel_only": work_units(w, m) * n_main / (main_ms * 1e-3) / scale if n_main and main_ms > 0 else None,
+           "l2": "operands larger than L2" if flush is None else "L2 flushed between steps"}
+    peaks, src = measured_peaks()
+    if w["bound"] == "hbm" and out["kernel_only"]:
+        out["frac_of_hbm_peak"] = out["kernel_only"] / peaks["hbm_gbs"]
+        out["peak_source"] = f"{src} STREAM-style copy {peaks['hbm_gbs']} GB/s"
+    if w["fn"] == "matmul_mm_i16" and out["kernel_only"]:
+        out["frac_of_tensor_peak"] = out["kernel_only"] / (2.0 * peaks["bf16_tflops"] / 4.0)
+        out["peak_source"] = f"2 x {src} cuBLAS bf16 burst / 4 limb products"
+    return out
+
+
 def run_mine(args, w):
     import torch
     import torch.distributed as dist
@@ -350,7 +395,7 @@ def run_mine(args, w):
             peak, peak_note = None, "no measured INT32 multiply-add peak on this pool"
         roofline = {"bound": w["bound"], "achieved": achieved, "peak": peak, "unit": w["unit"],
                     "frac": (achieved / peak) if achieved and peak else None, "traffic": None,
-                    "kernel": "gemm_tc_kernel" if w["bound"] == "tensor" else ("rows_warp_kernel" if w["bound"] == "hbm" else "gemm_simt_kernel"),
+                    "kernel": "gemm_tc_kernel" if w["bound"] == "tensor" else ("rows_group_kernel" if w["bound"] == "hbm" else "gemm_q16_fp64_kernel"),
                     "kernel_ms": main_ms / n_main if n_main else None, "peak_source": peak_note}
         line = {"metric": w["metric"], "value": value, "unit": w["unit"], "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps,
@@ -365,6 +410,13 @@ def run_mine(args, w):
                         "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": rows * n * 4,
                         "steps": e2e_steps},
                 "gpu_launches": launches, "clocks": clocks}
+        if world == 1 and args.workload == "gemm_i8" and not args.size and not args.no_others:
+            # the metric also names the Q16.16 GEMM, the GEMV and (by config) the int16 GEMM:
+            # their device-resident numbers ride along (each has its own --workload run too)
+            del a, b, c, ha, hb, hc
+            torch.cuda.empty_cache()
+            line["other_workloads"] = {name: quick_workload(name, blas, torch, stream)
+                                       for name in ("gemm_q16", "gemv_q16", "gemm_i16")}
         line["cpu_baseline"] = cpu_baseline(w) if world == 1 and not args.no_cpu else None
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -383,6 +435,7 @@ def main():
     ap.add_argument("--size", type=int, default=0, help="override M = K (= N) for quick runs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-check", action="store_true", help="skip the oracle gate before timing")
+    ap.add_argument("--no-others", action="store_true", help="skip the other configurations' ride-along numbers")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

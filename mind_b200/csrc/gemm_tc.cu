@@ -41,7 +41,6 @@ constexpr int UMMA_K = 32;              // K of one tcgen05.mma kind::i8
 constexpr int TC_THREADS = 192;
 constexpr int A_TILE_BYTES = BLOCK_M * BLOCK_K;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
-constexpr int GROUP_M = 16;             // m-tiles walked together, for L2 reuse
 
 template <int MODE, int PAIR>
 struct Cfg;
@@ -67,6 +66,8 @@ struct TcParams {
     int m, n, k;
     int m_tiles, n_tiles;  // tile grid; an m-tile is PAIR * 128 rows
     int vec_ok;            // C rows may be stored with 16-byte vectors
+    int group_m;           // m-tiles walked together before moving on in n (L2 reuse of A panels)
+    int hint_a, hint_b;    // L2 eviction policy per operand (see l2_policy)
     int* err;
 };
 
@@ -88,12 +89,13 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
     }
 }
 
-__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& tm, int& tn) {
-    const int per_group = GROUP_M * n_tiles;
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int group_m, int& tm,
+                                            int& tn) {
+    const int per_group = group_m * n_tiles;
     const int g = tile / per_group;
     const int r = tile - g * per_group;
-    const int gm0 = g * GROUP_M;
-    const int gsize = min(GROUP_M, m_tiles - gm0);
+    const int gm0 = g * group_m;
+    const int gsize = min(group_m, m_tiles - gm0);
     tm = gm0 + r % gsize;
     tn = r / gsize;
 }
@@ -173,9 +175,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
+            const uint64_t pol_a = l2_policy(p.hint_a), pol_b = l2_policy(p.hint_b);
             for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step) {
                 int tm, tn;
-                tile_coords(tile, p.m_tiles, p.n_tiles, tm, tn);
+                tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, tm, tn);
                 const int row_a = (tm * PAIR + (int)cta) * BLOCK_M;
                 const int row_b = tn * BLOCK_N + (int)cta * B_ROWS;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
@@ -189,31 +192,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                     if (PAIR == 1) {
                         const uint32_t bar = full0 + 8 * s;
                         mbar_arrive_expect_tx(bar, STAGE_BYTES);
-                        tma_load_2d(dst, &tm_a0, bar, kx, row_a);
-                        if (cfg::NA == 2) tma_load_2d(dst + A_TILE_BYTES, &tm_a1, bar, kx, row_a);
+                        tma_load_2d(dst, &tm_a0, bar, kx, row_a, pol_a);
+                        if (cfg::NA == 2) tma_load_2d(dst + A_TILE_BYTES, &tm_a1, bar, kx, row_a, pol_a);
                         const uint32_t db = dst + cfg::NA * A_TILE_BYTES;
                         if (!BMN) {
-                            tma_load_2d(db, &tm_b0, bar, kx, row_b);
-                            if (cfg::NB == 2) tma_load_2d(db + B_TILE_BYTES, &tm_b1, bar, kx, row_b);
+                            tma_load_2d(db, &tm_b0, bar, kx, row_b, pol_b);
+                            if (cfg::NB == 2) tma_load_2d(db + B_TILE_BYTES, &tm_b1, bar, kx, row_b, pol_b);
                         } else {
 #pragma unroll
                             for (int j = 0; j < B_ROWS / 128; ++j) {
-                                tma_load_2d(db + j * B_BOX_BYTES, &tm_b0, bar, row_b + 128 * j, kx);
+                                tma_load_2d(db + j * B_BOX_BYTES, &tm_b0, bar, row_b + 128 * j, kx, pol_b);
                                 if (cfg::NB == 2)
-                                    tma_load_2d(db + B_TILE_BYTES + j * B_BOX_BYTES, &tm_b1, bar, row_b + 128 * j, kx);
+                                    tma_load_2d(db + B_TILE_BYTES + j * B_BOX_BYTES, &tm_b1, bar, row_b + 128 * j, kx, pol_b);
                             }
                         }
                     } else if (BMN) {
                         const uint32_t bar = mapa(full0 + 8 * s, 0);
                         if (leader) mbar_arrive_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
-                        tma_load_2d_pair(dst, &tm_a0, bar, kx, row_a);
-                        if (cfg::NA == 2) tma_load_2d_pair(dst + A_TILE_BYTES, &tm_a1, bar, kx, row_a);
+                        tma_load_2d_pair(dst, &tm_a0, bar, kx, row_a, pol_a);
+                        if (cfg::NA == 2) tma_load_2d_pair(dst + A_TILE_BYTES, &tm_a1, bar, kx, row_a, pol_a);
                         const uint32_t db = dst + cfg::NA * A_TILE_BYTES;
 #pragma unroll
                         for (int j = 0; j < B_ROWS / 128; ++j) {
-                            tma_load_2d_pair(db + j * B_BOX_BYTES, &tm_b0, bar, row_b + 128 * j, kx);
+                            tma_load_2d_pair(db + j * B_BOX_BYTES, &tm_b0, bar, row_b + 128 * j, kx, pol_b);
                             if (cfg::NB == 2)
-                                tma_load_2d_pair(db + B_TILE_BYTES + j * B_BOX_BYTES, &tm_b1, bar, row_b + 128 * j, kx);
+                                tma_load_2d_pair(db + B_TILE_BYTES + j * B_BOX_BYTES, &tm_b1, bar, row_b + 128 * j, kx, pol_b);
                         }
                     } else {
                         // Both CTAs' copies complete on the LEADER's full barrier (it alone issues
@@ -222,11 +225,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                         // arrive: its release fence would drain the copies in flight every stage.
                         const uint32_t bar = mapa(full0 + 8 * s, 0);
                         if (leader) mbar_arrive_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
-                        tma_load_2d_pair(dst, &tm_a0, bar, kx, row_a);
-                        if (cfg::NA == 2) tma_load_2d_pair(dst + A_TILE_BYTES, &tm_a1, bar, kx, row_a);
+                        tma_load_2d_pair(dst, &tm_a0, bar, kx, row_a, pol_a);
+                        if (cfg::NA == 2) tma_load_2d_pair(dst + A_TILE_BYTES, &tm_a1, bar, kx, row_a, pol_a);
                         const uint32_t db = dst + cfg::NA * A_TILE_BYTES;
-                        tma_load_2d_pair(db, &tm_b0, bar, kx, row_b);
-                        if (cfg::NB == 2) tma_load_2d_pair(db + B_TILE_BYTES, &tm_b1, bar, kx, row_b);
+                        tma_load_2d_pair(db, &tm_b0, bar, kx, row_b, pol_b);
+                        if (cfg::NB == 2) tma_load_2d_pair(db + B_TILE_BYTES, &tm_b1, bar, kx, row_b, pol_b);
                     }
                 }
             }
@@ -294,7 +297,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
         uint32_t tcount = 0;
         for (int tile = tile_first; tile < total_tiles; tile += tile_step, ++tcount) {
             int tm, tn;
-            tile_coords(tile, p.m_tiles, p.n_tiles, tm, tn);
+            tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, tm, tn);
             const uint32_t as = tcount % ACC_STAGES, aph = (tcount / ACC_STAGES) & 1u;
             if (!wait_bounded(tfull0 + 8 * as, aph, abort_s, p.err, 4)) break;
             tc_fence_after();
@@ -418,6 +421,11 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     p.n_tiles = (int)((n + cfg::BLOCK_N - 1) / cfg::BLOCK_N);
     p.vec_ok = (n % 4 == 0) && (reinterpret_cast<uintptr_t>(c) % 16 == 0);
     p.err = ctx->err_word;
+    p.group_m = 16;
+    p.hint_a = p.hint_b = 0;
+    if (const char* e = getenv("MIND_B200_GROUP_M")) p.group_m = atoi(e) > 0 ? atoi(e) : 16;  // experiment hooks
+    if (const char* e = getenv("MIND_B200_HINT_A")) p.hint_a = atoi(e);
+    if (const char* e = getenv("MIND_B200_HINT_B")) p.hint_b = atoi(e);
     const long long total = (long long)p.m_tiles * p.n_tiles;
     if (total > 0x7fffffff) return fail(MIND_B200_ERR_TOO_LARGE, "too many output tiles");
     auto kern = gemm_tc_kernel<MODE, PAIR, BMN>;
