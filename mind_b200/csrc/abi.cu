@@ -115,29 +115,36 @@ int64_t check_dims(int64_t m, int64_t k, int64_t n) {
 }
 
 // ---------------------------------------------- host-operand pipeline (int8 GEMM)
-// With A and / or C in host memory a large GEMM is cut into row bands (independent,
-// like the reference's thread bands) so that the upload of band i+1, the product of
-// band i and the download of band i-1 overlap: copies run on two side streams, the
-// kernels on the library's stream, A and C bands are double-buffered in staging.
+// With A and / or C in host memory a large GEMM is cut into row bands (independent, like
+// the reference's thread bands) and, when C goes back to the host, into column chunks, so
+// that uploads, products and downloads overlap: copies run on two side streams, the kernels
+// on the library's stream.  Upload order is B chunk 0, the A bands, then the other B chunks;
+// the first C tile is on its way back after one B chunk and one A band have arrived, and
+// from then on the download link stays busy.  C tiles are double-buffered in staging.
 struct Pipe {
     cudaStream_t in = nullptr, out = nullptr;
-    cudaEvent_t start = nullptr, in_done[2] = {}, gemm_done[2] = {}, out_done[2] = {};
-    bool ready = false;
+    cudaEvent_t start = nullptr, gemm_done[2] = {}, out_done[2] = {};
+    std::vector<cudaEvent_t> ready;  // uploads: A bands, then B chunks
+    bool made = false;
 };
 Pipe g_pipe[64];
 
-int64_t pipe_for(DeviceCtx* ctx, Pipe** out) {
+int64_t pipe_for(DeviceCtx* ctx, size_t n_ready, Pipe** out) {
     Pipe& p = g_pipe[ctx->device];
-    if (!p.ready) {
+    if (!p.made) {
         MB200_CUDA(cudaStreamCreateWithFlags(&p.in, cudaStreamNonBlocking));
         MB200_CUDA(cudaStreamCreateWithFlags(&p.out, cudaStreamNonBlocking));
         MB200_CUDA(cudaEventCreateWithFlags(&p.start, cudaEventDisableTiming));
         for (int i = 0; i < 2; ++i) {
-            MB200_CUDA(cudaEventCreateWithFlags(&p.in_done[i], cudaEventDisableTiming));
             MB200_CUDA(cudaEventCreateWithFlags(&p.gemm_done[i], cudaEventDisableTiming));
             MB200_CUDA(cudaEventCreateWithFlags(&p.out_done[i], cudaEventDisableTiming));
         }
-        p.ready = true;
+        p.made = true;
+    }
+    while (p.ready.size() < n_ready) {
+        cudaEvent_t e;
+        MB200_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        p.ready.push_back(e);
     }
     *out = &p;
     return 0;
@@ -163,43 +170,79 @@ constexpr int64_t PIPE_MIN_ROWS = 1024;  // below this one band is as good as se
 
 int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const int8_t* b, bool b_host,
                           int32_t* c, bool c_host, int64_t m, int64_t k, int64_t n) {
-    Pipe* pp = nullptr;
-    MB200_TRY(pipe_for(ctx, &pp));
-    Pipe& P = *pp;
     const int64_t kp = (int64_t)align_up((size_t)k, 16);
-    int64_t band = (int64_t)align_up((size_t)((m + 7) / 8), 256);
+    const int64_t band = (int64_t)align_up((size_t)((m + 7) / 8), 256);
     const int64_t bands = (m + band - 1) / band;
+    // Column chunks only pay when C is downloaded, and need B readable in place per chunk.
+    const bool b_inplace_ok = !g_force_transpose && n % 16 == 0 && (b_host || reinterpret_cast<uintptr_t>(b) % 16 == 0);
+    const int64_t chunks = (c_host && b_inplace_ok && n >= 4096 && n % 64 == 0) ? 4 : 1;
+    const int64_t nj = n / chunks;  // columns per chunk (a multiple of 16 when chunks > 1)
+    Pipe* pp = nullptr;
+    MB200_TRY(pipe_for(ctx, (size_t)(bands + chunks), &pp));
+    Pipe& P = *pp;
 
-    // staging: B, two A bands (pitch kp), two C bands
+    // staging: all of B (as dense chunks), all of A (pitch kp), two C tiles
     const size_t sb = b_host ? align_up((size_t)k * n, 1024) : 0;
-    const size_t sa = a_host ? align_up((size_t)band * kp, 1024) : 0;
-    const size_t sc = c_host ? align_up((size_t)band * n * 4, 1024) : 0;
-    MB200_TRY(arena_reserve(ctx, ctx->staging, sb + 2 * sa + 2 * sc + 8192));
-    const int8_t* db = b;
-    if (b_host) {
-        int8_t* t = static_cast<int8_t*>(arena_take(ctx->staging, sb));
-        MB200_CUDA(cudaMemcpyAsync(t, b, (size_t)k * n, cudaMemcpyHostToDevice, ctx->stream));
-        db = t;
-    }
-    int8_t* a_slot[2] = {nullptr, nullptr};
+    const size_t sa = a_host ? align_up((size_t)m * kp, 1024) : 0;
+    const size_t sc = c_host ? align_up((size_t)band * nj * 4, 1024) : 0;
+    MB200_TRY(arena_reserve(ctx, ctx->staging, sb + sa + 2 * sc + 8192));
+    int8_t* b_stage = b_host ? static_cast<int8_t*>(arena_take(ctx->staging, sb)) : nullptr;
+    int8_t* a_stage = a_host ? static_cast<int8_t*>(arena_take(ctx->staging, sa)) : nullptr;
     int32_t* c_slot[2] = {nullptr, nullptr};
-    for (int s = 0; s < 2; ++s) {
-        if (a_host) a_slot[s] = static_cast<int8_t*>(arena_take(ctx->staging, sa));
+    for (int s = 0; s < 2; ++s)
         if (c_host) c_slot[s] = static_cast<int32_t*>(arena_take(ctx->staging, sc));
-    }
 
-    // scratch: transposed B and / or padded device A, laid out once for all bands
-    const bool b_direct = !g_force_transpose && n % 16 == 0 && reinterpret_cast<uintptr_t>(db) % 16 == 0;
+    // B as the kernels will see it: chunk j is dense [k][nj] in staging (host B), or a column
+    // window of the caller's device B (pitch n).
+    const int64_t b_pitch = b_host ? nj : n;
+    auto b_chunk = [&](int64_t j) -> const int8_t* {
+        return b_host ? b_stage + (size_t)j * k * nj : b + (size_t)j * nj;
+    };
+    const bool b_direct = b_inplace_ok;  // with a host B the staged chunks are 1024-byte aligned
     const bool a_dev_direct = a_host || (kp == k && reinterpret_cast<uintptr_t>(a) % 16 == 0);
     const size_t bt_bytes = b_direct ? 0 : (size_t)n * kp, ap_bytes = a_dev_direct ? 0 : (size_t)m * kp;
     MB200_TRY(arena_reserve(ctx, ctx->scratch, align_up(bt_bytes, 1024) + align_up(ap_bytes, 1024) + 2048));
+
+    // side streams start after everything already queued on the library's stream
+    MB200_CUDA(cudaEventRecord(P.start, ctx->stream));
+    MB200_CUDA(cudaStreamWaitEvent(P.in, P.start, 0));
+    MB200_CUDA(cudaStreamWaitEvent(P.out, P.start, 0));
+
+    // ---- uploads, all queued now on the in-stream in the order the products need them
+    auto upload_b = [&](int64_t j) -> int64_t {
+        if (chunks == 1)
+            MB200_CUDA(cudaMemcpyAsync(b_stage, b, (size_t)k * n, cudaMemcpyHostToDevice, P.in));
+        else
+            MB200_CUDA(cudaMemcpy2DAsync(b_stage + (size_t)j * k * nj, (size_t)nj, b + (size_t)j * nj, (size_t)n,
+                                         (size_t)nj, (size_t)k, cudaMemcpyHostToDevice, P.in));
+        MB200_CUDA(cudaEventRecord(P.ready[bands + j], P.in));
+        return 0;
+    };
+    if (b_host) MB200_TRY(upload_b(0));
+    if (a_host)
+        for (int64_t i = 0; i < bands; ++i) {
+            const int64_t r0 = i * band, rows = (m - r0 < band) ? m - r0 : band;
+            int8_t* dst = a_stage + (size_t)r0 * kp;
+            const int8_t* src = a + (size_t)r0 * k;
+            if (kp == k)
+                MB200_CUDA(cudaMemcpyAsync(dst, src, (size_t)rows * k, cudaMemcpyHostToDevice, P.in));
+            else  // pad to a 16-byte pitch on the way: the pad bytes are never read
+                MB200_CUDA(cudaMemcpy2DAsync(dst, (size_t)kp, src, (size_t)k, (size_t)k, (size_t)rows,
+                                             cudaMemcpyHostToDevice, P.in));
+            MB200_CUDA(cudaEventRecord(P.ready[i], P.in));
+        }
+    if (b_host)
+        for (int64_t j = 1; j < chunks; ++j) MB200_TRY(upload_b(j));
+
+    // ---- one-off re-layouts on the library's stream
     int8_t* bt = nullptr;
-    if (!b_direct) {
+    if (!b_direct) {  // chunks == 1 here
+        if (b_host) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.ready[bands], 0));
         bt = static_cast<int8_t*>(arena_take(ctx->scratch, bt_bytes));
-        MB200_TRY(launch_transpose_i8(ctx, db, bt, k, n, kp));
+        MB200_TRY(launch_transpose_i8(ctx, b_chunk(0), bt, k, n, kp));
     }
-    const int8_t* a_dev = a;
-    int64_t a_pitch = k;
+    const int8_t* a_dev = a_host ? a_stage : a;
+    int64_t a_pitch = a_host ? kp : k;
     if (!a_host && !a_dev_direct) {
         int8_t* ap = static_cast<int8_t*>(arena_take(ctx->scratch, ap_bytes));
         MB200_TRY(launch_pad_rows_i8(ctx, a, ap, m, k, kp));
@@ -207,47 +250,36 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
         a_pitch = kp;
     }
 
-    // side streams start after everything already queued on the library's stream
-    MB200_CUDA(cudaEventRecord(P.start, ctx->stream));
-    MB200_CUDA(cudaStreamWaitEvent(P.in, P.start, 0));
-    MB200_CUDA(cudaStreamWaitEvent(P.out, P.start, 0));
-    for (int64_t i = 0; i < bands; ++i) {
-        const int s = (int)(i & 1);
-        const int64_t r0 = i * band, rows = (m - r0 < band) ? m - r0 : band;
-        const int8_t* a_band;
-        int64_t pitch;
-        if (a_host) {
-            if (i >= 2) MB200_CUDA(cudaStreamWaitEvent(P.in, P.gemm_done[s], 0));  // slot free again
-            const int8_t* src = a + (size_t)r0 * k;
-            if (kp == k)
-                MB200_CUDA(cudaMemcpyAsync(a_slot[s], src, (size_t)rows * k, cudaMemcpyHostToDevice, P.in));
-            else  // pad to a 16-byte pitch on the way: the pad bytes are never read
-                MB200_CUDA(cudaMemcpy2DAsync(a_slot[s], (size_t)kp, src, (size_t)k, (size_t)k, (size_t)rows,
-                                             cudaMemcpyHostToDevice, P.in));
-            MB200_CUDA(cudaEventRecord(P.in_done[s], P.in));
-            MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.in_done[s], 0));
-            a_band = a_slot[s];
-            pitch = kp;
-        } else {
-            a_band = a_dev + (size_t)r0 * a_pitch;
-            pitch = a_pitch;
-        }
-        int32_t* c_band = c_host ? c_slot[s] : c + (size_t)r0 * n;
-        if (c_host && i >= 2) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.out_done[s], 0));
-        if (b_direct)
-            MB200_TRY(launch_gemm_i8_tc_bmn(ctx, a_band, db, c_band, rows, n, k, pitch, n));
-        else
-            MB200_TRY(launch_gemm_i8_tc(ctx, a_band, bt, c_band, rows, n, k, pitch, kp));
-        MB200_CUDA(cudaEventRecord(P.gemm_done[s], ctx->stream));
-        if (c_host) {
-            MB200_CUDA(cudaStreamWaitEvent(P.out, P.gemm_done[s], 0));
-            MB200_CUDA(cudaMemcpyAsync(c + (size_t)r0 * n, c_slot[s], (size_t)rows * n * 4,
-                                       cudaMemcpyDeviceToHost, P.out));
-            MB200_CUDA(cudaEventRecord(P.out_done[s], P.out));
+    // ---- products and downloads
+    int64_t t = 0;  // running C tile count: picks the staging slot
+    for (int64_t j = 0; j < chunks; ++j) {
+        if (b_host && b_direct) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.ready[bands + j], 0));
+        for (int64_t i = 0; i < bands; ++i, ++t) {
+            const int s = (int)(t & 1);
+            const int64_t r0 = i * band, rows = (m - r0 < band) ? m - r0 : band;
+            if (a_host && j == 0) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.ready[i], 0));
+            if (c_host && t >= 2) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.out_done[s], 0));  // slot free
+            int32_t* c_tile = c_host ? c_slot[s] : c + (size_t)r0 * n;
+            const int8_t* a_band = a_dev + (size_t)r0 * a_pitch;
+            if (b_direct)
+                MB200_TRY(launch_gemm_i8_tc_bmn(ctx, a_band, b_chunk(j), c_tile, rows, nj, k, a_pitch, b_pitch));
+            else
+                MB200_TRY(launch_gemm_i8_tc(ctx, a_band, bt, c_tile, rows, n, k, a_pitch, kp));
+            if (c_host) {
+                MB200_CUDA(cudaEventRecord(P.gemm_done[s], ctx->stream));
+                MB200_CUDA(cudaStreamWaitEvent(P.out, P.gemm_done[s], 0));
+                int32_t* dst = c + (size_t)r0 * n + (size_t)j * nj;
+                if (chunks == 1)
+                    MB200_CUDA(cudaMemcpyAsync(dst, c_slot[s], (size_t)rows * n * 4, cudaMemcpyDeviceToHost, P.out));
+                else
+                    MB200_CUDA(cudaMemcpy2DAsync(dst, (size_t)n * 4, c_slot[s], (size_t)nj * 4, (size_t)nj * 4,
+                                                 (size_t)rows, cudaMemcpyDeviceToHost, P.out));
+                MB200_CUDA(cudaEventRecord(P.out_done[s], P.out));
+            }
         }
     }
     if (c_host)
-        for (int s = 0; s < 2 && s < bands; ++s) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.out_done[s], 0));
+        for (int s = 0; s < 2 && s < t; ++s) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.out_done[s], 0));
     MB200_CUDA(cudaMemcpyAsync(ctx->err_host, ctx->err_word, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     MB200_CUDA(cudaStreamSynchronize(ctx->stream));
     return Call::check_err_word(ctx);
