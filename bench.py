@@ -45,6 +45,10 @@ WORKLOADS = {
                      unit="GB/s", dtype="q16.16 (s32)", bound="hbm"),
 }
 ELEM_BYTES = {KIND_Q16: 4, KIND_I8: 1, KIND_I16: 2}
+# dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel, one launch at the
+# workload's full size, from the ncu captures summarised under profiles/ (bytes).
+NCU_TRAFFIC = {"gemm_i8": 5596628736 + 1057698048, "gemv_q16": 1073876000 + 3520000,
+               "gemm_i16": 94822656 + 37608704}
 
 
 def work_units(w, m):
@@ -394,7 +398,8 @@ def run_mine(args, w):
         else:
             peak, peak_note = None, "no measured INT32 multiply-add peak on this pool"
         roofline = {"bound": w["bound"], "achieved": achieved, "peak": peak, "unit": w["unit"],
-                    "frac": (achieved / peak) if achieved and peak else None, "traffic": None,
+                    "frac": (achieved / peak) if achieved and peak else None,
+                    "traffic": NCU_TRAFFIC.get(args.workload) if not args.size and world == 1 else None,
                     "kernel": "gemm_tc_kernel" if w["bound"] == "tensor" else ("rows_group_kernel" if w["bound"] == "hbm" else "gemm_q16_fp64_kernel"),
                     "kernel_ms": main_ms / n_main if n_main else None, "peak_source": peak_note}
         line = {"metric": w["metric"], "value": value, "unit": w["unit"], "n_gpus": world,
