@@ -83,9 +83,7 @@ public:
         for (auto& o : ops_)
             if (o.host && o.output && o.bytes)
                 MB200_CUDA(cudaMemcpyAsync(o.user, o.dev, o.bytes, cudaMemcpyDeviceToHost, ctx_->stream));
-        if (waits_inside)
-            MB200_CUDA(cudaMemcpyAsync(ctx_->err_host, ctx_->err_word, sizeof(int),
-                                       cudaMemcpyDeviceToHost, ctx_->stream));
+        (void)waits_inside;  // the error word is host-mapped: nothing to fetch
         if (any_host_) {
             MB200_CUDA(cudaStreamSynchronize(ctx_->stream));
             return check_err_word(ctx_);
@@ -97,7 +95,6 @@ public:
         const int code = *ctx->err_host;
         if (code == 0) return 0;
         *ctx->err_host = 0;
-        cudaMemsetAsync(ctx->err_word, 0, sizeof(int), ctx->stream);
         return fail(MIND_B200_ERR_TIMEOUT,
                     "a bounded wait inside the GEMM kernel ran out (role code %d); the output is invalid",
                     code);
@@ -280,7 +277,6 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
     }
     if (c_host)
         for (int s = 0; s < 2 && s < t; ++s) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.out_done[s], 0));
-    MB200_CUDA(cudaMemcpyAsync(ctx->err_host, ctx->err_word, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     MB200_CUDA(cudaStreamSynchronize(ctx->stream));
     return Call::check_err_word(ctx);
 }

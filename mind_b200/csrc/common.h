@@ -49,8 +49,8 @@ struct DeviceCtx {
     cudaStream_t stream = nullptr;  // the stream every launch and copy goes to
     Arena scratch;                  // operand re-layouts (transposed B, limb planes, padded A)
     Arena staging;                  // device copies of host-pointer operands
-    int* err_word = nullptr;        // device word a kernel sets when a bounded wait runs out
-    int* err_host = nullptr;        // pinned mirror of err_word
+    int* err_word = nullptr;        // word a kernel sets when a bounded wait runs out (device view)
+    int* err_host = nullptr;        // the same word, host view (mapped pinned memory)
     // Optional timing of the main kernel of each call (CUDA events on `stream`).
     static constexpr int PROF_RING = 512;
     bool profile = false;

@@ -84,9 +84,10 @@ DeviceCtx* current_ctx() {
              major, minor);
         return nullptr;
     }
-    if (cudaMalloc(&ctx->err_word, sizeof(int)) != cudaSuccess ||
-        cudaMemset(ctx->err_word, 0, sizeof(int)) != cudaSuccess ||
-        cudaMallocHost(&ctx->err_host, sizeof(int)) != cudaSuccess) {
+    // The error word lives in mapped pinned host memory: a kernel writes it only when a bounded
+    // wait runs out, and the host reads it after a synchronisation without any copy per call.
+    if (cudaHostAlloc(&ctx->err_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer(reinterpret_cast<void**>(&ctx->err_word), ctx->err_host, 0) != cudaSuccess) {
         fail(MIND_B200_ERR_CUDA, "could not allocate the device error word: %s",
              cudaGetErrorString(cudaGetLastError()));
         return nullptr;

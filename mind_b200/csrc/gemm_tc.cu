@@ -453,16 +453,19 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     if (PAIR == 2) {
         // Not every SM need be pairable; a pair that is not resident would only start
         // after another one ends, so size the persistent grid to what fits at once.
-        int fit = 0;
-        cudaError_t oe = cudaOccupancyMaxActiveClusters(&fit, kern, &lc);
-        if (getenv("MIND_B200_DEBUG"))
-            fprintf(stderr, "[mind_b200] pair launch: units=%d fit=%d (%s)\n", units, fit,
-                    cudaGetErrorString(oe));
-        if (oe == cudaSuccess && fit > 0 && fit < units) {
+        static thread_local int fit_dev = -1, fit = 0;  // per template instance; asked once per device
+        if (fit_dev != ctx->device) {
+            lc.gridDim = dim3((unsigned)(ctx->sm_count / PAIR * PAIR), 1, 1);
+            if (cudaOccupancyMaxActiveClusters(&fit, kern, &lc) != cudaSuccess) {
+                cudaGetLastError();
+                fit = 0;
+            }
+            fit_dev = ctx->device;
+            lc.gridDim = dim3((unsigned)(units * PAIR), 1, 1);
+        }
+        if (fit > 0 && fit < units) {
             units = fit;
             lc.gridDim = dim3((unsigned)(units * PAIR), 1, 1);
-        } else {
-            cudaGetLastError();
         }
     }
     prof_begin(ctx);
@@ -480,18 +483,23 @@ int64_t set_pair_mode(int pair) {
     return 0;
 }
 
+// Measured on B200: the CTA-pair kernel is the faster int8 kernel once there is more than one
+// 128 x 256 tile per SM (3072^3 and up: +6 % to +17 %); below that one CTA per tile is as fast
+// or slightly faster and needs no cluster launch.
+static bool pair_pays(const DeviceCtx* ctx, int64_t m, int64_t n) {
+    return m > 128 && ((m + 127) / 128) * ((n + 255) / 256) > ctx->sm_count;
+}
+
 int64_t launch_gemm_i8_tc(DeviceCtx* ctx, const int8_t* a, const int8_t* bt, int32_t* c, int64_t m,
                           int64_t n, int64_t k, int64_t kp_a, int64_t kp_b) {
-    // Measured on B200: the CTA-pair kernel is the faster int8 kernel whenever an output
-    // tile of 256 rows is not mostly padding.
-    const bool pair = g_pair_mode == 2 || (g_pair_mode == 0 && m > 128);
+    const bool pair = g_pair_mode == 2 || (g_pair_mode == 0 && pair_pays(ctx, m, n));
     if (pair) return launch_tc<0, 2, false>(ctx, a, nullptr, bt, nullptr, c, m, n, k, kp_a, kp_b);
     return launch_tc<0, 1, false>(ctx, a, nullptr, bt, nullptr, c, m, n, k, kp_a, kp_b);
 }
 
 int64_t launch_gemm_i8_tc_bmn(DeviceCtx* ctx, const int8_t* a, const int8_t* b, int32_t* c, int64_t m,
                               int64_t n, int64_t k, int64_t kp_a, int64_t pitch_b) {
-    const bool pair = g_pair_mode == 2 || (g_pair_mode == 0 && m > 128);
+    const bool pair = g_pair_mode == 2 || (g_pair_mode == 0 && pair_pays(ctx, m, n));
     if (pair) return launch_tc<0, 2, true>(ctx, a, nullptr, b, nullptr, c, m, n, k, kp_a, pitch_b);
     return launch_tc<0, 1, true>(ctx, a, nullptr, b, nullptr, c, m, n, k, kp_a, pitch_b);
 }
