@@ -153,6 +153,10 @@ int64_t mind_b200_reserve(int64_t scratch_bytes, int64_t staging_bytes);
  * 16-byte aligned); 1 = the independent CUDA-core kernel kept as an on-device cross-check.
  * Every path gives identical bytes. */
 int64_t mind_b200_set_gemm_path(int64_t path);
+/* Self-test of the bounded waits inside the GEMM kernels: launches a one-warp kernel that waits
+ * (with the given limit, 1..1000 ms) on a barrier nothing will ever complete.  The expected
+ * result is MIND_B200_ERR_TIMEOUT with the CUDA context still usable. */
+int64_t mind_b200_selftest_wait_timeout(int64_t limit_ms);
 /* Kernel timing for measurements: while enabled, the dominant kernel of every call (the
  * GEMM / GEMV kernel itself, not the operand re-layout) is bracketed by CUDA events on the
  * library's stream.  mind_b200_profile_read waits for the stream, returns how many kernels

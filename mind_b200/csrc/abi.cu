@@ -542,6 +542,17 @@ int64_t mind_b200_set_gemm_path(int64_t path) {
     return fail(MIND_B200_ERR_INVALID, "gemm path must be 0 (auto), 1 (CUDA cores), 2 / 3 (CTA pairs / single CTA) or 4 / 5 (the same with B transposed first)");
 }
 
+int64_t mind_b200_selftest_wait_timeout(int64_t limit_ms) {
+    clear_error();
+    if (limit_ms < 1 || limit_ms > 1000) return fail(MIND_B200_ERR_INVALID, "limit must be 1..1000 ms");
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return MIND_B200_ERR_NO_DEVICE;
+    std::lock_guard<std::mutex> lock(g_call_mutex);
+    MB200_TRY(launch_wait_selftest(ctx, limit_ms));
+    MB200_CUDA(cudaStreamSynchronize(ctx->stream));
+    return Call::check_err_word(ctx);
+}
+
 int64_t mind_b200_profile(int64_t enable) {
     clear_error();
     DeviceCtx* ctx = current_ctx();

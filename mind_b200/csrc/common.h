@@ -103,6 +103,7 @@ int64_t launch_gemm_i16_tc_bmn(DeviceCtx* ctx, const int8_t* a_hi, const uint8_t
                                const int8_t* b_hi, const uint8_t* b_lo, int32_t* c, int64_t m,
                                int64_t n, int64_t k, int64_t kp_a, int64_t pitch_b);
 bool tc_pair_forced();
+int64_t launch_wait_selftest(DeviceCtx* ctx, int64_t limit_ms);
 // Re-layout kernels.
 int64_t launch_transpose_i8(DeviceCtx* ctx, const int8_t* b, int8_t* bt, int64_t k, int64_t n,
                             int64_t kp);

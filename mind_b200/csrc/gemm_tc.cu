@@ -72,7 +72,8 @@ struct TcParams {
 };
 
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_s,
-                                             int* err_g, int code) {
+                                             int* err_g, int code,
+                                             unsigned long long limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
@@ -80,7 +81,7 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 63u) == 0u) {
             if (*abort_s) return false;
-            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 *abort_s = 1;
                 atomicCAS(err_g, 0, code);
                 return false;
@@ -363,6 +364,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
     }
 }
 
+// A wait that nothing will ever satisfy, with a short limit: exercises the give-up path of
+// wait_bounded (error word written, kernel returns, context stays usable).
+__global__ void wait_selftest_kernel(int* err, unsigned long long limit_ns) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) wait_bounded(smem_u32(&bar), 0, &abort_flag, err, 9, limit_ns);
+}
+
 // 2-D map over a row-major 8-bit matrix [rows][k] with row pitch `pitch` bytes; the
 // box is 128 bytes of K by `box_rows` rows, written to shared memory with the
 // 128-byte swizzle.  Reads past `k` or `rows` return zeros.
@@ -476,6 +491,12 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
 }
 
 }  // namespace
+
+int64_t launch_wait_selftest(DeviceCtx* ctx, int64_t limit_ms) {
+    wait_selftest_kernel<<<1, 32, 0, ctx->stream>>>(ctx->err_word, (unsigned long long)limit_ms * 1000000ull);
+    count_launch();
+    return check_launch("wait_selftest_kernel");
+}
 
 int64_t set_pair_mode(int pair) {
     if (pair < 0 || pair > 2) return fail(MIND_B200_ERR_INVALID, "CTAs per tile must be 0 (auto), 1 or 2");

@@ -194,8 +194,8 @@ int64_t launch_rows(DeviceCtx* ctx, const void* w, const void* x, int32_t* y, in
         else
             rows_block_kernel<OP, false><<<grid, 512, 0, ctx->stream>>>(wc, x, y, rows, cols, row_bytes);
     } else {
-        int64_t blocks = (rows + 15) / 16;  // 16 warps per block
-        if (blocks > (int64_t)sms * 2) blocks = (int64_t)sms * 2;
+        int64_t blocks = (rows + 15) / 16;  // 16 warps per block, one row per warp, one pass
+        if (blocks > (int64_t)sms * 64) blocks = (int64_t)sms * 64;
         if (vec)
             rows_warp_kernel<OP, true><<<(unsigned)blocks, 512, 0, ctx->stream>>>(wc, x, y, rows, cols, row_bytes);
         else

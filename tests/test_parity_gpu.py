@@ -276,6 +276,24 @@ def test_unaligned_operands(gpu):
     assert np.array_equal(y[1:], O.gemv_q16(wbuf[1:].copy(), xbuf[1:].copy(), m, k))
 
 
+def test_bounded_wait_gives_up_cleanly(gpu):
+    """Every mbarrier wait in the GEMM kernels is bounded.  A one-warp kernel waits on a barrier
+    that nothing completes (limit 50 ms): the call must come back with ERR_TIMEOUT, and the
+    context must still compute correctly afterwards.  Nothing faults or hangs."""
+    import ctypes as C
+    import mind_b200
+    f = mind_b200.lib().mind_b200_selftest_wait_timeout
+    f.argtypes, f.restype = [C.c_int64], C.c_int64
+    assert f(50) == mind_b200.ERR_TIMEOUT
+    assert "bounded wait" in mind_b200.last_error()
+    g = O.Lcg(3)
+    a, b = g.i8(256 * 128), g.i8(128 * 256)
+    c = np.empty(256 * 256, dtype=np.int32)
+    gpu.matmul_mm_i8_v(a, b, c, 256, 128, 256)
+    assert np.array_equal(c, O.gemm_i8(a, b, 256, 128, 256))
+    assert f(0) == mind_b200.ERR_INVALID
+
+
 def test_errors_do_not_abort(gpu):
     import mind_b200
     a = np.zeros(16, dtype=np.int8)
