@@ -98,23 +98,24 @@ __global__ void split_rows_i16_kernel(const int16_t* __restrict__ a, int8_t* __r
         }
 }
 
-// 8 int16 per thread (one 16-byte load, two 8-byte stores); needs k % 8 == 0,
-// kp == k and a 16-byte aligned base.
+// 32 int16 per thread (four 16-byte loads in flight, eight 8-byte stores); needs k % 8 == 0,
+// kp == k and a 16-byte aligned base.  Byte permutes pick the low / high bytes.
 __global__ void split_rows_i16_vec_kernel(const uint4* __restrict__ a, uint2* __restrict__ hi,
                                           uint2* __restrict__ lo, int64_t n8) {
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n8;
-         i += (int64_t)gridDim.x * blockDim.x) {
-        const uint4 v = a[i];
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-        uint32_t h[2], l[2];
+    constexpr int U = 4;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i0 = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i0 < n8; i0 += stride * U) {
+        uint4 v[U];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const uint32_t w0 = w[2 * j], w1 = w[2 * j + 1];
-            l[j] = (w0 & 0xff) | ((w0 >> 8) & 0xff00) | ((w1 & 0xff) << 16) | ((w1 << 8) & 0xff000000u);
-            h[j] = ((w0 >> 8) & 0xff) | ((w0 >> 16) & 0xff00) | ((w1 << 8) & 0xff0000) | (w1 & 0xff000000u);
+        for (int u = 0; u < U; ++u)
+            if (i0 + u * stride < n8) v[u] = a[i0 + u * stride];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t i = i0 + u * stride;
+            if (i >= n8) break;
+            hi[i] = make_uint2(__byte_perm(v[u].x, v[u].y, 0x7531), __byte_perm(v[u].z, v[u].w, 0x7531));
+            lo[i] = make_uint2(__byte_perm(v[u].x, v[u].y, 0x6420), __byte_perm(v[u].z, v[u].w, 0x6420));
         }
-        hi[i] = make_uint2(h[0], h[1]);
-        lo[i] = make_uint2(l[0], l[1]);
     }
 }
 
@@ -159,8 +160,8 @@ int64_t launch_split_rows_i16(DeviceCtx* ctx, const int16_t* a, int8_t* hi, uint
                               int64_t k, int64_t kp) {
     if (kp == k && k % 8 == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0) {
         const int64_t n8 = m * k / 8;
-        int64_t blocks = (n8 + 255) / 256;
-        if (blocks > 148 * 32) blocks = 148 * 32;
+        int64_t blocks = (n8 + 256 * 4 - 1) / (256 * 4);  // one pass: four vectors per thread
+        if (blocks > 148 * 256) blocks = 148 * 256;
         split_rows_i16_vec_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(
             reinterpret_cast<const uint4*>(a), reinterpret_cast<uint2*>(hi),
             reinterpret_cast<uint2*>(lo), n8);
