@@ -83,7 +83,8 @@ def self_generated() -> dict:
 
 
 def main() -> None:
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    # default: a checkout of the reference beside this repository
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.dirname(os.path.dirname(HERE)), "..", "reference")
     if os.path.isdir(ref):
         with open(os.path.join(HERE, "reference_hashes.json"), "w") as f:
             json.dump(from_reference(ref), f, indent=1, sort_keys=True)
