@@ -140,9 +140,21 @@ def cpu_call(w, a, b, rows, threads=0):
         return O.baseline_gemm_i8(a, b, rows, k, n, threads)
     if w["fn"] == "matmul_mm_i16":
         return O.baseline_gemm_i16(a, b, rows, k, n, threads)
+    if cpu_kind(w) == "reference":
+        # the reference's own C dot and thread pool; b is B transposed for the GEMM
+        if w["fn"] == "matmul_mm_q16_v":
+            return O.reference_gemm_q16_bt(a, b, rows, k, n)
+        return O.reference_gemv_q16(a, b, rows, k)
     if w["fn"] == "matmul_mm_q16_v":
         return O.baseline_gemm_q16(a, b, rows, k, n, threads)
     return O.baseline_gemv_q16(a, b, rows, k, threads)
+
+
+def cpu_kind(w):
+    """"reference": the Q16.16 workloads are timed on the reference's own compiled C (dot +
+    pool, oracle/_ref) when it was built; "port": the threaded restatement (oracle/cpu_baseline.c)."""
+    import oracle as O
+    return "reference" if w["kind"] == KIND_Q16 and O.ref_lib() is not None else "port"
 
 
 def cpu_inputs(w, rows):
@@ -156,6 +168,8 @@ def cpu_inputs(w, rows):
     g2 = O.Lcg(w["seed"] ^ 0x5555)
     draw2 = {KIND_I8: g2.i8, KIND_I16: g2.i16, KIND_Q16: lambda c: g2.q16(c, w["shift"])}[w["kind"]]
     b = draw2(k * n)
+    if cpu_kind(w) == "reference" and n > 1:  # the reference's gate composes the GEMM over B transposed
+        b = np.ascontiguousarray(b.reshape(k, n).T).reshape(-1)
     return a, b
 
 
@@ -183,7 +197,7 @@ def cpu_baseline(w, target_s=15.0):
     _, used = cpu_call(w, a, b, rows)
     dt = time.perf_counter() - t0
     return {"value": work_units(w, rows) / dt / unit_scale(w), "unit": w["unit"], "cores": used,
-            "kind": "port",
+            "kind": cpu_kind(w),
             "sample": f"rows 0..{rows} of {w['m']} (all of K and N), {dt:.2f} s; row bands are independent, so time is linear in rows",
             "host_cpus": cores}
 
@@ -211,7 +225,7 @@ def run_reference(args, w):
             "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
             "config": {"workload": f"{args.workload} {w['m']}x{w['k']}x{w['n']}", "sample": sample},
-            "cpu_baseline": {"value": value, "unit": w["unit"], "cores": used, "kind": "port",
+            "cpu_baseline": {"value": value, "unit": w["unit"], "cores": used, "kind": cpu_kind(w),
                              "sample": sample, "host_cpus": cores},
             "e2e": {"value": value, "unit": w["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)

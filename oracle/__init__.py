@@ -60,6 +60,10 @@ def lib() -> C.CDLL:
             getattr(L, name).argtypes = [p, p, p, i64, i64, i64]
             getattr(L, name).restype = i64
         L.baseline_online_cpus.restype = i64
+        L.reference_gemv_q16_mt.argtypes = [p, p, p, p, p, i64, i64]
+        L.reference_gemv_q16_mt.restype = i64
+        L.reference_gemm_q16_bt_mt.argtypes = [p, p, p, p, p, i64, i64, i64]
+        L.reference_gemm_q16_bt_mt.restype = i64
         _lib = L
     return _lib
 
@@ -242,6 +246,29 @@ def baseline_gemv_i16(w, x, rows, cols, threads=0):
     y = np.empty(rows, dtype=np.int32)
     used = lib().baseline_gemv_i16_mt(_ptr(w), _ptr(x), _ptr(y), rows, cols, threads)
     return y, int(used)
+
+
+def _ref_fns():
+    R = ref_lib()
+    if R is None:
+        raise RuntimeError("oracle/_ref/libmind_ref.so was not built")
+    return (C.cast(R.__mind_blas_dot_q16, C.c_void_p), C.cast(R.__mind_blas_mt_dispatch, C.c_void_p))
+
+
+def reference_gemv_q16(w, x, rows, cols):
+    """GEMV by the reference's own C dot and thread pool (see cpu_baseline.c)."""
+    dot, disp = _ref_fns()
+    y = np.empty(rows, dtype=np.int32)
+    used = lib().reference_gemv_q16_mt(dot, disp, _ptr(w), _ptr(x), _ptr(y), rows, cols)
+    return y, int(used)
+
+
+def reference_gemm_q16_bt(a, bt, m, k, n):
+    """Q16.16 GEMM as row dots over B-transposed, by the reference's own C dot and pool."""
+    dot, disp = _ref_fns()
+    c = np.empty(m * n, dtype=np.int32)
+    used = lib().reference_gemm_q16_bt_mt(dot, disp, _ptr(a), _ptr(bt), _ptr(c), m, k, n)
+    return c, int(used)
 
 
 def online_cpus() -> int:

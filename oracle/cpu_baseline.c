@@ -298,3 +298,70 @@ BASELINE_EXPORT int64_t baseline_gemv_i16_mt(const int16_t *w, const int16_t *x,
     gemv_i16_ctx g = {w, x, y, cols};
     return run_bands(gemv_i16_band, &g, rows, threads);
 }
+
+/* ------------------------------------------------------------------------- *
+ * The reference's OWN code as the timed baseline for the Q16.16 paths: rows are
+ * computed by its `__mind_blas_dot_q16` (runtime-support/mind_intrinsics.c:1536-1547,
+ * AVX2 when the host has it) and scheduled by its persistent pool
+ * `__mind_blas_mt_dispatch` (:2017-2046) with its band rule
+ * (src/mlir/lowering.rs:10146-10205).  Both functions are passed in as addresses
+ * taken from the separately built reference library; nothing of it is compiled here.
+ * The GEMM is composed from row dots over B-transposed, as the reference's own
+ * gate composes it (tests/cross_substrate_identity.rs:82-94).
+ * ------------------------------------------------------------------------- */
+typedef int64_t (*ref_dot_fn)(int64_t, int64_t, int64_t);
+typedef void (*ref_dispatch_fn)(void *(*)(void *), char *, long, long);
+
+typedef struct {
+    ref_dot_fn dot;
+    const int32_t *w, *x;   /* GEMV: matrix, vector.  GEMM: A, B-transposed */
+    int32_t *y;
+    int64_t cols, n;        /* n == 0: GEMV; else GEMM with N = n */
+    int64_t rs, re;
+} ref_band;
+
+static void *ref_band_worker(void *p) {
+    ref_band *b = (ref_band *)p;
+    for (int64_t r = b->rs; r < b->re; ++r) {
+        const int32_t *row = b->w + r * b->cols;
+        if (b->n == 0) {
+            b->y[r] = (int32_t)b->dot((int64_t)(intptr_t)row, (int64_t)(intptr_t)b->x, b->cols);
+        } else {
+            for (int64_t j = 0; j < b->n; ++j)
+                b->y[r * b->n + j] =
+                    (int32_t)b->dot((int64_t)(intptr_t)row, (int64_t)(intptr_t)(b->x + j * b->cols), b->cols);
+        }
+    }
+    return NULL;
+}
+
+static int64_t ref_run(void *dot, void *dispatch, const int32_t *w, const int32_t *x, int32_t *y,
+                       int64_t rows, int64_t cols, int64_t n) {
+    if (rows <= 0) return 0;
+    int64_t ncpu = sysconf(_SC_NPROCESSORS_ONLN);
+    int64_t upper = rows < 256 ? rows : 256;
+    int64_t t = ncpu < upper ? ncpu : upper;
+    if (t < 1) t = 1;
+    int64_t band = (rows + t - 1) / t;
+    ref_band jobs[256];
+    int64_t used = 0;
+    for (int64_t i = 0; i < t; ++i) {
+        int64_t s = i * band, e = s + band;
+        if (e > rows) e = rows;
+        if (s >= e) break;
+        jobs[used++] = (ref_band){(ref_dot_fn)dot, w, x, y, cols, n, s, e};
+    }
+    ((ref_dispatch_fn)dispatch)(ref_band_worker, (char *)jobs, (long)sizeof(ref_band), (long)used);
+    return used;
+}
+
+BASELINE_EXPORT int64_t reference_gemv_q16_mt(void *dot, void *dispatch, const int32_t *w,
+                                              const int32_t *x, int32_t *y, int64_t rows, int64_t cols) {
+    return ref_run(dot, dispatch, w, x, y, rows, cols, 0);
+}
+
+BASELINE_EXPORT int64_t reference_gemm_q16_bt_mt(void *dot, void *dispatch, const int32_t *a,
+                                                 const int32_t *bt, int32_t *c, int64_t m, int64_t k,
+                                                 int64_t n) {
+    return ref_run(dot, dispatch, a, bt, c, m, k, n);
+}

@@ -148,3 +148,18 @@ def test_row_band_rule():
     assert O.row_bands(3, 8) == [(0, 1), (1, 2), (2, 3)]
     assert O.row_bands(1000, 1000)[-1][1] == 1000 and len(O.row_bands(1000, 1000)) <= 256
     assert O.row_bands(0, 4) == []
+
+
+@pytest.mark.skipif(O.ref_lib() is None, reason="the reference's C runtime was not built here")
+def test_reference_driven_baseline_matches_oracle():
+    """The timed Q16.16 CPU baseline (the reference's own dot + thread pool) gives the oracle's bytes."""
+    g = O.Lcg(77)
+    rows, cols = 301, 1030
+    w, x = g.q16(rows * cols), g.q16(cols)
+    y, used = O.reference_gemv_q16(w, x, rows, cols)
+    assert used >= 1 and np.array_equal(y, O.gemv_q16(w, x, rows, cols))
+    m, k, n = 37, 130, 75
+    a, b = g.q16(m * k, 0), g.q16(k * n, 0)
+    bt = np.ascontiguousarray(b.reshape(k, n).T).reshape(-1)
+    c, _ = O.reference_gemm_q16_bt(a, bt, m, k, n)
+    assert np.array_equal(c, O.gemm_q16(a, b, m, k, n))

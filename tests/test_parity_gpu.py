@@ -164,6 +164,31 @@ def test_gemm_q16_shapes(gpu, path):
             assert np.all(c[m * n :] == 0x5A5A5A5A)
 
 
+def test_random_shapes_all_kernels(gpu):
+    """Forty seeded random shapes per kernel family (ragged in every dimension), default paths."""
+    rng = np.random.default_rng(20260101)
+    for t in range(40):
+        m, k, n = (int(v) for v in rng.integers(1, 400, size=3))
+        if t % 5 == 0:
+            k = int(rng.integers(1, 40)) * 16       # aligned K: A is read in place
+        if t % 7 == 0:
+            n = int(rng.integers(1, 30)) * 16       # aligned N: B is read in place
+        g = O.Lcg(int(rng.integers(1, 2**62)))
+        a, b = g.i8(m * k), g.i8(k * n)
+        c = np.empty(m * n, dtype=np.int32)
+        gpu.matmul_mm_i8_v(a, b, c, m, k, n)
+        assert np.array_equal(c, O.gemm_i8(a, b, m, k, n)), ("i8", m, k, n)
+        a, b = g.i16(m * k), g.i16(k * n)
+        gpu.matmul_mm_i16(a, b, c, m, k, n)
+        assert np.array_equal(c, O.gemm_i16(a, b, m, k, n)), ("i16", m, k, n)
+        a, b = g.q16(m * k, 0), g.q16(k * n, 0)
+        gpu.matmul_mm_q16_v(a, b, c, m, k, n)
+        assert np.array_equal(c, O.gemm_q16(a, b, m, k, n)), ("q16", m, k, n)
+        y = np.empty(m, dtype=np.int32)
+        gpu.gemv_q16_mt(a, b[:k], y, m, k)
+        assert np.array_equal(y, O.gemv_q16(a, b[:k], m, k)), ("gemv", m, k)
+
+
 def test_q16_extreme_values(gpu):
     """INT_MIN / INT_MAX / -1 / 0x7FFF8000...: the hi/lo split must be exact everywhere."""
     specials = np.array([-2**31, 2**31 - 1, -1, 0, 1, 0x7FFF8000, 0x7FFF7FFF, -0x8000, 0x8000,
