@@ -11,6 +11,7 @@ namespace {
 std::mutex g_call_mutex;  // calls are serialised, like the reference's MT dispatch lock
 int g_gemm_path = 0;      // 0 = tensor cores, 1 = CUDA-core cross-check kernels
 bool g_force_transpose = false;  // tensor cores: always re-lay B out K-contiguous (testing)
+int g_q16_mode = 0;       // Q16.16 GEMM: 0 = pick by size, 6 = FP64-pipe kernel alone, 7 = tensor-core hybrid
 
 // One operand of a call: where the caller keeps it and where the kernels see it.
 struct Operand {
@@ -394,18 +395,44 @@ int64_t gemm_q16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t 
         MB200_CUDA(cudaMemsetAsync(call.dev<void>(ic), 0, (size_t)m * n * 4, ctx->stream));
     } else {
         const int32_t* db = call.dev<int32_t>(ib);
+        // one reservation for everything this call may put in scratch: the re-transposed B and
+        // the byte planes of the tensor-core hybrid
+        const int64_t kp = (int64_t)align_up((size_t)k, 16), np = (int64_t)align_up((size_t)n, 16);
+        const size_t a_plane = align_up((size_t)m * kp, 1024), b_plane = align_up((size_t)k * np, 1024);
+        const bool big = (double)m * (double)n * (double)k >= 268435456.0;
+        const bool may_hybrid = g_gemm_path != 1 && k % 4 == 0 && n % 4 == 0 &&
+                                (g_q16_mode == 7 || (g_q16_mode == 0 && big));
+        MB200_TRY(arena_reserve(ctx, ctx->scratch, (b_transposed ? align_up((size_t)k * n * 4, 1024) : 0) +
+                                                       (may_hybrid ? 4 * a_plane + 2 * b_plane : 0) + 16384));
         if (b_transposed) {
-            MB200_TRY(arena_reserve(ctx, ctx->scratch, (size_t)k * n * 4 + 2048));
             int32_t* bkn = static_cast<int32_t*>(arena_take(ctx->scratch, (size_t)k * n * 4));
             MB200_TRY(launch_transpose_i32(ctx, db, bkn, n, k));
             db = bkn;
         }
-        // Path 1 keeps the all-integer kernel (the cross-check); otherwise the three-pipe kernel
-        // runs whenever the operands allow 16-byte loads.
-        if (g_gemm_path != 1 && gemm_q16_fp64_usable(call.dev<int32_t>(ia), db, k, n))
-            MB200_TRY(launch_gemm_q16_fp64(ctx, call.dev<int32_t>(ia), db, call.dev<int32_t>(ic), m, k, n));
+        // Path 1 keeps the all-integer kernel (the cross-check).  Otherwise, when the operands
+        // allow 16-byte loads: large products split into a linear part a * (b >> 16) on the
+        // tensor cores (byte planes of a and of b >> 16, seven limb products) plus the floor part
+        // floor(a * (b & 0xffff) / 65536) on the FP64 pipe, added onto it; smaller ones run the
+        // single FP64-pipe kernel, where three extra launches would cost more than they save.
+        const int32_t* da = call.dev<int32_t>(ia);
+        int32_t* dc = call.dev<int32_t>(ic);
+        const bool fp64_ok = g_gemm_path != 1 && gemm_q16_fp64_usable(da, db, k, n);
+        const bool hybrid = fp64_ok && may_hybrid && reinterpret_cast<uintptr_t>(dc) % 16 == 0;
+        if (hybrid) {
+            uint8_t* ap[4];
+            uint8_t* bp[4] = {nullptr, nullptr, nullptr, nullptr};
+            for (int i = 0; i < 4; ++i) ap[i] = static_cast<uint8_t*>(arena_take(ctx->scratch, a_plane));
+            for (int i = 0; i < 2; ++i) bp[i] = static_cast<uint8_t*>(arena_take(ctx->scratch, b_plane));
+            MB200_TRY(launch_split_i32_bytes(ctx, da, ap, 0, m, k, kp));
+            MB200_TRY(launch_split_i32_bytes(ctx, db, bp, 1, k, n, np));
+            MB200_TRY(launch_gemm_q16_linear_tc(ctx, ap, bp, dc, m, n, k, kp, np));
+            MB200_TRY(launch_gemm_q16_floor_add(ctx, da, db, dc, m, k, n));
+            return call.end(true);
+        }
+        if (fp64_ok)
+            MB200_TRY(launch_gemm_q16_fp64(ctx, da, db, dc, m, k, n));
         else
-            MB200_TRY(launch_gemm_q16(ctx, call.dev<int32_t>(ia), db, call.dev<int32_t>(ic), m, k, n));
+            MB200_TRY(launch_gemm_q16(ctx, da, db, dc, m, k, n));
     }
     return call.end();
 }
@@ -533,13 +560,15 @@ int64_t mind_b200_set_gemm_path(int64_t path) {
     clear_error();
     std::lock_guard<std::mutex> lock(g_call_mutex);
     g_force_transpose = path == 4 || path == 5;
+    g_q16_mode = (path == 6 || path == 7) ? (int)path : 0;
     switch (path) {
+        case 6: case 7: g_gemm_path = 0; return set_pair_mode(0);  // Q16.16 GEMM kernel choice only
         case 0: g_gemm_path = 0; return set_pair_mode(0);  // tensor cores, kernel picked per call
         case 1: g_gemm_path = 1; return set_pair_mode(0);  // CUDA cores
         case 2: case 4: g_gemm_path = 0; return set_pair_mode(2);  // tensor cores, CTA pairs
         case 3: case 5: g_gemm_path = 0; return set_pair_mode(1);  // tensor cores, one CTA per tile
     }
-    return fail(MIND_B200_ERR_INVALID, "gemm path must be 0 (auto), 1 (CUDA cores), 2 / 3 (CTA pairs / single CTA) or 4 / 5 (the same with B transposed first)");
+    return fail(MIND_B200_ERR_INVALID, "gemm path must be 0 (auto), 1 (CUDA cores), 2 / 3 (CTA pairs / single CTA), 4 / 5 (the same with B transposed first) or 6 / 7 (Q16.16: FP64-pipe kernel alone / tensor-core hybrid)");
 }
 
 int64_t mind_b200_selftest_wait_timeout(int64_t limit_ms) {

@@ -103,6 +103,16 @@ int64_t launch_gemm_i16_tc_bmn(DeviceCtx* ctx, const int8_t* a_hi, const uint8_t
                                const int8_t* b_hi, const uint8_t* b_lo, int32_t* c, int64_t m,
                                int64_t n, int64_t k, int64_t kp_a, int64_t pitch_b);
 bool tc_pair_forced();
+// Q16.16 hybrid: byte planes of an int32 matrix (what = 0: all four bytes; 1: the two bytes
+// of element >> 16), and the tensor-core product of those planes (see gemm_tc.cu).
+int64_t launch_split_i32_bytes(DeviceCtx* ctx, const int32_t* src, uint8_t* const planes[4], int what,
+                               int64_t rows, int64_t cols, int64_t pitch);
+int64_t launch_gemm_q16_linear_tc(DeviceCtx* ctx, const uint8_t* const a_limb[4], const uint8_t* const bh_limb[2],
+                                  int32_t* p_out, int64_t m, int64_t n, int64_t k, int64_t kp_a,
+                                  int64_t pitch_b);
+// Floor part of the Q16.16 product on the FP64 pipe, added onto the linear part already in c.
+int64_t launch_gemm_q16_floor_add(DeviceCtx* ctx, const int32_t* a, const int32_t* b, int32_t* c, int64_t m,
+                                  int64_t k, int64_t n);
 int64_t launch_wait_selftest(DeviceCtx* ctx, int64_t limit_ms);
 // Re-layout kernels.
 int64_t launch_transpose_i8(DeviceCtx* ctx, const int8_t* b, int8_t* bt, int64_t k, int64_t n,

@@ -1,4 +1,5 @@
-// Q16.16 GEMM with the per-product floor on the FP64 pipe.
+// Q16.16 GEMM with the per-product floor on the FP64 pipe (alone, or as the floor half of the
+// tensor-core hybrid: see HYBRID below).
 //
 //   C[i,j] = (i32) sum_k ((i64)A[i,k] * (i64)B[k,j]) >> 16        (shift per product)
 //
@@ -42,19 +43,24 @@ __device__ __forceinline__ double fma_rm(double a, double b, double c) {
     return d;
 }
 __device__ __forceinline__ int32_t q16_hi_part(int32_t b) { return (b >> 16) + ((b >> 15) & 1); }
-__device__ __forceinline__ double q16_lo_scaled(int32_t b) {
-    return (double)(int32_t)(int16_t)(b & 0xffff) * (1.0 / 65536.0);  // exact: a power-of-two scale
+template <bool UNSIGNED_LOW>
+__device__ __forceinline__ double q16_lo_scaled(int32_t b) {  // exact: a power-of-two scale
+    return UNSIGNED_LOW ? (double)(b & 0xffff) * (1.0 / 65536.0)
+                        : (double)(int32_t)(int16_t)(b & 0xffff) * (1.0 / 65536.0);
 }
 
-template <int BM, int BN>
+// HYBRID: only the floor term sum_k floor(a * (b & 0xffff) / 65536) is computed here (with the
+// UNSIGNED low half, so that b >> 16 is the matching high part) and added onto the linear part
+// sum_k a * (b >> 16), which the tensor cores have already written to c.
+template <int BM, int BN, bool HYBRID>
 __global__ void __launch_bounds__(QTHREADS)
 gemm_q16_fp64_kernel(const int32_t* __restrict__ a, const int32_t* __restrict__ b, int32_t* __restrict__ c,
                      int m, int k, int n) {
     constexpr int TM = BM / 16, TN = BN / 16;
     static_assert(TM % 4 == 0 && TN % 4 == 0, "register tile is built from 4-wide groups");
-    __shared__ __align__(16) int32_t As[QBK][BM + 4];
+    __shared__ __align__(16) int32_t As[HYBRID ? 1 : QBK][BM + 4];
     __shared__ __align__(16) double Ad[QBK][BM + 2];  // A as binary64: converted once per element
-    __shared__ __align__(16) int32_t Bh[QBK][BN];
+    __shared__ __align__(16) int32_t Bh[HYBRID ? 1 : QBK][BN];
     __shared__ __align__(16) double2 Bd[QBK][BN / 2];  // [kk][(group * 2 + half) * 16 + tx]
 
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
@@ -82,7 +88,9 @@ gemm_q16_fp64_kernel(const int32_t* __restrict__ a, const int32_t* __restrict__ 
 #pragma unroll
         for (int i = 0; i < A_VEC; ++i) {
             const int r = (tid >> 2) + 64 * i, kq = (tid & 3) * 4;
-            As[kq][r] = ra[i].x; As[kq + 1][r] = ra[i].y; As[kq + 2][r] = ra[i].z; As[kq + 3][r] = ra[i].w;
+            if (!HYBRID) {
+                As[kq][r] = ra[i].x; As[kq + 1][r] = ra[i].y; As[kq + 2][r] = ra[i].z; As[kq + 3][r] = ra[i].w;
+            }
             Ad[kq][r] = __int2double_rn(ra[i].x); Ad[kq + 1][r] = __int2double_rn(ra[i].y);
             Ad[kq + 2][r] = __int2double_rn(ra[i].z); Ad[kq + 3][r] = __int2double_rn(ra[i].w);
         }
@@ -90,11 +98,14 @@ gemm_q16_fp64_kernel(const int32_t* __restrict__ a, const int32_t* __restrict__ 
         for (int i = 0; i < B_VEC; ++i) {
             const int e = tid + QTHREADS * i;
             const int kq = e / (BN / 4), cc = (e % (BN / 4)) * 4;
-            *reinterpret_cast<int4*>(&Bh[kq][cc]) =
-                make_int4(q16_hi_part(rb[i].x), q16_hi_part(rb[i].y), q16_hi_part(rb[i].z), q16_hi_part(rb[i].w));
+            if (!HYBRID)
+                *reinterpret_cast<int4*>(&Bh[kq][cc]) = make_int4(q16_hi_part(rb[i].x), q16_hi_part(rb[i].y),
+                                                                   q16_hi_part(rb[i].z), q16_hi_part(rb[i].w));
             const int g = cc / 64, t = (cc % 64) / 4;
-            Bd[kq][(g * 2) * 16 + t] = make_double2(q16_lo_scaled(rb[i].x), q16_lo_scaled(rb[i].y));
-            Bd[kq][(g * 2 + 1) * 16 + t] = make_double2(q16_lo_scaled(rb[i].z), q16_lo_scaled(rb[i].w));
+            Bd[kq][(g * 2) * 16 + t] =
+                make_double2(q16_lo_scaled<HYBRID>(rb[i].x), q16_lo_scaled<HYBRID>(rb[i].y));
+            Bd[kq][(g * 2 + 1) * 16 + t] =
+                make_double2(q16_lo_scaled<HYBRID>(rb[i].z), q16_lo_scaled<HYBRID>(rb[i].w));
         }
     };
 
@@ -128,10 +139,12 @@ gemm_q16_fp64_kernel(const int32_t* __restrict__ a, const int32_t* __restrict__ 
         for (int kk = 0; kk < QBK; ++kk) {
             int32_t av[TM], bh[TN];
             double ad[TM], bd[TN];
+            if (!HYBRID) {
 #pragma unroll
-            for (int g = 0; g < TM / 4; ++g) {
-                const int4 v = *reinterpret_cast<const int4*>(&As[kk][g * 64 + ty * 4]);
-                av[4 * g] = v.x; av[4 * g + 1] = v.y; av[4 * g + 2] = v.z; av[4 * g + 3] = v.w;
+                for (int g = 0; g < TM / 4; ++g) {
+                    const int4 v = *reinterpret_cast<const int4*>(&As[kk][g * 64 + ty * 4]);
+                    av[4 * g] = v.x; av[4 * g + 1] = v.y; av[4 * g + 2] = v.z; av[4 * g + 3] = v.w;
+                }
             }
 #pragma unroll
             for (int g = 0; g < TM / 4; ++g) {
@@ -141,8 +154,10 @@ gemm_q16_fp64_kernel(const int32_t* __restrict__ a, const int32_t* __restrict__ 
             }
 #pragma unroll
             for (int g = 0; g < TN / 4; ++g) {
-                const int4 v = *reinterpret_cast<const int4*>(&Bh[kk][g * 64 + tx * 4]);
-                bh[4 * g] = v.x; bh[4 * g + 1] = v.y; bh[4 * g + 2] = v.z; bh[4 * g + 3] = v.w;
+                if (!HYBRID) {
+                    const int4 v = *reinterpret_cast<const int4*>(&Bh[kk][g * 64 + tx * 4]);
+                    bh[4 * g] = v.x; bh[4 * g + 1] = v.y; bh[4 * g + 2] = v.z; bh[4 * g + 3] = v.w;
+                }
                 const double2 d0 = Bd[kk][(g * 2) * 16 + tx], d1 = Bd[kk][(g * 2 + 1) * 16 + tx];
                 bd[4 * g] = d0.x; bd[4 * g + 1] = d0.y; bd[4 * g + 2] = d1.x; bd[4 * g + 3] = d1.y;
             }
@@ -150,7 +165,7 @@ gemm_q16_fp64_kernel(const int32_t* __restrict__ a, const int32_t* __restrict__ 
             for (int i = 0; i < TM; ++i)
 #pragma unroll
                 for (int j = 0; j < TN; ++j) {
-                    acc[i][j] = mad_lo_u(av[i], bh[j], acc[i][j]);
+                    if (!HYBRID) acc[i][j] = mad_lo_u(av[i], bh[j], acc[i][j]);
                     facc[i][j] = fma_rm(ad[i], bd[j], facc[i][j]);
                 }
         }
@@ -170,24 +185,28 @@ gemm_q16_fp64_kernel(const int32_t* __restrict__ a, const int32_t* __restrict__ 
             const int cc = col0 + g * 64 + tx * 4;
             int32_t* dst = c + (size_t)r * n + cc;
             if (c_vec && cc + 3 < n) {
-                *reinterpret_cast<uint4*>(dst) =
-                    make_uint4(acc[i][4 * g], acc[i][4 * g + 1], acc[i][4 * g + 2], acc[i][4 * g + 3]);
+                uint4 o = make_uint4(acc[i][4 * g], acc[i][4 * g + 1], acc[i][4 * g + 2], acc[i][4 * g + 3]);
+                if (HYBRID) {
+                    const uint4 lin = *reinterpret_cast<const uint4*>(dst);
+                    o.x += lin.x; o.y += lin.y; o.z += lin.z; o.w += lin.w;
+                }
+                *reinterpret_cast<uint4*>(dst) = o;
             } else {
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                    if (cc + j < n) dst[j] = (int32_t)acc[i][4 * g + j];
+                    if (cc + j < n) dst[j] = (int32_t)(acc[i][4 * g + j] + (HYBRID ? (uint32_t)dst[j] : 0u));
             }
         }
     }
 }
 
-template <int BM, int BN>
+template <int BM, int BN, bool HYBRID>
 int64_t launch_fp64_cfg(DeviceCtx* ctx, const int32_t* a, const int32_t* b, int32_t* c, int64_t m,
                         int64_t k, int64_t n) {
     dim3 grid((unsigned)((n + BN - 1) / BN), (unsigned)((m + BM - 1) / BM));
     if (grid.y > 65535) return fail(MIND_B200_ERR_TOO_LARGE, "M too large for the CUDA-core GEMM grid");
     prof_begin(ctx);
-    gemm_q16_fp64_kernel<BM, BN><<<grid, QTHREADS, 0, ctx->stream>>>(a, b, c, (int)m, (int)k, (int)n);
+    gemm_q16_fp64_kernel<BM, BN, HYBRID><<<grid, QTHREADS, 0, ctx->stream>>>(a, b, c, (int)m, (int)k, (int)n);
     prof_end(ctx);
     count_launch();
     return check_launch("gemm_q16_fp64_kernel");
@@ -207,8 +226,16 @@ int64_t launch_gemm_q16_fp64(DeviceCtx* ctx, const int32_t* a, const int32_t* b,
     const int64_t sms = ctx->sm_count;
     auto tiles = [&](int bm, int bn) { return ((m + bm - 1) / bm) * ((n + bn - 1) / bn); };
     // 8 x 4 outputs per thread is the largest register tile that holds both accumulator sets.
-    if (tiles(128, 64) >= (sms * 3) / 4) return launch_fp64_cfg<128, 64>(ctx, a, b, c, m, k, n);
-    return launch_fp64_cfg<64, 64>(ctx, a, b, c, m, k, n);
+    if (tiles(128, 64) >= (sms * 3) / 4) return launch_fp64_cfg<128, 64, false>(ctx, a, b, c, m, k, n);
+    return launch_fp64_cfg<64, 64, false>(ctx, a, b, c, m, k, n);
+}
+
+int64_t launch_gemm_q16_floor_add(DeviceCtx* ctx, const int32_t* a, const int32_t* b, int32_t* c, int64_t m,
+                                  int64_t k, int64_t n) {
+    const int64_t sms = ctx->sm_count;
+    auto tiles = [&](int bm, int bn) { return ((m + bm - 1) / bm) * ((n + bn - 1) / bn); };
+    if (tiles(128, 64) >= (sms * 3) / 4) return launch_fp64_cfg<128, 64, true>(ctx, a, b, c, m, k, n);
+    return launch_fp64_cfg<64, 64, true>(ctx, a, b, c, m, k, n);
 }
 
 }  // namespace mb200

@@ -61,6 +61,11 @@ struct Cfg<1, 2> {
     static constexpr int BLOCK_N = 128, NA = 2, NB = 2, NACC = 3, ACC_STAGES = 1, STAGES = 4;
 };
 
+template <>
+struct Cfg<2, 1> {  // linear part of the Q16.16 product: a (4 limbs) x bh (2 limbs), 4 accumulators
+    static constexpr int BLOCK_N = 128, NA = 4, NB = 2, NACC = 4, ACC_STAGES = 1, STAGES = 2;
+};
+
 struct TcParams {
     int32_t* c;
     int m, n, k;
@@ -107,8 +112,10 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
 template <int MODE, int PAIR, bool BMN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
+               const __grid_constant__ CUtensorMap tm_a2, const __grid_constant__ CUtensorMap tm_a3,
                const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
                const TcParams p) {
+    static_assert(MODE != 2 || (PAIR == 1 && BMN), "the Q16.16 linear-part mode is single-CTA, B in place");
     using cfg = Cfg<MODE, PAIR>;
     constexpr int BLOCK_N = cfg::BLOCK_N;
     constexpr int B_ROWS = BLOCK_N / PAIR;  // columns of the output (rows of Bt) this CTA stages
@@ -150,7 +157,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
         fence_mbar_init();
         prefetch_tensormap(&tm_a0);
         prefetch_tensormap(&tm_b0);
-        if (cfg::NA == 2) prefetch_tensormap(&tm_a1);
+        if (cfg::NA >= 2) prefetch_tensormap(&tm_a1);
+        if (cfg::NA == 4) {
+            prefetch_tensormap(&tm_a2);
+            prefetch_tensormap(&tm_a3);
+        }
         if (cfg::NB == 2) prefetch_tensormap(&tm_b1);
     }
     if (warp == 1) {
@@ -194,7 +205,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                         const uint32_t bar = full0 + 8 * s;
                         mbar_arrive_expect_tx(bar, STAGE_BYTES);
                         tma_load_2d(dst, &tm_a0, bar, kx, row_a, pol_a);
-                        if (cfg::NA == 2) tma_load_2d(dst + A_TILE_BYTES, &tm_a1, bar, kx, row_a, pol_a);
+                        if (cfg::NA >= 2) tma_load_2d(dst + A_TILE_BYTES, &tm_a1, bar, kx, row_a, pol_a);
+                        if (cfg::NA == 4) {
+                            tma_load_2d(dst + 2 * A_TILE_BYTES, &tm_a2, bar, kx, row_a, pol_a);
+                            tma_load_2d(dst + 3 * A_TILE_BYTES, &tm_a3, bar, kx, row_a, pol_a);
+                        }
                         const uint32_t db = dst + cfg::NA * A_TILE_BYTES;
                         if (!BMN) {
                             tma_load_2d(db, &tm_b0, bar, kx, row_b, pol_b);
@@ -270,6 +285,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                         const uint64_t kb_off = (uint64_t)ks * B_KSTEP;
                         if (MODE == 0) {
                             mma_i8<PAIR>(d0, da0 + koff, db0 + kb_off, ID_SS, acc);
+                        } else if (MODE == 2) {
+                            // a = a3*2^24 + a2*2^16 + a1*2^8 + a0 (a3 signed), bh = bh1*256 + bh0 (bh1
+                            // signed); accumulator s collects the limb products of weight 2^(8s).
+                            const uint64_t a0d = da0 + koff;
+                            const uint64_t a1d = smem_desc_k_sw128(sa + A_TILE_BYTES) + koff;
+                            const uint64_t a2d = smem_desc_k_sw128(sa + 2 * A_TILE_BYTES) + koff;
+                            const uint64_t a3d = smem_desc_k_sw128(sa + 3 * A_TILE_BYTES) + koff;
+                            const uint64_t b0d = db0 + kb_off;
+                            const uint64_t b1d = smem_desc_mn_sw128(sb + B_TILE_BYTES, B_BOX_BYTES) + kb_off;
+                            mma_i8<PAIR>(d0, a0d, b0d, ID_UU, acc);                  // a0.bh0      -> s0
+                            mma_i8<PAIR>(d0 + BLOCK_N, a0d, b1d, ID_US, acc);        // a0.bh1      -> s1
+                            mma_i8<PAIR>(d0 + BLOCK_N, a1d, b0d, ID_UU, 1u);         // a1.bh0      -> s1
+                            mma_i8<PAIR>(d0 + 2 * BLOCK_N, a1d, b1d, ID_US, acc);    // a1.bh1      -> s2
+                            mma_i8<PAIR>(d0 + 2 * BLOCK_N, a2d, b0d, ID_UU, 1u);     // a2.bh0      -> s2
+                            mma_i8<PAIR>(d0 + 3 * BLOCK_N, a2d, b1d, ID_US, acc);    // a2.bh1      -> s3
+                            mma_i8<PAIR>(d0 + 3 * BLOCK_N, a3d, b0d, ID_SU, 1u);     // a3.bh0      -> s3
                         } else {
                             const uint64_t da1 = smem_desc_k_sw128(sa + A_TILE_BYTES) + koff;
                             const uint64_t db1 = (BMN ? smem_desc_mn_sw128(sb + B_TILE_BYTES, B_BOX_BYTES)
@@ -312,17 +343,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                 if (MODE == 0) {
                     tmem_ld32(t0 + c0, v);
                     tmem_ld_wait();
-                } else {
+                } else if (MODE == 2) {
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
-                        uint32_t hh[16], mid[16], ll[16];
-                        tmem_ld16(t0 + c0 + 16 * h, hh);
-                        tmem_ld16(t0 + BLOCK_N + c0 + 16 * h, mid);
-                        tmem_ld16(t0 + 2 * BLOCK_N + c0 + 16 * h, ll);
+                        uint32_t s0[16], s1[16], s2[16], s3[16];
+                        tmem_ld16(t0 + c0 + 16 * h, s0);
+                        tmem_ld16(t0 + BLOCK_N + c0 + 16 * h, s1);
+                        tmem_ld16(t0 + 2 * BLOCK_N + c0 + 16 * h, s2);
+                        tmem_ld16(t0 + 3 * BLOCK_N + c0 + 16 * h, s3);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) v[16 * h + j] = (hh[j] << 16) + (mid[j] << 8) + ll[j];
+                        for (int j = 0; j < 16; ++j)
+                            v[16 * h + j] = s0[j] + (s1[j] << 8) + (s2[j] << 16) + (s3[j] << 24);
                     }
+                } else {
+                    // all three accumulators' 32 columns in flight, one wait
+                    uint32_t mid[32], ll[32];
+                    tmem_ld32(t0 + c0, v);
+                    tmem_ld32(t0 + BLOCK_N + c0, mid);
+                    tmem_ld32(t0 + 2 * BLOCK_N + c0, ll);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = (v[j] << 16) + (mid[j] << 8) + ll[j];
                 }
                 if (row < p.m) {
                     const int col = col_tile + c0;
@@ -404,7 +446,8 @@ int g_pair_mode = 0;  // CTAs per tile: 1, 2 (cta_group::2 kernels), or 0 = pick
 // B[K][N] rows (BMN = true).
 template <int MODE, int PAIR, bool BMN>
 int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0, const void* b1,
-                  int32_t* c, int64_t m, int64_t n, int64_t k, int64_t kp_a, int64_t kp_b) {
+                  int32_t* c, int64_t m, int64_t n, int64_t k, int64_t kp_a, int64_t kp_b,
+                  const void* a2 = nullptr, const void* a3 = nullptr) {
     using cfg = Cfg<MODE, PAIR>;
     constexpr int B_ROWS = cfg::BLOCK_N / PAIR;
     constexpr int STAGE_BYTES = cfg::NA * A_TILE_BYTES + cfg::NB * B_ROWS * BLOCK_K;
@@ -420,7 +463,12 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
         MB200_TRY(make_tmap(&tb0, b0, k, n, kp_b, B_ROWS));
     ta1 = ta0;
     tb1 = tb0;
-    if (cfg::NA == 2) MB200_TRY(make_tmap(&ta1, a1, k, m, kp_a, BLOCK_M));
+    CUtensorMap ta2 = ta0, ta3 = ta0;
+    if (cfg::NA >= 2) MB200_TRY(make_tmap(&ta1, a1, k, m, kp_a, BLOCK_M));
+    if (cfg::NA == 4) {
+        MB200_TRY(make_tmap(&ta2, a2, k, m, kp_a, BLOCK_M));
+        MB200_TRY(make_tmap(&ta3, a3, k, m, kp_a, BLOCK_M));
+    }
     if (cfg::NB == 2) {
         if (BMN)
             MB200_TRY(make_tmap(&tb1, b1, n, k, kp_b, BLOCK_K));
@@ -484,7 +532,7 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
         }
     }
     prof_begin(ctx);
-    MB200_CUDA(cudaLaunchKernelEx(&lc, kern, ta0, ta1, tb0, tb1, p));
+    MB200_CUDA(cudaLaunchKernelEx(&lc, kern, ta0, ta1, ta2, ta3, tb0, tb1, p));
     prof_end(ctx);
     count_launch();
     return check_launch("gemm_tc_kernel");
@@ -526,6 +574,16 @@ int64_t launch_gemm_i8_tc_bmn(DeviceCtx* ctx, const int8_t* a, const int8_t* b, 
 }
 
 bool tc_pair_forced() { return g_pair_mode == 2; }
+
+// Linear part of the Q16.16 GEMM on tensor cores: P[i,j] = sum_k a[i,k] * bh[k,j] mod 2^32,
+// from the four byte planes of a (a_limb[0] lowest, a_limb[3] signed) and the two byte planes
+// of bh = b >> 16 (bh_limb[1] signed), B planes in B's own orientation ([K][pitch_b]).
+int64_t launch_gemm_q16_linear_tc(DeviceCtx* ctx, const uint8_t* const a_limb[4], const uint8_t* const bh_limb[2],
+                                  int32_t* p_out, int64_t m, int64_t n, int64_t k, int64_t kp_a,
+                                  int64_t pitch_b) {
+    return launch_tc<2, 1, true>(ctx, a_limb[0], a_limb[1], bh_limb[0], bh_limb[1], p_out, m, n, k, kp_a,
+                                 pitch_b, a_limb[2], a_limb[3]);
+}
 
 // One CTA per tile only: a pair would give each CTA 64 columns of B, half a swizzle atom.
 int64_t launch_gemm_i16_tc_bmn(DeviceCtx* ctx, const int8_t* a_hi, const uint8_t* a_lo,

@@ -119,7 +119,55 @@ __global__ void split_rows_i16_vec_kernel(const uint4* __restrict__ a, uint2* __
     }
 }
 
+// int32 matrix [rows][cols] -> byte planes [rows][pitch] (cols % 4 == 0, 16-byte aligned source).
+// WHAT = 0: the four bytes of each element (plane 3 holds the signed top byte);
+// WHAT = 1: the two bytes of (element >> 16), i.e. planes 0 / 1 = bytes 2 / 3 of the element.
+template <int WHAT>
+__global__ void split_i32_bytes_kernel(const int4* __restrict__ src, uint8_t* __restrict__ p0,
+                                       uint8_t* __restrict__ p1, uint8_t* __restrict__ p2,
+                                       uint8_t* __restrict__ p3, int64_t rows, int64_t cols4, int64_t pitch) {
+    const int64_t total = rows * cols4;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / cols4, c = (i - r * cols4) * 4;
+        const int4 v = src[i];
+        // byte b of the four elements, packed in element order
+        const uint32_t lo01 = __byte_perm(v.x, v.y, 0x5140), lo23 = __byte_perm(v.z, v.w, 0x5140);  // bytes 0,1
+        const uint32_t hi01 = __byte_perm(v.x, v.y, 0x7362), hi23 = __byte_perm(v.z, v.w, 0x7362);  // bytes 2,3
+        // lo01 = [x.b0, y.b0, x.b1, y.b1], lo23 = [z.b0, w.b0, z.b1, w.b1]; likewise hi* for bytes 2, 3
+        const uint32_t b0 = __byte_perm(lo01, lo23, 0x5410), b1 = __byte_perm(lo01, lo23, 0x7632);
+        const uint32_t b2 = __byte_perm(hi01, hi23, 0x5410), b3 = __byte_perm(hi01, hi23, 0x7632);
+        const int64_t o = r * pitch + c;
+        if (WHAT == 0) {
+            *reinterpret_cast<uint32_t*>(p0 + o) = b0;
+            *reinterpret_cast<uint32_t*>(p1 + o) = b1;
+            *reinterpret_cast<uint32_t*>(p2 + o) = b2;
+            *reinterpret_cast<uint32_t*>(p3 + o) = b3;
+        } else {
+            *reinterpret_cast<uint32_t*>(p0 + o) = b2;
+            *reinterpret_cast<uint32_t*>(p1 + o) = b3;
+        }
+    }
+}
+
 }  // namespace
+
+int64_t launch_split_i32_bytes(DeviceCtx* ctx, const int32_t* src, uint8_t* const planes[4], int what,
+                               int64_t rows, int64_t cols, int64_t pitch) {
+    const int64_t total = rows * (cols / 4);
+    if (total <= 0) return 0;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 64) blocks = 148 * 64;
+    const int4* s4 = reinterpret_cast<const int4*>(src);
+    if (what == 0)
+        split_i32_bytes_kernel<0><<<(unsigned)blocks, 256, 0, ctx->stream>>>(s4, planes[0], planes[1], planes[2],
+                                                                             planes[3], rows, cols / 4, pitch);
+    else
+        split_i32_bytes_kernel<1><<<(unsigned)blocks, 256, 0, ctx->stream>>>(s4, planes[0], planes[1], nullptr,
+                                                                             nullptr, rows, cols / 4, pitch);
+    count_launch();
+    return check_launch("split_i32_bytes_kernel");
+}
 
 int64_t launch_transpose_i8(DeviceCtx* ctx, const int8_t* b, int8_t* bt, int64_t k, int64_t n,
                             int64_t kp) {

@@ -150,7 +150,8 @@ def test_gemm_i16_shapes(gpu, path):
         assert np.all(c[m * n :] == 0x5A5A5A5A)
 
 
-@pytest.mark.parametrize("path", [0, 1])  # 0: FP64-pipe kernel where shapes allow; 1: all-integer kernel
+# 0: by size; 1: all-integer kernel; 6: FP64-pipe kernel alone; 7: tensor-core linear part + FP64 floor part
+@pytest.mark.parametrize("path", [0, 1, 6, 7])
 def test_gemm_q16_shapes(gpu, path):
     gpu.set_gemm_path(path)
     # the last shape crosses the 4096-step fold of the FP64 accumulators twice
