@@ -397,6 +397,29 @@ def run_mine(args, w):
     if not torch.equal(hc[: rows * n], c[: rows * n].cpu()):
         raise SystemExit(f"rank {rank}: host-pointer call and device-pointer call disagree")
 
+    # Optional: the rank-ordered all-gather of the C bands over NCCL (not part of `value`: the
+    # path needs no collective; reported so that "with the gather" can be read off too).
+    gather_ms = None
+    if world > 1 and args.gather and w["fn"] != "gemv_q16_mt":
+        from mind_b200.shard import all_gather_rows
+        band_rows = -(-m // world)
+        full = None
+        for _ in range(2):
+            full = all_gather_rows(c[: rows * n], m, n)
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record(stream)
+        for _ in range(5):
+            full = all_gather_rows(c[: rows * n], m, n)
+        g1.record(stream)
+        torch.cuda.synchronize()
+        t = torch.tensor([g0.elapsed_time(g1) / 5], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        gather_ms = float(t.item())
+        if not torch.equal(full[r0:r1].reshape(-1), c[: rows * n]):
+            raise SystemExit(f"rank {rank}: gathered C does not hold this rank's band")
+        del full
+
     if rank == 0:
         peaks, peak_src = measured_peaks()
         scale = unit_scale(w)
@@ -414,7 +437,9 @@ def run_mine(args, w):
             if w["fn"] == "matmul_mm_i16":
                 peak, peak_note = peak / 4.0, peak_note + " / 4 limb products"
         else:
-            peak, peak_note = None, "no measured INT32 multiply-add peak on this pool"
+            # not measured on this pool: derived from the FP64 pipe's issue rate, one fma per MAC
+            peak = 2.0 * 64 * 148 * 1.965e9 / scale
+            peak_note = "derived: 64 FP64 FMA / clock / SM x 148 SMs x 1.965 GHz, one FMA per MAC (no measured figure)"
         roofline = {"bound": w["bound"], "achieved": achieved, "peak": peak, "unit": w["unit"],
                     "frac": (achieved / peak) if achieved and peak else None,
                     "traffic": NCU_TRAFFIC.get(args.workload) if not args.size and world == 1 else None,
@@ -433,6 +458,9 @@ def run_mine(args, w):
                         "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": rows * n * 4,
                         "steps": e2e_steps},
                 "gpu_launches": launches, "clocks": clocks}
+        if gather_ms is not None:
+            line["all_gather_c"] = {"ms": gather_ms, "bytes_received_per_rank": m * n * 4,
+                                    "note": "NCCL all-gather of the C row bands, rank order; outside `value`"}
         if world == 1 and args.workload == "gemm_i8" and not args.size and not args.no_others:
             # the metric also names the Q16.16 GEMM, the GEMV and (by config) the int16 GEMM:
             # their device-resident numbers ride along (each has its own --workload run too)
@@ -459,6 +487,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-check", action="store_true", help="skip the oracle gate before timing")
     ap.add_argument("--no-others", action="store_true", help="skip the other configurations' ride-along numbers")
+    ap.add_argument("--gather", action="store_true", help="N > 1: also time the optional all-gather of C")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
