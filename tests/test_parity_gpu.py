@@ -227,6 +227,25 @@ def test_wrap_fixture_and_overflowing_i8(gpu):
         gpu.matmul_mm_i8_v(a, b, c, m, k, n)
         want = np.int64(16384) * k
         assert np.all(c.astype(np.int64) == ((want + 2**31) % 2**32) - 2**31)
+    # unsigned limb products overflow an accumulator too: int16 operands 255 (hi limb 0, lo limb
+    # 255) with K = 40000 put 65025 * 40000 > 2^31 into the lo.lo accumulator; same for the
+    # byte planes of the Q16.16 hybrid (a = 255, b = 255 << 16)
+    m, k, n = 128, 40000, 16
+    a16 = np.full(m * k, 255, dtype=np.int16)
+    b16 = np.full(k * n, 255, dtype=np.int16)
+    want = np.int64(65025) * k
+    for path in (3, 2):
+        gpu.set_gemm_path(path)
+        c = np.empty(m * n, dtype=np.int32)
+        gpu.matmul_mm_i16(a16, b16, c, m, k, n)
+        assert np.all(c.astype(np.int64) == ((want + 2**31) % 2**32) - 2**31)
+    gpu.set_gemm_path(7)
+    aq = np.full(m * k, 255, dtype=np.int32)
+    bq = np.full(k * n, 255 << 16, dtype=np.int32)
+    c = np.empty(m * n, dtype=np.int32)
+    gpu.matmul_mm_q16_v(aq, bq, c, m, k, n)
+    assert np.array_equal(c, O.gemm_q16(aq, bq, m, k, n))
+    assert np.all(c.astype(np.int64) == ((want + 2**31) % 2**32) - 2**31)
 
 
 @pytest.mark.parametrize("rows,cols", [(1, 1), (2, 3), (4, 4), (8, 16), (16, 9), (3, 65), (512, 130),
