@@ -24,9 +24,6 @@
 // Out-of-range rows / K tails are zero-filled by TMA; stores are predicated.
 // Every wait is bounded in time: when it runs out the kernel records a code in
 // the device error word, all roles leave their loops, and the kernel exits cleanly.
-#include <stdio.h>
-#include <stdlib.h>
-
 #include "common.h"
 #include "ptx.cuh"
 

@@ -19,25 +19,12 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
     return t;
 }
 
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "elect.sync _|p, 0xFFFFFFFF;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(pred));
-    return pred != 0;
-}
-
 // ------------------------------------------------------------------ mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
 __device__ __forceinline__ void fence_mbar_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() {
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -55,15 +42,6 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta) 
         "mapa.shared::cluster.u32 r, %0, %1;\n\t"
         "mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [r];\n\t}" ::"r"(bar),
         "r"(cta)
-        : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t bar, uint32_t bytes,
-                                                              uint32_t cta) {
-    asm volatile(
-        "{\n\t.reg .b32 r;\n\t"
-        "mapa.shared::cluster.u32 r, %0, %2;\n\t"
-        "mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [r], %1;\n\t}" ::"r"(bar),
-        "r"(bytes), "r"(cta)
         : "memory");
 }
 __device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t cta) {
