@@ -226,3 +226,31 @@ def test_runtime_mirror(gpu):
     for h in (ha, hb, hc):
         assert L.mind_b200_rt_deallocate(h) == 0
     assert L.mind_b200_rt_deallocate(ha) == mind_b200.ERR_INVALID
+
+
+def test_stability_reruns(gpu):
+    """The reference's multithreaded benches re-run each kernel 256 times into fresh buffers and
+    require identical bytes every time (benches/det_matmul_q16_mt.rs:88, :292-301)."""
+    n = 512
+    seed = 0xDEADBEEF00000000 ^ n
+    a = lcg_dev(gpu, n * n, 0, seed)
+    b = lcg_dev(gpu, n * n, 0, seed, offset=n * n)
+    want = torch.from_numpy(O.gemm_q16(a.cpu().numpy(), b.cpu().numpy(), n, n, n)).cuda()
+    for path in (0, 7, 1):  # single FP64-pipe kernel (this size), tensor-core hybrid, all-integer kernel
+        gpu.set_gemm_path(path)
+        for _ in range(256 if path != 1 else 32):
+            c = torch.empty(n * n, dtype=torch.int32, device="cuda")
+            gpu.matmul_mm_q16_mt_v(a, b, c, n, n, n)
+            assert torch.equal(c, want), path
+    gpu.set_gemm_path(0)
+    a8 = lcg_dev(gpu, 1024 * 1024, 1, seed)
+    b8 = lcg_dev(gpu, 1024 * 1024, 1, seed, offset=1024 * 1024)
+    first = None
+    for path in (3, 2):
+        gpu.set_gemm_path(path)
+        for _ in range(128):
+            c = torch.empty(1024 * 1024, dtype=torch.int32, device="cuda")
+            gpu.matmul_mm_i8_mt_v(a8, b8, c, 1024, 1024, 1024)
+            if first is None:
+                first = c
+            assert torch.equal(c, first), path
