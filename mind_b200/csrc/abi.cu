@@ -399,7 +399,7 @@ int64_t gemm_q16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t 
         // the byte planes of the tensor-core hybrid
         const int64_t kp = (int64_t)align_up((size_t)k, 16), np = (int64_t)align_up((size_t)n, 16);
         const size_t a_plane = align_up((size_t)m * kp, 1024), b_plane = align_up((size_t)k * np, 1024);
-        const bool big = (double)m * (double)n * (double)k >= 268435456.0;
+        const bool big = (double)m * (double)n * (double)k >= 536870912.0;  // measured cross-over: 768^3 .. 1024^3
         const bool may_hybrid = g_gemm_path != 1 && k % 4 == 0 && n % 4 == 0 &&
                                 (g_q16_mode == 7 || (g_q16_mode == 0 && big));
         MB200_TRY(arena_reserve(ctx, ctx->scratch, (b_transposed ? align_up((size_t)k * n * 4, 1024) : 0) +
@@ -413,7 +413,8 @@ int64_t gemm_q16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t 
         // allow 16-byte loads: large products split into a linear part a * (b >> 16) on the
         // tensor cores (byte planes of a and of b >> 16, seven limb products) plus the floor part
         // floor(a * (b & 0xffff) / 65536) on the FP64 pipe, added onto it; smaller ones run the
-        // single FP64-pipe kernel, where three extra launches would cost more than they save.
+        // single FP64-pipe kernel (both halves on the CUDA cores), where three extra launches
+        // would cost more than they save.
         const int32_t* da = call.dev<int32_t>(ia);
         int32_t* dc = call.dev<int32_t>(ic);
         const bool fp64_ok = g_gemm_path != 1 && gemm_q16_fp64_usable(da, db, k, n);

@@ -154,7 +154,7 @@ def test_gemm_i16_shapes(gpu, path):
 @pytest.mark.parametrize("path", [0, 1, 6, 7])
 def test_gemm_q16_shapes(gpu, path):
     gpu.set_gemm_path(path)
-    # the last shape crosses the 4096-step fold of the FP64 accumulators twice
+    # the last shape has a long K on a single output tile: many blocks add into the same outputs
     for (m, k, n) in GEMM_SHAPES + [(256, 64, 128), (1024, 1024, 64), (260, 132, 516), (70, 8200, 68)]:
         for shift in (12, 0):  # the reference's range, and full range (wrap past 2^31)
             g = O.Lcg(0xDEADBEEF00000000 ^ (m * 1000003 + k * 1009 + n + 2))
@@ -208,6 +208,26 @@ def test_q16_extreme_values(gpu):
         assert int(y[0]) == O.dot_q16(specials, x)
         assert gpu.dot_q16_v(specials, x, k) == O.dot_q16(specials, x)
         assert gpu.dot_l1_q16_v(specials, x, k) == O.dot_l1_q16(specials, x)
+
+
+def test_q16_floor_chain_range_and_long_k(gpu):
+    """The hybrid's floor kernel adds floor(a * (b & 0xffff) / 65536) to a binary64 chain that is
+    exact for 2^20 terms of either sign at full magnitude; longer K is cut into slices.  Drive
+    both ends of the range across one slice boundary: a = INT_MIN / INT_MAX with b & 0xffff =
+    0xffff for K = 2^20 + 48, several blocks sharing one output tile."""
+    m, n, k = 8, 4, (1 << 20) + 48
+    gpu.set_gemm_path(7)
+    try:
+        for aval in (-2**31, 2**31 - 1):
+            a = np.full(m * k, aval, dtype=np.int64).astype(np.int32)
+            a[:: 7] = 12345                                  # not all equal
+            b = np.full(k * n, 0xFFFF, dtype=np.int32)
+            b[:: 5] = -1                                     # b >> 16 = -1, low half 0xffff
+            c = np.empty(m * n, dtype=np.int32)
+            gpu.matmul_mm_q16_v(a, b, c, m, k, n)
+            assert np.array_equal(c, O.gemm_q16(a, b, m, k, n)), aval
+    finally:
+        gpu.set_gemm_path(0)
 
 
 def test_wrap_fixture_and_overflowing_i8(gpu):
