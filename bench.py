@@ -280,6 +280,75 @@ def quick_workload(name, blas, torch, stream, steps=30):
     return out
 
 
+def latency_workloads(blas, torch, stream):
+    """The launch-latency regime: benchmark configuration 1 (int8 256^3) and the reference's routing
+    shape (scores[11922] = catalog[11922 x 384] . query, benches/det_gemv_q16_mt.rs:56-58), device
+    resident.  Per call: back-to-back calls on one stream, and the same calls replayed from a CUDA
+    graph (32 per graph), which removes the host's launch cost."""
+    out = {}
+
+    def per_call_us(fn, reps):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
+
+    def graphed_us(fn, batch=32, reps=20):
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        try:
+            with torch.cuda.stream(side):
+                blas.set_stream(side.cuda_stream)
+                fn()
+                torch.cuda.synchronize()
+                with torch.cuda.graph(graph, stream=side):
+                    for _ in range(batch):
+                        fn()
+            blas.set_stream(stream.cuda_stream)
+            return per_call_us(graph.replay, reps) / batch
+        except RuntimeError as ex:  # reported in the line, does not end the bench
+            return f"capture failed: {str(ex)[:120]}"
+        finally:
+            blas.set_stream(stream.cuda_stream)
+
+    n = 256
+    seed = 0xDEADBEEF00000000 ^ n
+    a = torch.empty(n * n, dtype=torch.int8, device="cuda")
+    b = torch.empty(n * n, dtype=torch.int8, device="cuda")
+    c = torch.empty(n * n, dtype=torch.int32, device="cuda")
+    blas.lcg_fill(a, n * n, KIND_I8, seed, 0, 0)
+    blas.lcg_fill(b, n * n, KIND_I8, seed, n * n, 0)
+    call = lambda: blas.matmul_mm_i8_v(a, b, c, n, n, n)
+    us, gus = per_call_us(call, 200), graphed_us(call)
+    out["gemm_i8_256"] = {"workload": "gemm_i8 256x256x256", "us_per_call": us, "top_s": 2.0 * n ** 3 / us / 1e6,
+                          "us_per_call_cuda_graph": gus,
+                          "top_s_cuda_graph": 2.0 * n ** 3 / gus / 1e6 if isinstance(gus, float) else None,
+                          "note": "launch-latency regime: a roofline fraction is not meaningful"}
+
+    m, k, q = 11922, 384, 64
+    seed = 0xDEADBEEF00000000 ^ ((m << 20) ^ k)
+    w = torch.empty(m * k, dtype=torch.int32, device="cuda")
+    x = torch.empty(k * q, dtype=torch.int32, device="cuda")
+    y = torch.empty(m * q, dtype=torch.int32, device="cuda")
+    blas.lcg_fill(w, m * k, KIND_Q16, seed, 0, 15)
+    blas.lcg_fill(x, k * q, KIND_Q16, seed, m * k, 15)
+    call = lambda: blas.gemv_q16_mt(w, x, y, m, k)
+    us, gus = per_call_us(call, 200), graphed_us(call)
+    batched = per_call_us(lambda: blas.matmul_mm_q16_v(w, x, y, m, k, q), 50)
+    out["gemv_q16_routing"] = {"workload": f"gemv_q16 {m}x{k}", "us_per_call": us,
+                               "gb_s": (4.0 * m * k + 4 * k + 4 * m) / us / 1e3,
+                               "us_per_call_cuda_graph": gus,
+                               "batched_queries": {"queries": q, "as": f"gemm_q16 {m}x{k}x{q}", "us_per_call": batched,
+                                                   "us_per_query": batched / q}}
+    return out
+
+
 def run_mine(args, w):
     import torch
     import torch.distributed as dist
@@ -468,6 +537,7 @@ def run_mine(args, w):
             torch.cuda.empty_cache()
             line["other_workloads"] = {name: quick_workload(name, blas, torch, stream)
                                        for name in ("gemm_q16", "gemv_q16", "gemm_i16")}
+            line["other_workloads"].update(latency_workloads(blas, torch, stream))
         line["cpu_baseline"] = cpu_baseline(w) if world == 1 and not args.no_cpu else None
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -79,6 +79,19 @@ def self_generated() -> dict:
     g = O.Lcg(seed)
     w, x = g.q16(512 * 130), g.q16(130)
     out["gemv-q16-512x130"] = {"seed": seed, "sha256": O.canonical_hash_i32(O.gemv_q16(w, x, 512, 130))}
+    # the workload set the reference names but has not hashed yet (docs/rfcs/0020-mind-bench-
+    # reproducibility-harness.md:93-95: matmul-q16-32 / -256 / -1024, seed 0xDEADBEEF), generated
+    # like its committed gemm-q16-fused-64x64x64: A drawn before B, >> 12, B[K][N] used in place
+    for n in (32, 256, 1024):
+        seed = 0xDEADBEEF
+        g = O.Lcg(seed)
+        a, b = g.q16(n * n), g.q16(n * n)
+        if n <= 256:
+            c = O.gemm_q16(a, b, n, n, n)
+        else:
+            c, _ = O.baseline_gemm_q16(a, b, n, n, n)
+            assert np.array_equal(O.gemm_q16(a[: 8 * n], b, 8, n, n), c[: 8 * n])
+        out[f"matmul-q16-{n}"] = {"seed": seed, "shift": 12, "sha256": O.canonical_hash_i32(c)}
     return out
 
 

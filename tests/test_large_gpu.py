@@ -105,6 +105,24 @@ def test_config2_q16_1024(gpu):
     assert O.canonical_hash_i32(c.cpu().numpy()) == e["sha256"]
 
 
+def test_reproducibility_harness_workloads(gpu):
+    """matmul-q16-32 / -256 / -1024 (docs/rfcs/0020-mind-bench-reproducibility-harness.md:93-95):
+    every Q16.16 GEMM form reproduces the oracle's hash, host and device operands alike."""
+    for n in (32, 256, 1024):
+        e = SELF[f"matmul-q16-{n}"]
+        a = lcg_dev(gpu, n * n, 0, e["seed"], shift=e["shift"])
+        b = lcg_dev(gpu, n * n, 0, e["seed"], offset=n * n, shift=e["shift"])
+        for path in (0, 1, 6, 7):
+            gpu.set_gemm_path(path)
+            c = torch.empty(n * n, dtype=torch.int32, device="cuda")
+            gpu.matmul_mm_q16_mt_v(a, b, c, n, n, n)
+            assert O.canonical_hash_i32(c.cpu().numpy()) == e["sha256"], (n, path)
+        gpu.set_gemm_path(0)
+        ch = np.empty(n * n, dtype=np.int32)
+        gpu.matmul_mm_q16_v(a.cpu().numpy(), b.cpu().numpy(), ch, n, n, n)
+        assert O.canonical_hash_i32(ch) == e["sha256"], n
+
+
 def freivalds(gpu, a, b, c, m, k, n, elem_bytes, rounds=4):
     """Exact check in Z/2^32: C.v == A.(B.v) for random int32 vectors v."""
     gen = torch.Generator(device="cuda").manual_seed(1234)

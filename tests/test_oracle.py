@@ -127,6 +127,12 @@ def test_self_generated_fixtures():
     g = O.Lcg(e["seed"])
     w, x = g.q16(512 * 130), g.q16(130)
     assert O.canonical_hash_i32(O.gemv_q16(w, x, 512, 130)) == e["sha256"]
+    # the workload names of the reference's reproducibility harness (no hash committed upstream yet)
+    for n in (32, 256):
+        e = SELF[f"matmul-q16-{n}"]
+        g = O.Lcg(e["seed"])
+        a, b = g.q16(n * n, e["shift"]), g.q16(n * n, e["shift"])
+        assert O.canonical_hash_i32(O.gemm_q16(a, b, n, n, n)) == e["sha256"]
 
 
 @pytest.mark.parametrize("m,k,n,threads", [(1, 1, 1, 1), (37, 130, 75, 3), (130, 513, 129, 8), (5, 0, 7, 2)])
