@@ -1,5 +1,8 @@
 // extern "C" entry points of libmind_b200: argument checks, host / device pointer
 // classification, staging of host operands, operand re-layout, kernel dispatch.
+#include <stdlib.h>
+#include <stdio.h>
+#include <time.h>
 #include <mutex>
 #include <vector>
 
@@ -116,12 +119,12 @@ int64_t check_dims(int64_t m, int64_t k, int64_t n) {
 // With A and / or C in host memory a large GEMM is cut into row bands (independent, like
 // the reference's thread bands) and, when C goes back to the host, into column chunks, so
 // that uploads, products and downloads overlap: copies run on two side streams, the kernels
-// on the library's stream.  Upload order is B chunk 0, the A bands, then the other B chunks;
-// the first C tile is on its way back after one B chunk and one A band have arrived, and
-// from then on the download link stays busy.  C tiles are double-buffered in staging.
+// on the library's stream.  Uploads alternate between B chunks and A bands; the first C tile
+// is on its way back after one of each has arrived, and after about two rounds the download
+// link stays busy.  C tiles are double-buffered in staging.
 struct Pipe {
     cudaStream_t in = nullptr, out = nullptr;
-    cudaEvent_t start = nullptr, gemm_done[2] = {}, out_done[2] = {};
+    cudaEvent_t start = nullptr, gemm_done[4] = {}, out_done[4] = {};
     std::vector<cudaEvent_t> ready;  // uploads: A bands, then B chunks
     bool made = false;
 };
@@ -133,7 +136,7 @@ int64_t pipe_for(DeviceCtx* ctx, size_t n_ready, Pipe** out) {
         MB200_CUDA(cudaStreamCreateWithFlags(&p.in, cudaStreamNonBlocking));
         MB200_CUDA(cudaStreamCreateWithFlags(&p.out, cudaStreamNonBlocking));
         MB200_CUDA(cudaEventCreateWithFlags(&p.start, cudaEventDisableTiming));
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < 4; ++i) {
             MB200_CUDA(cudaEventCreateWithFlags(&p.gemm_done[i], cudaEventDisableTiming));
             MB200_CUDA(cudaEventCreateWithFlags(&p.out_done[i], cudaEventDisableTiming));
         }
@@ -173,7 +176,8 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
     const int64_t bands = (m + band - 1) / band;
     // Column chunks only pay when C is downloaded, and need B readable in place per chunk.
     const bool b_inplace_ok = !g_force_transpose && n % 16 == 0 && (b_host || reinterpret_cast<uintptr_t>(b) % 16 == 0);
-    const int64_t chunks = (c_host && b_inplace_ok && n >= 4096 && n % 64 == 0) ? 4 : 1;
+    static const int want8 = getenv("MB200_CHUNKS8") ? atoi(getenv("MB200_CHUNKS8")) : 0;
+    const int64_t chunks = !(c_host && b_inplace_ok && n >= 4096) ? 1 : (want8 && n >= 8192 && n % 128 == 0) ? 8 : (n % 64 == 0) ? 4 : 1;
     const int64_t nj = n / chunks;  // columns per chunk (a multiple of 16 when chunks > 1)
     Pipe* pp = nullptr;
     MB200_TRY(pipe_for(ctx, (size_t)(bands + chunks), &pp));
@@ -183,11 +187,12 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
     const size_t sb = b_host ? align_up((size_t)k * n, 1024) : 0;
     const size_t sa = a_host ? align_up((size_t)m * kp, 1024) : 0;
     const size_t sc = c_host ? align_up((size_t)band * nj * 4, 1024) : 0;
-    MB200_TRY(arena_reserve(ctx, ctx->staging, sb + sa + 2 * sc + 8192));
+    static const int nslot = getenv("MB200_SLOTS") ? atoi(getenv("MB200_SLOTS")) : 2;
+    MB200_TRY(arena_reserve(ctx, ctx->staging, sb + sa + nslot * sc + 8192));
     int8_t* b_stage = b_host ? static_cast<int8_t*>(arena_take(ctx->staging, sb)) : nullptr;
     int8_t* a_stage = a_host ? static_cast<int8_t*>(arena_take(ctx->staging, sa)) : nullptr;
-    int32_t* c_slot[2] = {nullptr, nullptr};
-    for (int s = 0; s < 2; ++s)
+    int32_t* c_slot[4] = {nullptr, nullptr, nullptr, nullptr};
+    for (int s = 0; s < nslot; ++s)
         if (c_host) c_slot[s] = static_cast<int32_t*>(arena_take(ctx->staging, sc));
 
     // B as the kernels will see it: chunk j is dense [k][nj] in staging (host B), or a column
@@ -206,19 +211,46 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
     MB200_CUDA(cudaStreamWaitEvent(P.in, P.start, 0));
     MB200_CUDA(cudaStreamWaitEvent(P.out, P.start, 0));
 
-    // ---- uploads, all queued now on the in-stream in the order the products need them
-    auto upload_b = [&](int64_t j) -> int64_t {
-        if (chunks == 1)
-            MB200_CUDA(cudaMemcpyAsync(b_stage, b, (size_t)k * n, cudaMemcpyHostToDevice, P.in));
-        else
-            MB200_CUDA(cudaMemcpy2DAsync(b_stage + (size_t)j * k * nj, (size_t)nj, b + (size_t)j * nj, (size_t)n,
-                                         (size_t)nj, (size_t)k, cudaMemcpyHostToDevice, P.in));
-        MB200_CUDA(cudaEventRecord(P.ready[bands + j], P.in));
-        return 0;
-    };
-    if (b_host) MB200_TRY(upload_b(0));
-    if (a_host)
-        for (int64_t i = 0; i < bands; ++i) {
+    // ---- the order of work.  A tile (band i, chunk j) can be multiplied once A band i and B
+    // chunk j are on the device.  Uploads alternate between the two operands so that the set of
+    // finished uploads grows as a square (t bands and t chunks give t^2 tiles: the download link
+    // is fed after about two rounds, instead of after all of A as with "every band, then the
+    // next chunk"); operands that are already on the device count as uploaded from the start.
+    struct Step { bool is_a; int64_t idx; };
+    std::vector<Step> uploads;
+    std::vector<std::pair<int64_t, int64_t>> tiles;  // (band, chunk) in the order they become possible
+    {
+        int64_t ia = a_host ? 0 : bands, jb = b_host ? 0 : chunks;
+        for (int64_t j = 0; j < jb; ++j)
+            for (int64_t i = 0; i < ia; ++i) tiles.emplace_back(i, j);
+        while (ia < bands || jb < chunks) {
+            // B first (no product needs only A), then whichever operand is behind in proportion
+            static const int old_order = getenv("MB200_ORDER") ? atoi(getenv("MB200_ORDER")) : 0;
+            const bool take_b = jb < chunks && (ia == bands || jb == 0 || (!old_order && jb * bands < ia * chunks));
+            if (take_b) {
+                uploads.push_back({false, jb});
+                for (int64_t i = 0; i < ia; ++i) tiles.emplace_back(i, jb);
+                ++jb;
+            } else {
+                uploads.push_back({true, ia});
+                for (int64_t j = 0; j < jb; ++j) tiles.emplace_back(ia, j);
+                ++ia;
+            }
+        }
+    }
+
+    // ---- uploads, all queued now on the in-stream in that order
+    for (const Step& u : uploads) {
+        if (!u.is_a) {
+            const int64_t j = u.idx;
+            if (chunks == 1)
+                MB200_CUDA(cudaMemcpyAsync(b_stage, b, (size_t)k * n, cudaMemcpyHostToDevice, P.in));
+            else
+                MB200_CUDA(cudaMemcpy2DAsync(b_stage + (size_t)j * k * nj, (size_t)nj, b + (size_t)j * nj, (size_t)n,
+                                             (size_t)nj, (size_t)k, cudaMemcpyHostToDevice, P.in));
+            MB200_CUDA(cudaEventRecord(P.ready[bands + j], P.in));
+        } else {
+            const int64_t i = u.idx;
             const int64_t r0 = i * band, rows = (m - r0 < band) ? m - r0 : band;
             int8_t* dst = a_stage + (size_t)r0 * kp;
             const int8_t* src = a + (size_t)r0 * k;
@@ -229,8 +261,7 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
                                              cudaMemcpyHostToDevice, P.in));
             MB200_CUDA(cudaEventRecord(P.ready[i], P.in));
         }
-    if (b_host)
-        for (int64_t j = 1; j < chunks; ++j) MB200_TRY(upload_b(j));
+    }
 
     // ---- one-off re-layouts on the library's stream
     int8_t* bt = nullptr;
@@ -249,36 +280,65 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
     }
 
     // ---- products and downloads
+    static const int trace = getenv("MB200_TRACE") ? 1 : 0;
+    double tw = 0, tg = 0, tc = 0;
+    std::vector<cudaEvent_t> trace_ev;
+    auto now = []() { timespec ts; clock_gettime(CLOCK_MONOTONIC, &ts); return ts.tv_sec * 1e3 + ts.tv_nsec * 1e-6; };
     int64_t t = 0;  // running C tile count: picks the staging slot
-    for (int64_t j = 0; j < chunks; ++j) {
-        if (b_host && b_direct) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.ready[bands + j], 0));
-        for (int64_t i = 0; i < bands; ++i, ++t) {
-            const int s = (int)(t & 1);
-            const int64_t r0 = i * band, rows = (m - r0 < band) ? m - r0 : band;
-            if (a_host && j == 0) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.ready[i], 0));
-            if (c_host && t >= 2) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.out_done[s], 0));  // slot free
-            int32_t* c_tile = c_host ? c_slot[s] : c + (size_t)r0 * n;
-            const int8_t* a_band = a_dev + (size_t)r0 * a_pitch;
-            if (b_direct)
-                MB200_TRY(launch_gemm_i8_tc_bmn(ctx, a_band, b_chunk(j), c_tile, rows, nj, k, a_pitch, b_pitch));
-            else
-                MB200_TRY(launch_gemm_i8_tc(ctx, a_band, bt, c_tile, rows, n, k, a_pitch, kp));
-            if (c_host) {
-                MB200_CUDA(cudaEventRecord(P.gemm_done[s], ctx->stream));
-                MB200_CUDA(cudaStreamWaitEvent(P.out, P.gemm_done[s], 0));
-                int32_t* dst = c + (size_t)r0 * n + (size_t)j * nj;
-                if (chunks == 1)
-                    MB200_CUDA(cudaMemcpyAsync(dst, c_slot[s], (size_t)rows * n * 4, cudaMemcpyDeviceToHost, P.out));
-                else
-                    MB200_CUDA(cudaMemcpy2DAsync(dst, (size_t)n * 4, c_slot[s], (size_t)nj * 4, (size_t)nj * 4,
-                                                 (size_t)rows, cudaMemcpyDeviceToHost, P.out));
-                MB200_CUDA(cudaEventRecord(P.out_done[s], P.out));
-            }
+    std::vector<char> a_waited((size_t)bands, 0), b_waited((size_t)chunks, 0);
+    for (const auto& ij : tiles) {
+        const int64_t i = ij.first, j = ij.second;
+        const int s = (int)(t % nslot);
+        const int64_t r0 = i * band, rows = (m - r0 < band) ? m - r0 : band;
+        const double t0 = now();
+        if (b_host && b_direct && !b_waited[j]) {
+            MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.ready[bands + j], 0));
+            b_waited[j] = 1;
         }
+        if (a_host && !a_waited[i]) {
+            MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.ready[i], 0));
+            a_waited[i] = 1;
+        }
+        if (c_host && t >= nslot) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.out_done[s], 0));  // slot free
+        int32_t* c_tile = c_host ? c_slot[s] : c + (size_t)r0 * n;  // a device C is never cut into chunks
+        const int8_t* a_band = a_dev + (size_t)r0 * a_pitch;
+        const double t1 = now();
+        if (b_direct)
+            MB200_TRY(launch_gemm_i8_tc_bmn(ctx, a_band, b_chunk(j), c_tile, rows, nj, k, a_pitch, b_pitch));
+        else
+            MB200_TRY(launch_gemm_i8_tc(ctx, a_band, bt, c_tile, rows, n, k, a_pitch, kp));
+        const double t2 = now();
+        tw += t1 - t0; tg += t2 - t1;
+        if (c_host) {
+            MB200_CUDA(cudaEventRecord(P.gemm_done[s], ctx->stream));
+            MB200_CUDA(cudaStreamWaitEvent(P.out, P.gemm_done[s], 0));
+            int32_t* dst = c + (size_t)r0 * n + (size_t)j * nj;
+            cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+            if (trace) { cudaEventCreate(&ev0); cudaEventCreate(&ev1); cudaEventRecord(ev0, P.out); }
+            if (chunks == 1)
+                MB200_CUDA(cudaMemcpyAsync(dst, c_slot[s], (size_t)rows * n * 4, cudaMemcpyDeviceToHost, P.out));
+            else
+                MB200_CUDA(cudaMemcpy2DAsync(dst, (size_t)n * 4, c_slot[s], (size_t)nj * 4, (size_t)nj * 4,
+                                             (size_t)rows, cudaMemcpyDeviceToHost, P.out));
+            if (trace) { cudaEventRecord(ev1, P.out); trace_ev.push_back(ev0); trace_ev.push_back(ev1); }
+            MB200_CUDA(cudaEventRecord(P.out_done[s], P.out));
+        }
+        tc += now() - t2;
+        ++t;
     }
+    if (trace) fprintf(stderr, "pipeline host ms: waits %.3f, gemm launches %.3f, download enqueue %.3f over %lld tiles\n", tw, tg, tc, (long long)t);
     if (c_host)
-        for (int s = 0; s < 2 && s < t; ++s) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.out_done[s], 0));
+        for (int s = 0; s < nslot && s < t; ++s) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.out_done[s], 0));
     MB200_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (trace && trace_ev.size() >= 4) {
+        float copy = 0, span = 0, gap = 0, x = 0;
+        for (size_t q = 0; q + 1 < trace_ev.size(); q += 2) { cudaEventElapsedTime(&x, trace_ev[q], trace_ev[q + 1]); copy += x; }
+        for (size_t q = 1; q + 1 < trace_ev.size(); q += 2) { cudaEventElapsedTime(&x, trace_ev[q], trace_ev[q + 1]); gap += x; }
+        cudaEventElapsedTime(&span, trace_ev.front(), trace_ev.back());
+        fprintf(stderr, "downloads: %zu copies, %.3f ms each, gaps %.3f ms each, span %.2f ms\n", trace_ev.size() / 2,
+                copy / (trace_ev.size() / 2), gap / (trace_ev.size() / 2 - 1), span);
+        for (cudaEvent_t e : trace_ev) cudaEventDestroy(e);
+    }
     return Call::check_err_word(ctx);
 }
 

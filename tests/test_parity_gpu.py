@@ -118,9 +118,9 @@ def test_gemm_i8_host_operand_pipeline(gpu, path):
     in overlap.  Ragged last band, K % 16 != 0 (padded on upload), N % 16 != 0."""
     import torch
     gpu.set_gemm_path(path)
-    # the last two shapes also split N into column chunks on the way back to the host
+    # the last four shapes also split N into 4 / 8 column chunks on the way back to the host
     for (m, k, n) in [(1024, 64, 48), (2500, 100, 36), (1300, 256, 512), (4097, 33, 257), (8192, 512, 128),
-                      (1024, 64, 4096), (1100, 48, 4160)]:
+                      (1024, 64, 4096), (1100, 48, 4160), (1024, 32, 8192), (1030, 16, 8320)]:
         g = O.Lcg(0xDEADBEEF00000000 ^ (m * 7 + k * 3 + n))
         a, b = g.i8(m * k), g.i8(k * n)
         want = O.gemm_i8(a, b, m, k, n)
