@@ -1,8 +1,5 @@
 // extern "C" entry points of libmind_b200: argument checks, host / device pointer
 // classification, staging of host operands, operand re-layout, kernel dispatch.
-#include <stdlib.h>
-#include <stdio.h>
-#include <time.h>
 #include <mutex>
 #include <vector>
 
@@ -124,7 +121,7 @@ int64_t check_dims(int64_t m, int64_t k, int64_t n) {
 // link stays busy.  C tiles are double-buffered in staging.
 struct Pipe {
     cudaStream_t in = nullptr, out = nullptr;
-    cudaEvent_t start = nullptr, gemm_done[4] = {}, out_done[4] = {};
+    cudaEvent_t start = nullptr, gemm_done[2] = {}, out_done[2] = {};
     std::vector<cudaEvent_t> ready;  // uploads: A bands, then B chunks
     bool made = false;
 };
@@ -136,7 +133,7 @@ int64_t pipe_for(DeviceCtx* ctx, size_t n_ready, Pipe** out) {
         MB200_CUDA(cudaStreamCreateWithFlags(&p.in, cudaStreamNonBlocking));
         MB200_CUDA(cudaStreamCreateWithFlags(&p.out, cudaStreamNonBlocking));
         MB200_CUDA(cudaEventCreateWithFlags(&p.start, cudaEventDisableTiming));
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < 2; ++i) {
             MB200_CUDA(cudaEventCreateWithFlags(&p.gemm_done[i], cudaEventDisableTiming));
             MB200_CUDA(cudaEventCreateWithFlags(&p.out_done[i], cudaEventDisableTiming));
         }
@@ -176,8 +173,9 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
     const int64_t bands = (m + band - 1) / band;
     // Column chunks only pay when C is downloaded, and need B readable in place per chunk.
     const bool b_inplace_ok = !g_force_transpose && n % 16 == 0 && (b_host || reinterpret_cast<uintptr_t>(b) % 16 == 0);
-    static const int want8 = getenv("MB200_CHUNKS8") ? atoi(getenv("MB200_CHUNKS8")) : 0;
-    const int64_t chunks = !(c_host && b_inplace_ok && n >= 4096) ? 1 : (want8 && n >= 8192 && n % 128 == 0) ? 8 : (n % 64 == 0) ? 4 : 1;
+    // Four, not more: a strided download slows down beside running kernels as its rows get shorter
+    // (measured with a GEMM on another stream: 57 GB/s for 64 KiB rows, 48 for 16 KiB, 31 for 8 KiB).
+    const int64_t chunks = (c_host && b_inplace_ok && n >= 4096 && n % 64 == 0) ? 4 : 1;
     const int64_t nj = n / chunks;  // columns per chunk (a multiple of 16 when chunks > 1)
     Pipe* pp = nullptr;
     MB200_TRY(pipe_for(ctx, (size_t)(bands + chunks), &pp));
@@ -187,11 +185,11 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
     const size_t sb = b_host ? align_up((size_t)k * n, 1024) : 0;
     const size_t sa = a_host ? align_up((size_t)m * kp, 1024) : 0;
     const size_t sc = c_host ? align_up((size_t)band * nj * 4, 1024) : 0;
-    static const int nslot = getenv("MB200_SLOTS") ? atoi(getenv("MB200_SLOTS")) : 2;
+    constexpr int nslot = 2;
     MB200_TRY(arena_reserve(ctx, ctx->staging, sb + sa + nslot * sc + 8192));
     int8_t* b_stage = b_host ? static_cast<int8_t*>(arena_take(ctx->staging, sb)) : nullptr;
     int8_t* a_stage = a_host ? static_cast<int8_t*>(arena_take(ctx->staging, sa)) : nullptr;
-    int32_t* c_slot[4] = {nullptr, nullptr, nullptr, nullptr};
+    int32_t* c_slot[nslot] = {nullptr, nullptr};
     for (int s = 0; s < nslot; ++s)
         if (c_host) c_slot[s] = static_cast<int32_t*>(arena_take(ctx->staging, sc));
 
@@ -225,8 +223,7 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
             for (int64_t i = 0; i < ia; ++i) tiles.emplace_back(i, j);
         while (ia < bands || jb < chunks) {
             // B first (no product needs only A), then whichever operand is behind in proportion
-            static const int old_order = getenv("MB200_ORDER") ? atoi(getenv("MB200_ORDER")) : 0;
-            const bool take_b = jb < chunks && (ia == bands || jb == 0 || (!old_order && jb * bands < ia * chunks));
+            const bool take_b = jb < chunks && (ia == bands || jb == 0 || jb * bands < ia * chunks);
             if (take_b) {
                 uploads.push_back({false, jb});
                 for (int64_t i = 0; i < ia; ++i) tiles.emplace_back(i, jb);
@@ -280,17 +277,12 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
     }
 
     // ---- products and downloads
-    static const int trace = getenv("MB200_TRACE") ? 1 : 0;
-    double tw = 0, tg = 0, tc = 0;
-    std::vector<cudaEvent_t> trace_ev;
-    auto now = []() { timespec ts; clock_gettime(CLOCK_MONOTONIC, &ts); return ts.tv_sec * 1e3 + ts.tv_nsec * 1e-6; };
     int64_t t = 0;  // running C tile count: picks the staging slot
     std::vector<char> a_waited((size_t)bands, 0), b_waited((size_t)chunks, 0);
     for (const auto& ij : tiles) {
         const int64_t i = ij.first, j = ij.second;
         const int s = (int)(t % nslot);
         const int64_t r0 = i * band, rows = (m - r0 < band) ? m - r0 : band;
-        const double t0 = now();
         if (b_host && b_direct && !b_waited[j]) {
             MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.ready[bands + j], 0));
             b_waited[j] = 1;
@@ -302,43 +294,26 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
         if (c_host && t >= nslot) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.out_done[s], 0));  // slot free
         int32_t* c_tile = c_host ? c_slot[s] : c + (size_t)r0 * n;  // a device C is never cut into chunks
         const int8_t* a_band = a_dev + (size_t)r0 * a_pitch;
-        const double t1 = now();
         if (b_direct)
             MB200_TRY(launch_gemm_i8_tc_bmn(ctx, a_band, b_chunk(j), c_tile, rows, nj, k, a_pitch, b_pitch));
         else
             MB200_TRY(launch_gemm_i8_tc(ctx, a_band, bt, c_tile, rows, n, k, a_pitch, kp));
-        const double t2 = now();
-        tw += t1 - t0; tg += t2 - t1;
         if (c_host) {
             MB200_CUDA(cudaEventRecord(P.gemm_done[s], ctx->stream));
             MB200_CUDA(cudaStreamWaitEvent(P.out, P.gemm_done[s], 0));
             int32_t* dst = c + (size_t)r0 * n + (size_t)j * nj;
-            cudaEvent_t ev0 = nullptr, ev1 = nullptr;
-            if (trace) { cudaEventCreate(&ev0); cudaEventCreate(&ev1); cudaEventRecord(ev0, P.out); }
             if (chunks == 1)
                 MB200_CUDA(cudaMemcpyAsync(dst, c_slot[s], (size_t)rows * n * 4, cudaMemcpyDeviceToHost, P.out));
             else
                 MB200_CUDA(cudaMemcpy2DAsync(dst, (size_t)n * 4, c_slot[s], (size_t)nj * 4, (size_t)nj * 4,
                                              (size_t)rows, cudaMemcpyDeviceToHost, P.out));
-            if (trace) { cudaEventRecord(ev1, P.out); trace_ev.push_back(ev0); trace_ev.push_back(ev1); }
             MB200_CUDA(cudaEventRecord(P.out_done[s], P.out));
         }
-        tc += now() - t2;
         ++t;
     }
-    if (trace) fprintf(stderr, "pipeline host ms: waits %.3f, gemm launches %.3f, download enqueue %.3f over %lld tiles\n", tw, tg, tc, (long long)t);
     if (c_host)
         for (int s = 0; s < nslot && s < t; ++s) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.out_done[s], 0));
     MB200_CUDA(cudaStreamSynchronize(ctx->stream));
-    if (trace && trace_ev.size() >= 4) {
-        float copy = 0, span = 0, gap = 0, x = 0;
-        for (size_t q = 0; q + 1 < trace_ev.size(); q += 2) { cudaEventElapsedTime(&x, trace_ev[q], trace_ev[q + 1]); copy += x; }
-        for (size_t q = 1; q + 1 < trace_ev.size(); q += 2) { cudaEventElapsedTime(&x, trace_ev[q], trace_ev[q + 1]); gap += x; }
-        cudaEventElapsedTime(&span, trace_ev.front(), trace_ev.back());
-        fprintf(stderr, "downloads: %zu copies, %.3f ms each, gaps %.3f ms each, span %.2f ms\n", trace_ev.size() / 2,
-                copy / (trace_ev.size() / 2), gap / (trace_ev.size() / 2 - 1), span);
-        for (cudaEvent_t e : trace_ev) cudaEventDestroy(e);
-    }
     return Call::check_err_word(ctx);
 }
 
