@@ -389,23 +389,33 @@ int64_t gemm_i16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t 
     } else {
         const int64_t kp = (int64_t)align_up((size_t)k, 16);
         const int64_t np = (int64_t)align_up((size_t)n, 16);
-        // B's limb planes keep B's own orientation ([K][np], N contiguous) unless the CTA-pair
-        // kernel is forced, whose B tiles must be K-contiguous.
+        // B's limb planes keep B's own orientation ([K][np], N contiguous) unless a transposed B
+        // is asked for (paths 4 / 5, and 2: the int16 kernel has no CTA-pair form).
         const bool b_transposed = g_force_transpose || tc_pair_forced();
         const size_t a_plane = align_up((size_t)m * kp, 1024);
         const size_t b_plane = align_up(b_transposed ? (size_t)n * kp : (size_t)k * np, 1024);
-        MB200_TRY(arena_reserve(ctx, ctx->scratch, 2 * a_plane + 2 * b_plane + 4096));
+        const size_t sums = align_up((size_t)m * 4, 1024);
+        MB200_TRY(arena_reserve(ctx, ctx->scratch, 2 * a_plane + 2 * b_plane + sums + 5120));
         int8_t* a_hi = static_cast<int8_t*>(arena_take(ctx->scratch, a_plane));
         uint8_t* a_lo = static_cast<uint8_t*>(arena_take(ctx->scratch, a_plane));
         int8_t* b_hi = static_cast<int8_t*>(arena_take(ctx->scratch, b_plane));
         uint8_t* b_lo = static_cast<uint8_t*>(arena_take(ctx->scratch, b_plane));
-        MB200_TRY(launch_split_rows_i16(ctx, call.dev<int16_t>(ia), a_hi, a_lo, m, k, kp));
+        // a = 256 * a_hi + a_lo (a_lo unsigned); b = 256 * b_hi + (b_lo' + 128) with b_lo' signed, so
+        // that B's two planes share a signedness and one MMA takes both; 128 * sum_k a[i][k] goes
+        // back in the epilogue.
+        int32_t* a_sums = static_cast<int32_t*>(arena_take(ctx->scratch, sums));
         if (b_transposed) {
+            MB200_TRY(launch_split_rows_i16(ctx, call.dev<int16_t>(ia), a_hi, a_lo, m, k, kp, false, a_sums, false,
+                                            nullptr, 0));
             MB200_TRY(launch_split_transpose_i16(ctx, call.dev<int16_t>(ib), b_hi, b_lo, k, n, kp));
-            MB200_TRY(launch_gemm_i16_tc(ctx, a_hi, a_lo, b_hi, b_lo, call.dev<int32_t>(ic), m, n, k, kp));
+            MB200_TRY(launch_gemm_i16_tc(ctx, a_hi, a_lo, b_hi, b_lo, a_sums, call.dev<int32_t>(ic), m, n, k, kp));
         } else {
-            MB200_TRY(launch_split_rows_i16(ctx, call.dev<int16_t>(ib), b_hi, b_lo, k, n, np));
-            MB200_TRY(launch_gemm_i16_tc_bmn(ctx, a_hi, a_lo, b_hi, b_lo, call.dev<int32_t>(ic), m, n, k, kp, np));
+            // B first: its launch also clears the row sums that A's launch then adds into
+            MB200_TRY(launch_split_rows_i16(ctx, call.dev<int16_t>(ib), b_hi, b_lo, k, n, np, true, nullptr, false,
+                                            a_sums, m));
+            MB200_TRY(launch_split_rows_i16(ctx, call.dev<int16_t>(ia), a_hi, a_lo, m, k, kp, false, a_sums, true,
+                                            nullptr, 0));
+            MB200_TRY(launch_gemm_i16_tc_bmn(ctx, a_hi, a_lo, b_hi, b_lo, a_sums, call.dev<int32_t>(ic), m, n, k, kp, np));
         }
     }
     return call.end(true);

@@ -91,17 +91,19 @@ EncodeTiledFn encode_tiled_fn();
 // K-contiguous with row pitch `kp` bytes (kp % 16 == 0, bases 16-byte aligned).
 int64_t launch_gemm_i8_tc(DeviceCtx* ctx, const int8_t* a, const int8_t* bt, int32_t* c, int64_t m,
                           int64_t n, int64_t k, int64_t kp_a, int64_t kp_b);
-// int16 GEMM as four 8-bit limb products on tensor cores; operands are limb planes.
+// int16 GEMM as four 8-bit limb products on tensor cores; operands are limb planes: A high
+// (signed) / low (unsigned), B high (signed) / low minus 128 (signed), and the int32 row sums
+// of A, which put the 128 back.
 int64_t launch_gemm_i16_tc(DeviceCtx* ctx, const int8_t* a_hi, const uint8_t* a_lo,
-                           const int8_t* bt_hi, const uint8_t* bt_lo, int32_t* c, int64_t m,
-                           int64_t n, int64_t k, int64_t kp);
+                           const int8_t* bt_hi, const uint8_t* bt_lo, const int32_t* a_row_sums,
+                           int32_t* c, int64_t m, int64_t n, int64_t k, int64_t kp);
 // Same products with B used as the caller has it (B[K][N], row pitch `pitch_b` bytes,
 // pitch_b % 16 == 0, base 16-byte aligned): no transpose pass.
 int64_t launch_gemm_i8_tc_bmn(DeviceCtx* ctx, const int8_t* a, const int8_t* b, int32_t* c, int64_t m,
                               int64_t n, int64_t k, int64_t kp_a, int64_t pitch_b);
 int64_t launch_gemm_i16_tc_bmn(DeviceCtx* ctx, const int8_t* a_hi, const uint8_t* a_lo,
-                               const int8_t* b_hi, const uint8_t* b_lo, int32_t* c, int64_t m,
-                               int64_t n, int64_t k, int64_t kp_a, int64_t pitch_b);
+                               const int8_t* b_hi, const uint8_t* b_lo, const int32_t* a_row_sums,
+                               int32_t* c, int64_t m, int64_t n, int64_t k, int64_t kp_a, int64_t pitch_b);
 bool tc_pair_forced();
 // Q16.16 hybrid: byte planes of an int32 matrix (what = 0: all four bytes; 1: the two bytes
 // of element >> 16), and the tensor-core product of those planes (see gemm_tc.cu).
@@ -121,8 +123,12 @@ int64_t launch_transpose_i32(DeviceCtx* ctx, const int32_t* src, int32_t* dst, i
                              int64_t cols);
 int64_t launch_pad_rows_i8(DeviceCtx* ctx, const int8_t* a, int8_t* ap, int64_t m, int64_t k,
                            int64_t kp);
+// lo_minus_128: store the low plane minus 128 (the B operand); row_sums: if not null, receives
+// the int32 sum of every row (the A operand; sums_are_zero says an earlier launch cleared it);
+// zero_buf / zero_n: a buffer this launch clears on the way (the next launch's row sums).
 int64_t launch_split_rows_i16(DeviceCtx* ctx, const int16_t* a, int8_t* hi, uint8_t* lo, int64_t m,
-                              int64_t k, int64_t kp);
+                              int64_t k, int64_t kp, bool lo_minus_128, int32_t* row_sums, bool sums_are_zero,
+                              int32_t* zero_buf, int64_t zero_n);
 int64_t launch_split_transpose_i16(DeviceCtx* ctx, const int16_t* b, int8_t* bt_hi, uint8_t* bt_lo,
                                    int64_t k, int64_t n, int64_t kp);
 // CUDA-core kernels.

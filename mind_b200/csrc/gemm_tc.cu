@@ -46,16 +46,12 @@ struct Cfg<0, 1> {
     static constexpr int BLOCK_N = 256, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 2, STAGES = 4;
 };
 template <>
-struct Cfg<1, 1> {
-    static constexpr int BLOCK_N = 128, NA = 2, NB = 2, NACC = 3, ACC_STAGES = 1, STAGES = 3;
+struct Cfg<1, 1> {  // int16: two accumulators of 2 x BLOCK_N columns (A high / A low times [B high | B low])
+    static constexpr int BLOCK_N = 128, NA = 2, NB = 2, NACC = 4, ACC_STAGES = 1, STAGES = 3;
 };
 template <>
 struct Cfg<0, 2> {
     static constexpr int BLOCK_N = 256, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 2, STAGES = 6;
-};
-template <>
-struct Cfg<1, 2> {
-    static constexpr int BLOCK_N = 128, NA = 2, NB = 2, NACC = 3, ACC_STAGES = 1, STAGES = 4;
 };
 
 template <>
@@ -70,6 +66,7 @@ struct TcParams {
     int vec_ok;            // C rows may be stored with 16-byte vectors
     int group_m;           // m-tiles walked together before moving on in n (L2 reuse of A panels)
     int hint_a, hint_b;    // L2 eviction policy per operand (see l2_policy)
+    const int32_t* row_sums;  // int16 mode: sum of every row of A
     int* err;
 };
 
@@ -113,6 +110,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
                const TcParams p) {
     static_assert(MODE != 2 || (PAIR == 1 && BMN), "the Q16.16 linear-part mode is single-CTA, B in place");
+    static_assert(MODE != 1 || PAIR == 1, "the int16 mode is single-CTA");
     using cfg = Cfg<MODE, PAIR>;
     constexpr int BLOCK_N = cfg::BLOCK_N;
     constexpr int B_ROWS = BLOCK_N / PAIR;  // columns of the output (rows of Bt) this CTA stages
@@ -299,13 +297,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                             mma_i8<PAIR>(d0 + 3 * BLOCK_N, a2d, b1d, ID_US, acc);    // a2.bh1      -> s3
                             mma_i8<PAIR>(d0 + 3 * BLOCK_N, a3d, b0d, ID_SU, 1u);     // a3.bh0      -> s3
                         } else {
+                            // The two planes of B lie side by side in the stage (high, then low
+                            // minus 128: both signed), exactly like a 2 x BLOCK_N wide int8 tile, so
+                            // one MMA of N = 2 x BLOCK_N forms [hi.hi | hi.lo'] and a second one
+                            // [lo.hi | lo.lo']: A is read from shared memory twice per 32 of K
+                            // instead of four times (the kernel is bound by shared-memory reads).
+                            static_assert(MODE != 1 || B_TILE_BYTES == B_BOX_BYTES, "planes must be adjacent boxes");
+                            constexpr uint32_t ID2_SS = idesc_i8(UMMA_M, 2 * BLOCK_N, true, true, BMN);
+                            constexpr uint32_t ID2_US = idesc_i8(UMMA_M, 2 * BLOCK_N, false, true, BMN);
                             const uint64_t da1 = smem_desc_k_sw128(sa + A_TILE_BYTES) + koff;
-                            const uint64_t db1 = (BMN ? smem_desc_mn_sw128(sb + B_TILE_BYTES, B_BOX_BYTES)
-                                                      : smem_desc_k_sw128(sb + B_TILE_BYTES)) + kb_off;
-                            mma_i8<PAIR>(d0, da0 + koff, db0 + kb_off, ID_SS, acc);          // hi.hi
-                            mma_i8<PAIR>(d0 + BLOCK_N, da0 + koff, db1, ID_SU, acc);         // hi.lo
-                            mma_i8<PAIR>(d0 + BLOCK_N, da1, db0 + kb_off, ID_US, 1u);        // lo.hi
-                            mma_i8<PAIR>(d0 + 2 * BLOCK_N, da1, db1, ID_UU, acc);            // lo.lo
+                            mma_i8<PAIR>(d0, da0 + koff, db0 + kb_off, ID2_SS, acc);               // hi.[hi | lo']
+                            mma_i8<PAIR>(d0 + 2 * BLOCK_N, da1, db0 + kb_off, ID2_US, acc);        // lo.[hi | lo']
                         }
                     }
                     if (PAIR == 1)
@@ -354,14 +356,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                             v[16 * h + j] = s0[j] + (s1[j] << 8) + (s2[j] << 16) + (s3[j] << 24);
                     }
                 } else {
-                    // all three accumulators' 32 columns in flight, one wait
-                    uint32_t mid[32], ll[32];
-                    tmem_ld32(t0 + c0, v);
-                    tmem_ld32(t0 + BLOCK_N + c0, mid);
-                    tmem_ld32(t0 + 2 * BLOCK_N + c0, ll);
-                    tmem_ld_wait();
+                    // columns [0, N) hi.hi, [N, 2N) hi.lo', [2N, 3N) lo.hi, [3N, 4N) lo.lo' with
+                    // lo' = lo - 128: 128 * (row sum of A) puts the 128 back (all mod 2^32)
+                    const uint32_t back = row < p.m ? 128u * (uint32_t)p.row_sums[row] : 0u;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = (v[j] << 16) + (mid[j] << 8) + ll[j];
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t hh[16], hl[16], lh[16], ll[16];
+                        tmem_ld16(t0 + c0 + 16 * h, hh);
+                        tmem_ld16(t0 + BLOCK_N + c0 + 16 * h, hl);
+                        tmem_ld16(t0 + 2 * BLOCK_N + c0 + 16 * h, lh);
+                        tmem_ld16(t0 + 3 * BLOCK_N + c0 + 16 * h, ll);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            v[16 * h + j] = (hh[j] << 16) + ((hl[j] + lh[j]) << 8) + ll[j] + back;
+                    }
                 }
                 if (row < p.m) {
                     const int col = col_tile + c0;
@@ -444,7 +453,7 @@ int g_pair_mode = 0;  // CTAs per tile: 1, 2 (cta_group::2 kernels), or 0 = pick
 template <int MODE, int PAIR, bool BMN>
 int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0, const void* b1,
                   int32_t* c, int64_t m, int64_t n, int64_t k, int64_t kp_a, int64_t kp_b,
-                  const void* a2 = nullptr, const void* a3 = nullptr) {
+                  const void* a2 = nullptr, const void* a3 = nullptr, const int32_t* row_sums = nullptr) {
     using cfg = Cfg<MODE, PAIR>;
     constexpr int B_ROWS = cfg::BLOCK_N / PAIR;
     constexpr int STAGE_BYTES = cfg::NA * A_TILE_BYTES + cfg::NB * B_ROWS * BLOCK_K;
@@ -480,6 +489,7 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     p.m_tiles = (int)((m + BLOCK_M * PAIR - 1) / (BLOCK_M * PAIR));
     p.n_tiles = (int)((n + cfg::BLOCK_N - 1) / cfg::BLOCK_N);
     p.vec_ok = (n % 4 == 0) && (reinterpret_cast<uintptr_t>(c) % 16 == 0);
+    p.row_sums = row_sums;
     p.err = ctx->err_word;
     // Tile order and L2 policy, measured at 16384^3 (DRAM reads were 16x the operand bytes with
     // 16 m-tiles per group and no hints): groups of 8 m-tiles keep the group's A panels
@@ -584,18 +594,17 @@ int64_t launch_gemm_q16_linear_tc(DeviceCtx* ctx, const uint8_t* const a_limb[4]
 
 // One CTA per tile only: a pair would give each CTA 64 columns of B, half a swizzle atom.
 int64_t launch_gemm_i16_tc_bmn(DeviceCtx* ctx, const int8_t* a_hi, const uint8_t* a_lo,
-                               const int8_t* b_hi, const uint8_t* b_lo, int32_t* c, int64_t m,
-                               int64_t n, int64_t k, int64_t kp_a, int64_t pitch_b) {
-    return launch_tc<1, 1, true>(ctx, a_hi, a_lo, b_hi, b_lo, c, m, n, k, kp_a, pitch_b);
+                               const int8_t* b_hi, const uint8_t* b_lo, const int32_t* a_row_sums,
+                               int32_t* c, int64_t m, int64_t n, int64_t k, int64_t kp_a, int64_t pitch_b) {
+    return launch_tc<1, 1, true>(ctx, a_hi, a_lo, b_hi, b_lo, c, m, n, k, kp_a, pitch_b, nullptr, nullptr,
+                                 a_row_sums);
 }
 
 int64_t launch_gemm_i16_tc(DeviceCtx* ctx, const int8_t* a_hi, const uint8_t* a_lo,
-                           const int8_t* bt_hi, const uint8_t* bt_lo, int32_t* c, int64_t m,
-                           int64_t n, int64_t k, int64_t kp) {
-    // Measured on B200: with three accumulators per tile the single-CTA kernel is as fast
-    // or faster than the pair kernel at every size tried, so auto keeps one CTA per tile.
-    if (g_pair_mode == 2) return launch_tc<1, 2, false>(ctx, a_hi, a_lo, bt_hi, bt_lo, c, m, n, k, kp, kp);
-    return launch_tc<1, 1, false>(ctx, a_hi, a_lo, bt_hi, bt_lo, c, m, n, k, kp, kp);
+                           const int8_t* bt_hi, const uint8_t* bt_lo, const int32_t* a_row_sums,
+                           int32_t* c, int64_t m, int64_t n, int64_t k, int64_t kp) {
+    return launch_tc<1, 1, false>(ctx, a_hi, a_lo, bt_hi, bt_lo, c, m, n, k, kp, kp, nullptr, nullptr,
+                                  a_row_sums);
 }
 
 }  // namespace mb200

@@ -36,7 +36,9 @@ __global__ void transpose_i8_kernel(const int8_t* __restrict__ b, int8_t* __rest
     }
 }
 
-// in: [K][N] int16; out: hi / lo planes [N][kp].
+// in: [K][N] int16; out: hi / lo planes [N][kp].  The low plane is stored minus 128 (as a signed
+// byte: low ^ 0x80), so that both planes of B are signed and one MMA can take them side by side;
+// the GEMM adds 128 * (row sum of A) back.
 __global__ void split_transpose_i16_kernel(const int16_t* __restrict__ b, int8_t* __restrict__ bt_hi,
                                            uint8_t* __restrict__ bt_lo, int k, int n, int64_t kp) {
     __shared__ int16_t tile[TT][TT + 2];
@@ -59,7 +61,7 @@ __global__ void split_transpose_i16_kernel(const int16_t* __restrict__ b, int8_t
                 lo |= (uint32_t)(v & 0xff) << (8 * j);
             }
             *reinterpret_cast<uint32_t*>(bt_hi + (size_t)nn * kp + kk) = hi;
-            *reinterpret_cast<uint32_t*>(bt_lo + (size_t)nn * kp + kk) = lo;
+            *reinterpret_cast<uint32_t*>(bt_lo + (size_t)nn * kp + kk) = lo ^ 0x80808080u;
         }
     }
 }
@@ -88,33 +90,88 @@ __global__ void pad_rows_i8_kernel(const int8_t* __restrict__ a, int8_t* __restr
             ap[r * kp + c] = c < k ? a[r * k + c] : (int8_t)0;
 }
 
+// Row-wise split of an int16 matrix into a signed high-byte plane and a low-byte plane.
+// lo_xor = 0x80 stores the low plane minus 128 (see split_transpose_i16_kernel: the B operand);
+// row_sums, when given, receives the int32 sum of every row (the A operand).
+// One block per row at a time, so the row sum needs no atomics here.
 __global__ void split_rows_i16_kernel(const int16_t* __restrict__ a, int8_t* __restrict__ hi,
-                                      uint8_t* __restrict__ lo, int64_t m, int64_t k, int64_t kp) {
-    for (int64_t r = blockIdx.x; r < m; r += gridDim.x)
+                                      uint8_t* __restrict__ lo, int64_t m, int64_t k, int64_t kp,
+                                      uint32_t lo_xor, int32_t* __restrict__ row_sums,
+                                      int32_t* __restrict__ zero_buf, int64_t zero_n) {
+    __shared__ int warp_part[8];
+    for (int64_t z = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; z < zero_n; z += (int64_t)gridDim.x * blockDim.x)
+        zero_buf[z] = 0;
+    for (int64_t r = blockIdx.x; r < m; r += gridDim.x) {
+        int sum = 0;
         for (int64_t c = threadIdx.x; c < kp; c += blockDim.x) {
             const int v = c < k ? (int)a[r * k + c] : 0;
             hi[r * kp + c] = (int8_t)(v >> 8);
-            lo[r * kp + c] = (uint8_t)(v & 0xff);
+            lo[r * kp + c] = (uint8_t)((v & 0xff) ^ lo_xor);
+            sum += v;
         }
+        if (row_sums) {  // uniform across the block
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = sum;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                int t = 0;
+                for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += warp_part[w];
+                row_sums[r] = t;
+            }
+            __syncthreads();
+        }
+    }
 }
 
 // 32 int16 per thread (four 16-byte loads in flight, eight 8-byte stores); needs k % 8 == 0,
-// kp == k and a 16-byte aligned base.  Byte permutes pick the low / high bytes.
+// kp == k and a 16-byte aligned base.  Byte permutes pick the low / high bytes.  Row sums (zero
+// on entry) are added once per warp when its 256 elements lie in one row, else per thread.
+// zero_buf: an unrelated buffer to clear on the way (the row sums of the NEXT split launch).
 __global__ void split_rows_i16_vec_kernel(const uint4* __restrict__ a, uint2* __restrict__ hi,
-                                          uint2* __restrict__ lo, int64_t n8) {
+                                          uint2* __restrict__ lo, int64_t n8, uint32_t lo_xor4,
+                                          int32_t* __restrict__ row_sums, int64_t k8,
+                                          int32_t* __restrict__ zero_buf, int64_t zero_n) {
     constexpr int U = 4;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i0 = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i0 < n8; i0 += stride * U) {
+    const int lane = threadIdx.x & 31;
+    for (int64_t z = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; z < zero_n; z += stride) zero_buf[z] = 0;
+    const bool small = n8 < 0x7fffffff;  // 32-bit division for the row index
+    // the loop runs on the warp's first index, so that every lane takes part in the shuffles
+    for (int64_t w0 = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~31); w0 < n8; w0 += stride * U) {
         uint4 v[U];
 #pragma unroll
         for (int u = 0; u < U; ++u)
-            if (i0 + u * stride < n8) v[u] = a[i0 + u * stride];
+            if (w0 + lane + u * stride < n8) v[u] = a[w0 + lane + u * stride];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int64_t i = i0 + u * stride;
-            if (i >= n8) break;
-            hi[i] = make_uint2(__byte_perm(v[u].x, v[u].y, 0x7531), __byte_perm(v[u].z, v[u].w, 0x7531));
-            lo[i] = make_uint2(__byte_perm(v[u].x, v[u].y, 0x6420), __byte_perm(v[u].z, v[u].w, 0x6420));
+            const int64_t i = w0 + lane + u * stride;
+            const bool ok = i < n8;
+            uint2 h = make_uint2(0u, 0u), l = make_uint2(0u, 0u);
+            if (ok) {
+                h = make_uint2(__byte_perm(v[u].x, v[u].y, 0x7531), __byte_perm(v[u].z, v[u].w, 0x7531));
+                l = make_uint2(__byte_perm(v[u].x, v[u].y, 0x6420), __byte_perm(v[u].z, v[u].w, 0x6420));
+                hi[i] = h;
+                lo[i] = make_uint2(l.x ^ lo_xor4, l.y ^ lo_xor4);
+            }
+            if (row_sums) {  // uniform
+                int sum = 256 * (__dp4a((int)h.x, 0x01010101, 0) + __dp4a((int)h.y, 0x01010101, 0)) +
+                          (int)(__dp4a(l.x, 0x01010101u, 0u) + __dp4a(l.y, 0x01010101u, 0u));
+                const int64_t first = w0 + u * stride;  // the warp's first vector: a multiple of 32
+                if (k8 % 32 == 0) {  // a warp's 256 elements never straddle rows
+                    sum = __reduce_add_sync(0xffffffffu, sum);
+                    if (lane == 0 && first < n8)
+                        atomicAdd(row_sums + (small ? (int64_t)((uint32_t)first / (uint32_t)k8) : first / k8), sum);
+                } else {
+                    const int64_t r = !ok ? -1 : small ? (int64_t)((uint32_t)i / (uint32_t)k8) : i / k8;
+                    const int64_t r_first = __shfl_sync(0xffffffffu, r, 0);
+                    if (__all_sync(0xffffffffu, !ok || r == r_first)) {
+                        sum = __reduce_add_sync(0xffffffffu, sum);
+                        if (lane == 0 && r_first >= 0) atomicAdd(row_sums + r_first, sum);
+                    } else if (ok) {
+                        atomicAdd(row_sums + r, sum);
+                    }
+                }
+            }
         }
     }
 }
@@ -205,17 +262,22 @@ int64_t launch_pad_rows_i8(DeviceCtx* ctx, const int8_t* a, int8_t* ap, int64_t 
 }
 
 int64_t launch_split_rows_i16(DeviceCtx* ctx, const int16_t* a, int8_t* hi, uint8_t* lo, int64_t m,
-                              int64_t k, int64_t kp) {
+                              int64_t k, int64_t kp, bool lo_minus_128, int32_t* row_sums, bool sums_are_zero,
+                              int32_t* zero_buf, int64_t zero_n) {
+    const uint32_t x = lo_minus_128 ? 0x80u : 0u;
     if (kp == k && k % 8 == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0) {
+        if (row_sums && !sums_are_zero) MB200_CUDA(cudaMemsetAsync(row_sums, 0, (size_t)m * 4, ctx->stream));
         const int64_t n8 = m * k / 8;
         int64_t blocks = (n8 + 256 * 4 - 1) / (256 * 4);  // one pass: four vectors per thread
         if (blocks > 148 * 256) blocks = 148 * 256;
+        if (blocks < 1) blocks = 1;
         split_rows_i16_vec_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(
             reinterpret_cast<const uint4*>(a), reinterpret_cast<uint2*>(hi),
-            reinterpret_cast<uint2*>(lo), n8);
+            reinterpret_cast<uint2*>(lo), n8, x * 0x01010101u, row_sums, k / 8, zero_buf, zero_n);
     } else {
         unsigned grid = (unsigned)(m < 148 * 16 ? m : 148 * 16);
-        split_rows_i16_kernel<<<grid, 256, 0, ctx->stream>>>(a, hi, lo, m, k, kp);
+        if (grid < 1) grid = 1;
+        split_rows_i16_kernel<<<grid, 256, 0, ctx->stream>>>(a, hi, lo, m, k, kp, x, row_sums, zero_buf, zero_n);
     }
     count_launch();
     return check_launch("split_rows_i16_kernel");
