@@ -12,13 +12,15 @@
 // MODE 0 (int8):  one s8 x s8 product, BLOCK_N = 256, two accumulator stages so the
 //                 epilogue of tile t overlaps the main loop of tile t + 1.
 // MODE 1 (int16): operands arrive as 8-bit limb planes, a = 256*hi + lo with hi signed
-//                 and lo unsigned; four limb products go to three accumulators
-//                 (hi.hi | hi.lo + lo.hi | lo.lo) and the epilogue forms
-//                 (HH << 16) + (MID << 8) + LL with 32-bit wrap, which equals the
-//                 exact sum truncated to 32 bits.  Every partial stays below 2^31 for
-//                 K <= 2^15, and wrap inside an accumulator would be harmless anyway
-//                 (the tensor core does not saturate: descriptor bit 3 is 0).
-// The PAIR = 2 variant runs one tile on a pair of CTAs (a 2-CTA cluster,
+//                 and lo unsigned, b = 256*hi + (lo' + 128) with both planes signed.
+//                 B's planes lie side by side in the stage, so two MMAs of N = 256
+//                 per 32 of K give [hi.hi | hi.lo'] and [lo.hi | lo.lo'] in two
+//                 accumulators, and the epilogue forms
+//                 (HH << 16) + ((HL' + LH) << 8) + LL' + 128 * rowsum(a) with 32-bit
+//                 wrap, which equals the exact sum truncated to 32 bits.  Wrap inside
+//                 an accumulator is harmless (the tensor core does not saturate:
+//                 descriptor bit 3 is 0).  One CTA per tile.
+// The PAIR = 2 variant (int8) runs one tile on a pair of CTAs (a 2-CTA cluster,
 // tcgen05 cta_group::2): 256 rows of A (128 per CTA) by BLOCK_N rows of Bt, of which
 // each CTA stages only its half, which halves the shared-memory traffic per MMA.
 // Out-of-range rows / K tails are zero-filled by TMA; stores are predicated.
