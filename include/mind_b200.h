@@ -152,7 +152,9 @@ int64_t mind_b200_reserve(int64_t scratch_bytes, int64_t staging_bytes);
  * transposed into scratch first (otherwise B is read in place whenever its pitch and base are
  * 16-byte aligned); 1 = the independent CUDA-core kernels kept as an on-device cross-check
  * (for Q16.16: the all-integer kernel); 6 / 7 = Q16.16 GEMM only: the FP64-pipe kernel alone /
- * the tensor-core hybrid at every size (default: hybrid from 2^29 products up, i.e. about 800^3).
+ * the tensor-core hybrid at every size (default: hybrid from 2^29 products up, i.e. about 800^3);
+ * 8 / 9 = the hybrid with its two halves one after the other / side by side on two streams
+ * (default: side by side up to 2^31 products, where the tensor-core half is latency-bound).
  * Every path gives identical bytes. */
 int64_t mind_b200_set_gemm_path(int64_t path);
 /* Self-test of the bounded waits inside the GEMM kernels: launches a one-warp kernel that waits

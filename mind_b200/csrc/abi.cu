@@ -12,6 +12,7 @@ std::mutex g_call_mutex;  // calls are serialised, like the reference's MT dispa
 int g_gemm_path = 0;      // 0 = tensor cores, 1 = CUDA-core cross-check kernels
 bool g_force_transpose = false;  // tensor cores: always re-lay B out K-contiguous (testing)
 int g_q16_mode = 0;       // Q16.16 GEMM: 0 = pick by size, 6 = FP64-pipe kernel alone, 7 = tensor-core hybrid
+int g_q16_side_sms = -1;  // hybrid: SMs given to the tensor-core half beside the FP64 half (-1 = by size, 0 = in sequence)
 
 // One operand of a call: where the caller keeps it and where the kernels see it.
 struct Operand {
@@ -469,10 +470,39 @@ int64_t gemm_q16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t 
             uint8_t* bp[4] = {nullptr, nullptr, nullptr, nullptr};
             for (int i = 0; i < 4; ++i) ap[i] = static_cast<uint8_t*>(arena_take(ctx->scratch, a_plane));
             for (int i = 0; i < 2; ++i) bp[i] = static_cast<uint8_t*>(arena_take(ctx->scratch, b_plane));
+            // Products up to 2^31 (1024^3 is 2^30): the tensor-core half is latency-bound (a few
+            // k-blocks per tile, fewer tiles than SMs) and the FP64 half takes five times as long, so
+            // the two run side by side: c is zeroed, the byte split and the tensor-core kernel go to
+            // a second stream on 16 SMs, the FP64 kernel keeps the rest, and both add onto c with
+            // red.global.add (sums mod 2^32 commute).  Measured at 1024^3: 122 us against 135 us in
+            // sequence (8 / 12 / 24 SMs: 170 / 133 / 127 us); from 1536^3 up the sequence is as fast
+            // or faster (the tensor-core half is ~6 % of the work there and would idle its SMs).
+            const double work = (double)m * (double)n * (double)k;
+            const int side_sms = g_q16_side_sms >= 0 ? g_q16_side_sms : (work <= 2147483648.0 ? 16 : 0);
+            if (side_sms > 0 && side_sms < ctx->sm_count) {
+                MB200_CUDA(cudaMemsetAsync(dc, 0, (size_t)m * n * 4, ctx->stream));
+                MB200_CUDA(cudaEventRecord(ctx->fork_ev, ctx->stream));
+                MB200_CUDA(cudaStreamWaitEvent(ctx->side, ctx->fork_ev, 0));
+                cudaStream_t main_stream = ctx->stream;
+                const bool profiling = ctx->profile;
+                ctx->stream = ctx->side;  // the launchers below use the context's stream
+                ctx->profile = false;     // kernel timing covers the FP64 kernel, which spans the call
+                int64_t rc = launch_split_i32_bytes(ctx, da, ap, 0, m, k, kp);
+                if (!rc) rc = launch_split_i32_bytes(ctx, db, bp, 1, k, n, np);
+                if (!rc) rc = launch_gemm_q16_linear_tc(ctx, ap, bp, dc, m, n, k, kp, np, true, side_sms);
+                ctx->stream = main_stream;
+                ctx->profile = profiling;
+                // join even after a failed launch, so that the side stream never outlives the call
+                MB200_CUDA(cudaEventRecord(ctx->join_ev, ctx->side));
+                if (!rc) rc = launch_gemm_q16_floor_add(ctx, da, db, dc, m, k, n, ctx->sm_count - side_sms);
+                MB200_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->join_ev, 0));
+                if (rc) return rc;
+                return call.end(true);
+            }
             MB200_TRY(launch_split_i32_bytes(ctx, da, ap, 0, m, k, kp));
             MB200_TRY(launch_split_i32_bytes(ctx, db, bp, 1, k, n, np));
-            MB200_TRY(launch_gemm_q16_linear_tc(ctx, ap, bp, dc, m, n, k, kp, np));
-            MB200_TRY(launch_gemm_q16_floor_add(ctx, da, db, dc, m, k, n));
+            MB200_TRY(launch_gemm_q16_linear_tc(ctx, ap, bp, dc, m, n, k, kp, np, false, 0));
+            MB200_TRY(launch_gemm_q16_floor_add(ctx, da, db, dc, m, k, n, 0));
             return call.end(true);
         }
         if (fp64_ok)
@@ -606,15 +636,16 @@ int64_t mind_b200_set_gemm_path(int64_t path) {
     clear_error();
     std::lock_guard<std::mutex> lock(g_call_mutex);
     g_force_transpose = path == 4 || path == 5;
-    g_q16_mode = (path == 6 || path == 7) ? (int)path : 0;
+    g_q16_mode = path == 6 ? 6 : (path >= 7 && path <= 9) ? 7 : 0;
+    g_q16_side_sms = path == 8 ? 0 : path == 9 ? 16 : -1;
     switch (path) {
-        case 6: case 7: g_gemm_path = 0; return set_pair_mode(0);  // Q16.16 GEMM kernel choice only
+        case 6: case 7: case 8: case 9: g_gemm_path = 0; return set_pair_mode(0);  // Q16.16 GEMM kernel choice only
         case 0: g_gemm_path = 0; return set_pair_mode(0);  // tensor cores, kernel picked per call
         case 1: g_gemm_path = 1; return set_pair_mode(0);  // CUDA cores
         case 2: case 4: g_gemm_path = 0; return set_pair_mode(2);  // tensor cores, CTA pairs
         case 3: case 5: g_gemm_path = 0; return set_pair_mode(1);  // tensor cores, one CTA per tile
     }
-    return fail(MIND_B200_ERR_INVALID, "gemm path must be 0 (auto), 1 (CUDA cores), 2 / 3 (CTA pairs / single CTA), 4 / 5 (the same with B transposed first) or 6 / 7 (Q16.16: FP64-pipe kernel alone / tensor-core hybrid)");
+    return fail(MIND_B200_ERR_INVALID, "gemm path must be 0 (auto), 1 (CUDA cores), 2 / 3 (CTA pairs / single CTA), 4 / 5 (the same with B transposed first) 6 / 7 (Q16.16: FP64-pipe kernel alone / tensor-core hybrid) or 8 / 9 (the hybrid with its halves in sequence / side by side)");
 }
 
 int64_t mind_b200_selftest_wait_timeout(int64_t limit_ms) {

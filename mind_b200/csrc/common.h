@@ -51,6 +51,10 @@ struct DeviceCtx {
     Arena staging;                  // device copies of host-pointer operands
     int* err_word = nullptr;        // word a kernel sets when a bounded wait runs out (device view)
     int* err_host = nullptr;        // the same word, host view (mapped pinned memory)
+    // A second stream for work that runs beside the kernels on `stream` inside one call (forked
+    // and joined with the two events).
+    cudaStream_t side = nullptr;
+    cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
     // Optional timing of the main kernel of each call (CUDA events on `stream`).
     static constexpr int PROF_RING = 512;
     bool profile = false;
@@ -111,10 +115,10 @@ int64_t launch_split_i32_bytes(DeviceCtx* ctx, const int32_t* src, uint8_t* cons
                                int64_t rows, int64_t cols, int64_t pitch);
 int64_t launch_gemm_q16_linear_tc(DeviceCtx* ctx, const uint8_t* const a_limb[4], const uint8_t* const bh_limb[2],
                                   int32_t* p_out, int64_t m, int64_t n, int64_t k, int64_t kp_a,
-                                  int64_t pitch_b);
+                                  int64_t pitch_b, bool accumulate, int max_ctas);
 // Floor part of the Q16.16 product on the FP64 pipe, added onto the linear part already in c.
 int64_t launch_gemm_q16_floor_add(DeviceCtx* ctx, const int32_t* a, const int32_t* b, int32_t* c, int64_t m,
-                                  int64_t k, int64_t n);
+                                  int64_t k, int64_t n, int max_blocks);
 int64_t launch_wait_selftest(DeviceCtx* ctx, int64_t limit_ms);
 // Re-layout kernels.
 int64_t launch_transpose_i8(DeviceCtx* ctx, const int8_t* b, int8_t* bt, int64_t k, int64_t n,

@@ -93,6 +93,13 @@ DeviceCtx* current_ctx() {
         return nullptr;
     }
     *ctx->err_host = 0;
+    // made here, not on first use: a first use could fall inside a stream capture
+    if (cudaStreamCreateWithFlags(&ctx->side, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&ctx->fork_ev, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&ctx->join_ev, cudaEventDisableTiming) != cudaSuccess) {
+        fail(MIND_B200_ERR_CUDA, "could not create the side stream: %s", cudaGetErrorString(cudaGetLastError()));
+        return nullptr;
+    }
     ctx->sm_count = sms;
     ctx->stream = nullptr;
     ctx->device = dev;

@@ -207,7 +207,7 @@ gemm_q16_fp64_kernel(const int32_t* __restrict__ a, const int32_t* __restrict__ 
 
 template <int BN, bool FULL>
 int64_t launch_q16_streamk(DeviceCtx* ctx, const int32_t* a, const int32_t* b, int32_t* c, int64_t m, int64_t k,
-                           int64_t n) {
+                           int64_t n, int max_blocks) {
     if (m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff)
         return fail(MIND_B200_ERR_TOO_LARGE, "GEMM dimension above 2^31-1");
     constexpr int SMEM = (int)sizeof(Q16Smem<BN, FULL>);
@@ -224,7 +224,8 @@ int64_t launch_q16_streamk(DeviceCtx* ctx, const int32_t* a, const int32_t* b, i
     for (int64_t k0 = 0; k0 < k; k0 += K_SLICE) {
         const int64_t kc = k - k0 < K_SLICE ? k - k0 : K_SLICE;
         const int64_t k_steps = (kc + QBK - 1) / QBK, units = m_tiles * n_tiles * k_steps;
-        const unsigned grid = (unsigned)(units < ctx->sm_count ? units : ctx->sm_count);
+        const int64_t cap = max_blocks > 0 && max_blocks < ctx->sm_count ? max_blocks : ctx->sm_count;
+        const unsigned grid = (unsigned)(units < cap ? units : cap);
         prof_begin(ctx);
         gemm_q16_fp64_kernel<BN, FULL><<<grid, QTHREADS, SMEM, ctx->stream>>>(
             a + k0, b + k0 * n, c, (int)m, (int)kc, (int)n, (int)k, (int)n_tiles, (int)k_steps, (long long)units);
@@ -246,13 +247,14 @@ bool gemm_q16_fp64_usable(const int32_t* a, const int32_t* b, int64_t k, int64_t
 // c = the whole product (c is zeroed here, then added to)
 int64_t launch_gemm_q16_fp64(DeviceCtx* ctx, const int32_t* a, const int32_t* b, int32_t* c, int64_t m,
                              int64_t k, int64_t n) {
-    return launch_q16_streamk<64, true>(ctx, a, b, c, m, k, n);
+    return launch_q16_streamk<64, true>(ctx, a, b, c, m, k, n, 0);
 }
 
-// c += the floor half (c holds the linear half)
+// c += the floor half (c holds the linear half, or the linear half is being added beside this
+// kernel); max_blocks > 0 leaves the other SMs to that kernel
 int64_t launch_gemm_q16_floor_add(DeviceCtx* ctx, const int32_t* a, const int32_t* b, int32_t* c, int64_t m,
-                                  int64_t k, int64_t n) {
-    return launch_q16_streamk<128, false>(ctx, a, b, c, m, k, n);
+                                  int64_t k, int64_t n, int max_blocks) {
+    return launch_q16_streamk<128, false>(ctx, a, b, c, m, k, n, max_blocks);
 }
 
 }  // namespace mb200

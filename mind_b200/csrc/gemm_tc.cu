@@ -69,6 +69,7 @@ struct TcParams {
     int group_m;           // m-tiles walked together before moving on in n (L2 reuse of A panels)
     int hint_a, hint_b;    // L2 eviction policy per operand (see l2_policy)
     const int32_t* row_sums;  // int16 mode: sum of every row of A
+    int accumulate;           // add onto C with red.global.add (C shared with a kernel running beside this one)
     int* err;
 };
 
@@ -376,7 +377,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                 }
                 if (row < p.m) {
                     const int col = col_tile + c0;
-                    if (p.vec_ok && col + 32 <= p.n) {
+                    if (p.accumulate) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col + j < p.n) atomicAdd(reinterpret_cast<unsigned int*>(crow) + col + j, v[j]);
+                    } else if (p.vec_ok && col + 32 <= p.n) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 4)
                             *reinterpret_cast<uint4*>(crow + col + j) =
@@ -455,7 +460,8 @@ int g_pair_mode = 0;  // CTAs per tile: 1, 2 (cta_group::2 kernels), or 0 = pick
 template <int MODE, int PAIR, bool BMN>
 int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0, const void* b1,
                   int32_t* c, int64_t m, int64_t n, int64_t k, int64_t kp_a, int64_t kp_b,
-                  const void* a2 = nullptr, const void* a3 = nullptr, const int32_t* row_sums = nullptr) {
+                  const void* a2 = nullptr, const void* a3 = nullptr, const int32_t* row_sums = nullptr,
+                  bool accumulate = false, int max_ctas = 0) {
     using cfg = Cfg<MODE, PAIR>;
     constexpr int B_ROWS = cfg::BLOCK_N / PAIR;
     constexpr int STAGE_BYTES = cfg::NA * A_TILE_BYTES + cfg::NB * B_ROWS * BLOCK_K;
@@ -492,6 +498,7 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     p.n_tiles = (int)((n + cfg::BLOCK_N - 1) / cfg::BLOCK_N);
     p.vec_ok = (n % 4 == 0) && (reinterpret_cast<uintptr_t>(c) % 16 == 0);
     p.row_sums = row_sums;
+    p.accumulate = accumulate ? 1 : 0;
     p.err = ctx->err_word;
     // Tile order and L2 policy, measured at 16384^3 (DRAM reads were 16x the operand bytes with
     // 16 m-tiles per group and no hints): groups of 8 m-tiles keep the group's A panels
@@ -510,6 +517,7 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     }
     int units = ctx->sm_count / PAIR;  // CTAs (or CTA pairs) resident at once
     if (total < units) units = (int)total;
+    if (max_ctas > 0 && PAIR == 1 && units > max_ctas) units = max_ctas;
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3((unsigned)(units * PAIR), 1, 1);
     lc.blockDim = dim3(TC_THREADS, 1, 1);
@@ -587,14 +595,15 @@ bool tc_pair_forced() { return g_pair_mode == 2; }
 // Linear part of the Q16.16 GEMM on tensor cores: P[i,j] = sum_k a[i,k] * bh[k,j] mod 2^32,
 // from the four byte planes of a (a_limb[0] lowest, a_limb[3] signed) and the two byte planes
 // of bh = b >> 16 (bh_limb[1] signed), B planes in B's own orientation ([K][pitch_b]).
+// accumulate: add onto p_out (red.global.add) instead of storing; max_ctas > 0 caps the persistent
+// grid, for running beside another kernel that holds the other SMs.
 int64_t launch_gemm_q16_linear_tc(DeviceCtx* ctx, const uint8_t* const a_limb[4], const uint8_t* const bh_limb[2],
                                   int32_t* p_out, int64_t m, int64_t n, int64_t k, int64_t kp_a,
-                                  int64_t pitch_b) {
+                                  int64_t pitch_b, bool accumulate, int max_ctas) {
     return launch_tc<2, 1, true>(ctx, a_limb[0], a_limb[1], bh_limb[0], bh_limb[1], p_out, m, n, k, kp_a,
-                                 pitch_b, a_limb[2], a_limb[3]);
+                                 pitch_b, a_limb[2], a_limb[3], nullptr, accumulate, max_ctas);
 }
 
-// One CTA per tile only: a pair would give each CTA 64 columns of B, half a swizzle atom.
 int64_t launch_gemm_i16_tc_bmn(DeviceCtx* ctx, const int8_t* a_hi, const uint8_t* a_lo,
                                const int8_t* b_hi, const uint8_t* b_lo, const int32_t* a_row_sums,
                                int32_t* c, int64_t m, int64_t n, int64_t k, int64_t kp_a, int64_t pitch_b) {

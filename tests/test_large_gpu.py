@@ -112,7 +112,7 @@ def test_reproducibility_harness_workloads(gpu):
         e = SELF[f"matmul-q16-{n}"]
         a = lcg_dev(gpu, n * n, 0, e["seed"], shift=e["shift"])
         b = lcg_dev(gpu, n * n, 0, e["seed"], offset=n * n, shift=e["shift"])
-        for path in (0, 1, 6, 7):
+        for path in (0, 1, 6, 7, 8, 9):
             gpu.set_gemm_path(path)
             c = torch.empty(n * n, dtype=torch.int32, device="cuda")
             gpu.matmul_mm_q16_mt_v(a, b, c, n, n, n)
@@ -254,7 +254,7 @@ def test_stability_reruns(gpu):
     a = lcg_dev(gpu, n * n, 0, seed)
     b = lcg_dev(gpu, n * n, 0, seed, offset=n * n)
     want = torch.from_numpy(O.gemm_q16(a.cpu().numpy(), b.cpu().numpy(), n, n, n)).cuda()
-    for path in (0, 7, 1):  # single FP64-pipe kernel (this size), tensor-core hybrid, all-integer kernel
+    for path in (0, 8, 9, 1):  # single FP64-pipe kernel (this size), hybrid in sequence / side by side, all-integer
         gpu.set_gemm_path(path)
         for _ in range(256 if path != 1 else 32):
             c = torch.empty(n * n, dtype=torch.int32, device="cuda")
@@ -272,3 +272,52 @@ def test_stability_reruns(gpu):
             if first is None:
                 first = c
             assert torch.equal(c, first), path
+
+
+def test_cuda_graph_capture_and_replay(gpu):
+    """Device-pointer calls are plain stream work: after one warm-up call (scratch sized, kernel
+    attributes set) they can be captured into a CUDA graph and replayed, the two-stream Q16.16
+    hybrid included (its side stream forks from and joins the captured stream)."""
+    n = 1024
+    seed = 0xDEADBEEF00000000 ^ n
+    a8 = lcg_dev(gpu, n * n, 1, seed)
+    b8 = lcg_dev(gpu, n * n, 1, seed, offset=n * n)
+    a16 = lcg_dev(gpu, n * n, 2, seed)
+    b16 = lcg_dev(gpu, n * n, 2, seed, offset=n * n)
+    aq = lcg_dev(gpu, n * n, 0, seed, shift=13)
+    bq = lcg_dev(gpu, n * n, 0, seed, offset=n * n, shift=13)
+    side = torch.cuda.Stream()
+    cases = [("i8", 0, lambda c: gpu.matmul_mm_i8_v(a8, b8, c, n, n, n)),
+             ("i16", 0, lambda c: gpu.matmul_mm_i16(a16, b16, c, n, n, n)),
+             ("q16 one kernel", 6, lambda c: gpu.matmul_mm_q16_v(aq, bq, c, n, n, n)),
+             ("q16 hybrid in sequence", 8, lambda c: gpu.matmul_mm_q16_v(aq, bq, c, n, n, n)),
+             ("q16 hybrid side by side", 9, lambda c: gpu.matmul_mm_q16_v(aq, bq, c, n, n, n)),
+             ("gemv", 0, lambda c: gpu.gemv_q16_mt(aq, bq, c, n, n))]
+    try:
+        for name, path, call in cases:
+            gpu.set_gemm_path(path)
+            want = torch.empty(n * n, dtype=torch.int32, device="cuda")
+            gpu.set_stream(torch.cuda.current_stream().cuda_stream)
+            call(want)
+            torch.cuda.synchronize()
+            out = torch.zeros(n * n, dtype=torch.int32, device="cuda")
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                gpu.set_stream(side.cuda_stream)
+                call(out)                      # warm-up on the capturing stream
+                torch.cuda.synchronize()
+                out.zero_()
+                with torch.cuda.graph(graph, stream=side):
+                    call(out)
+            gpu.set_stream(torch.cuda.current_stream().cuda_stream)
+            torch.cuda.synchronize()
+            assert int(out.abs().max()) == 0, name   # capture records, it does not run
+            for _ in range(3):
+                out.zero_()
+                graph.replay()
+                torch.cuda.synchronize()
+                rows = n if name == "gemv" else n * n
+                assert torch.equal(out[:rows], want[:rows]), name
+    finally:
+        gpu.set_gemm_path(0)
+        gpu.set_stream(torch.cuda.current_stream().cuda_stream)

@@ -150,8 +150,9 @@ def test_gemm_i16_shapes(gpu, path):
         assert np.all(c[m * n :] == 0x5A5A5A5A)
 
 
-# 0: by size; 1: all-integer kernel; 6: FP64-pipe kernel alone; 7: tensor-core linear part + FP64 floor part
-@pytest.mark.parametrize("path", [0, 1, 6, 7])
+# 0: by size; 1: all-integer kernel; 6: FP64-pipe kernel alone; 7: tensor-core linear part + FP64 floor
+# part (8: one after the other, 9: side by side on two streams, both adding onto C)
+@pytest.mark.parametrize("path", [0, 1, 6, 7, 8, 9])
 def test_gemm_q16_shapes(gpu, path):
     gpu.set_gemm_path(path)
     # the last shape has a long K on a single output tile: many blocks add into the same outputs
