@@ -371,3 +371,37 @@ def test_errors_do_not_abort(gpu):
         gpu.matmul_mm_q16_v(a.ctypes.data + 1, a, c, 2, 2, 2)  # misaligned int32
     gpu.matmul_mm_i8_v(a, a, c, 4, 4, 4)  # and the library still works afterwards
     assert np.all(c == 0)
+
+
+def test_calls_from_several_host_threads(gpu):
+    """The reference's intrinsics may be called from any thread (its MT forms take a process-wide
+    lock, runtime-support/mind_intrinsics.c:1929 and :1976); here calls are serialised inside the library
+    and every thread must get its own exact result, host operands and all kernel families mixed."""
+    import threading
+    errors = []
+
+    def worker(t):
+        try:
+            g = O.Lcg(1000 + t)
+            for it in range(6):
+                m, k, n = 40 + 13 * t + it, 64 + 16 * ((t + it) % 5), 48 + 16 * t
+                a8, b8 = g.i8(m * k), g.i8(k * n)
+                c = np.empty(m * n, dtype=np.int32)
+                gpu.matmul_mm_i8_v(a8, b8, c, m, k, n)
+                assert np.array_equal(c, O.gemm_i8(a8, b8, m, k, n)), ("i8", t, it)
+                aq, bq = g.q16(m * k), g.q16(k * n)
+                gpu.matmul_mm_q16_v(aq, bq, c, m, k, n)
+                assert np.array_equal(c, O.gemm_q16(aq, bq, m, k, n)), ("q16", t, it)
+                y = np.empty(m, dtype=np.int32)
+                gpu.gemv_q16_mt(aq, bq[:k], y, m, k)
+                assert np.array_equal(y, O.gemv_q16(aq, bq[:k], m, k)), ("gemv", t, it)
+                assert gpu.dot_q16_v(aq[:k], bq[:k], k) == O.dot_q16(aq[:k], bq[:k]), ("dot", t, it)
+        except BaseException as ex:  # noqa: BLE001 - reported in the main thread
+            errors.append(ex)
+
+    threads = [threading.Thread(target=worker, args=(t,)) for t in range(4)]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    assert not errors, errors
