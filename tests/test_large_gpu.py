@@ -321,3 +321,25 @@ def test_cuda_graph_capture_and_replay(gpu):
     finally:
         gpu.set_gemm_path(0)
         gpu.set_stream(torch.cuda.current_stream().cuda_stream)
+
+
+def test_pinned_host_operands_through_the_pipeline(gpu):
+    """Page-locked host operands (what the end-to-end bench passes): uploads and downloads are
+    then truly asynchronous, so the band / chunk ordering is what keeps the bytes right."""
+    m, k, n = 4096, 1024, 8192
+    seed = 0xDEADBEEF00000000 ^ 4097
+    a = lcg_dev(gpu, m * k, 1, seed)
+    b = lcg_dev(gpu, k * n, 1, seed, offset=m * k)
+    want = torch.empty(m * n, dtype=torch.int32, device="cuda")
+    gpu.matmul_mm_i8_v(a, b, want, m, k, n)
+    ha, hb = a.cpu().pin_memory(), b.cpu().pin_memory()
+    for rep in range(3):
+        hc = torch.full((m * n,), -1, dtype=torch.int32).pin_memory()
+        gpu.matmul_mm_i8_v(ha, hb, hc, m, k, n)          # all three on the host
+        assert torch.equal(hc, want.cpu()), rep
+    hc = torch.full((m * n,), -1, dtype=torch.int32).pin_memory()
+    gpu.matmul_mm_i8_v(a, hb, hc, m, k, n)               # A on the device
+    assert torch.equal(hc, want.cpu())
+    hc = torch.full((m * n,), -1, dtype=torch.int32).pin_memory()
+    gpu.matmul_mm_i8_v(ha, b, hc, m, k, n)               # B on the device
+    assert torch.equal(hc, want.cpu())
