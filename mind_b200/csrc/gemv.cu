@@ -50,6 +50,23 @@ __device__ __forceinline__ uint32_t fma_word(uint32_t acc, int32_t w, int32_t x)
         return acc + (w >= x ? (uint32_t)w - (uint32_t)x : (uint32_t)x - (uint32_t)w);
     }
 }
+// int16 rows: x = 256 * xh + xl (xh signed, xl unsigned bytes), so w . x = 256 * (w . xh) + w . xl,
+// and dp2a multiplies two packed int16 of w by two bytes at once: eight dp2a and four byte
+// permutes per eight elements, with no sign extension of w (the shift-and-multiply form left
+// the kernel at 0.70 of the copy bandwidth).  lo collects w . xl, hi collects w . xh.
+__device__ __forceinline__ void dp2a_word_pair(uint32_t& lo, uint32_t& hi, int32_t w0, int32_t w1, uint32_t xl,
+                                               uint32_t xh) {
+    asm("dp2a.lo.s32.u32 %0, %1, %2, %0;" : "+r"(lo) : "r"(w0), "r"(xl));
+    asm("dp2a.hi.s32.u32 %0, %1, %2, %0;" : "+r"(lo) : "r"(w1), "r"(xl));
+    asm("dp2a.lo.s32.s32 %0, %1, %2, %0;" : "+r"(hi) : "r"(w0), "r"(xh));
+    asm("dp2a.hi.s32.s32 %0, %1, %2, %0;" : "+r"(hi) : "r"(w1), "r"(xh));
+}
+__device__ __forceinline__ void i16_vec(uint32_t& lo, uint32_t& hi, const int4& w, const int4& x) {
+    // bytes of four consecutive x elements: low bytes 0x6420, high bytes 0x7531
+    dp2a_word_pair(lo, hi, w.x, w.y, __byte_perm(x.x, x.y, 0x6420), __byte_perm(x.x, x.y, 0x7531));
+    dp2a_word_pair(lo, hi, w.z, w.w, __byte_perm(x.z, x.w, 0x6420), __byte_perm(x.z, x.w, 0x7531));
+}
+
 template <int OP>
 __device__ __forceinline__ uint32_t fma_vec(uint32_t acc, const int4& w, const int4& x) {
     acc = fma_word<OP>(acc, w.x, x.x);
@@ -70,14 +87,26 @@ __device__ __forceinline__ uint32_t row_partial(const void* wrow, const void* x,
         const int4* xv = static_cast<const int4*>(x);
         int64_t i = tid;
         constexpr int U = 8;
+        uint32_t hi = 0;  // int16 only: the sum of w . (high bytes of x)
         for (; i + (int64_t)(U - 1) * nthr < nvec; i += (int64_t)U * nthr) {
             int4 w[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) w[u] = ld_stream(wv + i + (int64_t)u * nthr);
 #pragma unroll
-            for (int u = 0; u < U; ++u) acc = fma_vec<OP>(acc, w[u], __ldg(xv + i + (int64_t)u * nthr));
+            for (int u = 0; u < U; ++u) {
+                if (OP == OP_I16)
+                    i16_vec(acc, hi, w[u], __ldg(xv + i + (int64_t)u * nthr));
+                else
+                    acc = fma_vec<OP>(acc, w[u], __ldg(xv + i + (int64_t)u * nthr));
+            }
         }
-        for (; i < nvec; i += nthr) acc = fma_vec<OP>(acc, ld_stream(wv + i), __ldg(xv + i));
+        for (; i < nvec; i += nthr) {
+            if (OP == OP_I16)
+                i16_vec(acc, hi, ld_stream(wv + i), __ldg(xv + i));
+            else
+                acc = fma_vec<OP>(acc, ld_stream(wv + i), __ldg(xv + i));
+        }
+        if (OP == OP_I16) acc += hi << 8;
     } else if (OP == OP_I16) {
         const int16_t* w = static_cast<const int16_t*>(wrow);
         const int16_t* xs = static_cast<const int16_t*>(x);

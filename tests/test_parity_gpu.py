@@ -405,3 +405,19 @@ def test_calls_from_several_host_threads(gpu):
     for th in threads:
         th.join()
     assert not errors, errors
+
+
+def test_i16_rows_extreme_values(gpu):
+    """int16 row reductions split x into bytes for dp2a: every corner of the 16-bit range, in
+    every position of a 16-byte vector, vectorised (aligned) and scalar (odd length) paths."""
+    specials = np.array([-32768, 32767, -1, 0, 1, 255, 256, -256, -255, 127, 128, -128, -129, 0x7F00, -0x7F00, 0x00FF],
+                        dtype=np.int16)
+    for cols in (16, 64, 1024, 1037):
+        reps = -(-cols // specials.size)
+        w = np.stack([np.tile(np.roll(specials, s), reps)[:cols] for s in range(16)]).astype(np.int16)
+        for shift in range(16):
+            x = np.tile(np.roll(specials, -shift), reps)[:cols].astype(np.int16)
+            y = np.empty(16, dtype=np.int32)
+            gpu.matmul_rmajor_i16_v(np.ascontiguousarray(w).reshape(-1), x, y, 16, cols)
+            assert np.array_equal(y, O.gemv_i16(np.ascontiguousarray(w).reshape(-1), x, 16, cols)), (cols, shift)
+            assert gpu.dot_i16_v(np.ascontiguousarray(w[3]), x, cols) == O.dot_i16(np.ascontiguousarray(w[3]), x)
