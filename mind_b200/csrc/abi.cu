@@ -552,20 +552,25 @@ int64_t dot(int kind, int64_t a, int64_t b, int64_t len) {
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return 0;
     std::lock_guard<std::mutex> lock(g_call_mutex);
-    int32_t result = 0;
+    // The kernel writes the scalar straight into mapped pinned memory: no staging, no copy back.
     Call call(ctx);
     const int ia = call.add((void*)a, (size_t)len * es, false);
     const int ib = call.add((void*)b, (size_t)len * es, false);
-    const int ir = call.add(&result, 4, true);  // a host operand: the call is synchronous
     if (call.begin() != 0) return 0;
+    int32_t* out = ctx->scalar_dev;
     int64_t st;
     if (kind == 0)
-        st = launch_gemv_q16(ctx, call.dev<int32_t>(ia), call.dev<int32_t>(ib), call.dev<int32_t>(ir), 1, len);
+        st = launch_gemv_q16(ctx, call.dev<int32_t>(ia), call.dev<int32_t>(ib), out, 1, len);
     else if (kind == 1)
-        st = launch_gemv_i16(ctx, call.dev<int16_t>(ia), call.dev<int16_t>(ib), call.dev<int32_t>(ir), 1, len);
+        st = launch_gemv_i16(ctx, call.dev<int16_t>(ia), call.dev<int16_t>(ib), out, 1, len);
     else
-        st = launch_dist_l1_q16(ctx, call.dev<int32_t>(ia), call.dev<int32_t>(ib), call.dev<int32_t>(ir), len);
+        st = launch_dist_l1_q16(ctx, call.dev<int32_t>(ia), call.dev<int32_t>(ib), out, len);
     if (st != 0 || call.end() != 0) return 0;
+    if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) {  // device operands: end() did not wait
+        fail(MIND_B200_ERR_CUDA, "synchronisation failed: %s", cudaGetErrorString(cudaGetLastError()));
+        return 0;
+    }
+    const int32_t result = *reinterpret_cast<volatile int32_t*>(ctx->scalar_host);
     return (int64_t)result;
 }
 

@@ -51,6 +51,8 @@ struct DeviceCtx {
     Arena staging;                  // device copies of host-pointer operands
     int* err_word = nullptr;        // word a kernel sets when a bounded wait runs out (device view)
     int* err_host = nullptr;        // the same word, host view (mapped pinned memory)
+    int* scalar_host = nullptr;     // where a kernel leaves a scalar result for the host (mapped pinned memory)
+    int32_t* scalar_dev = nullptr;  // the same word, device view
     // A second stream for work that runs beside the kernels on `stream` inside one call (forked
     // and joined with the two events).
     cudaStream_t side = nullptr;

@@ -86,13 +86,16 @@ DeviceCtx* current_ctx() {
     }
     // The error word lives in mapped pinned host memory: a kernel writes it only when a bounded
     // wait runs out, and the host reads it after a synchronisation without any copy per call.
-    if (cudaHostAlloc(&ctx->err_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
+    // (a second word of the same allocation receives scalar results: the dots)
+    if (cudaHostAlloc(&ctx->err_host, 2 * sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
         cudaHostGetDevicePointer(reinterpret_cast<void**>(&ctx->err_word), ctx->err_host, 0) != cudaSuccess) {
         fail(MIND_B200_ERR_CUDA, "could not allocate the device error word: %s",
              cudaGetErrorString(cudaGetLastError()));
         return nullptr;
     }
     *ctx->err_host = 0;
+    ctx->scalar_host = ctx->err_host + 1;
+    ctx->scalar_dev = reinterpret_cast<int32_t*>(ctx->err_word + 1);
     // made here, not on first use: a first use could fall inside a stream capture
     if (cudaStreamCreateWithFlags(&ctx->side, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreateWithFlags(&ctx->fork_ev, cudaEventDisableTiming) != cudaSuccess ||
