@@ -346,6 +346,20 @@ def latency_workloads(blas, torch, stream):
                                "us_per_call_cuda_graph": gus,
                                "batched_queries": {"queries": q, "as": f"gemm_q16 {m}x{k}x{q}", "us_per_call": batched,
                                                    "us_per_query": batched / q}}
+    # the int16 row kernel (matmul_rmajor_i16_v) at the GEMV configuration's shape: HBM-bound too
+    m = k = 16384
+    w16 = torch.empty(m * k, dtype=torch.int16, device="cuda")
+    x16 = torch.empty(k, dtype=torch.int16, device="cuda")
+    y16 = torch.empty(m, dtype=torch.int32, device="cuda")
+    seed = 0xDEADBEEF00000000 ^ ((m << 20) ^ k)
+    blas.lcg_fill(w16, m * k, KIND_I16, seed, 0, 0)
+    blas.lcg_fill(x16, k, KIND_I16, seed, m * k, 0)
+    us = per_call_us(lambda: blas.matmul_rmajor_i16_v(w16, x16, y16, m, k), 30)
+    peaks, src = measured_peaks()
+    gbs = (2.0 * m * k + 2 * k + 4 * m) / us / 1e3
+    out["gemv_i16"] = {"workload": f"gemv_i16 {m}x{k}", "us_per_call": us, "gb_s": gbs,
+                       "frac_of_hbm_peak": gbs / peaks["hbm_gbs"], "peak_source": f"{src} STREAM-style copy",
+                       "l2": "operands larger than L2"}
     return out
 
 
