@@ -143,11 +143,13 @@ rows_warp_kernel(const char* __restrict__ w, const void* __restrict__ x, int32_t
 template <int OP, bool VEC>
 __global__ void __launch_bounds__(512)
 rows_block_kernel(const char* __restrict__ w, const void* __restrict__ x, int32_t* __restrict__ y,
-                  int64_t rows, int64_t cols, int64_t row_bytes) {
+                  int64_t rows, int64_t cols, int64_t row_bytes, int64_t x_period) {
     __shared__ uint32_t part[16];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
-        uint32_t s = warp_sum(row_partial<OP, VEC>(w + r * row_bytes, x, cols, threadIdx.x, blockDim.x));
+        // x_period > 1: "row" r is piece r % x_period of a longer row, and meets that piece of x
+        const char* xr = static_cast<const char*>(x) + (x_period > 1 ? (r % x_period) * row_bytes : 0);
+        uint32_t s = warp_sum(row_partial<OP, VEC>(w + r * row_bytes, xr, cols, threadIdx.x, blockDim.x));
         if (lane == 0) part[wid] = s;
         __syncthreads();
         if (wid == 0) {
@@ -157,6 +159,16 @@ rows_block_kernel(const char* __restrict__ w, const void* __restrict__ x, int32_
         }
         __syncthreads();
     }
+}
+
+// y[r] = sum of the `parts` partial sums of row r (few, very long rows cut into pieces).
+__global__ void sum_parts_kernel(const int32_t* __restrict__ partial, int32_t* __restrict__ y, int64_t rows,
+                                 int parts) {
+    const int64_t r = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    uint32_t t = 0;
+    for (int p = 0; p < parts; ++p) t += (uint32_t)partial[r * parts + p];
+    y[r] = (int32_t)t;
 }
 
 // WPR warps share a row (interleaved 512-byte pieces), 16 / WPR rows per block per pass;
@@ -205,6 +217,18 @@ int64_t launch_rows(DeviceCtx* ctx, const void* w, const void* x, int32_t* y, in
     // and a persistent grid, 100 % this way).
     const int64_t nvec = cols / EPV;
     const int wpr = nvec >= 4096 ? 8 : (nvec >= 2048 ? 4 : (nvec >= 1024 ? 2 : 1));
+    // pieces per row for the few-long-rows case: a power of two that divides the row's vectors,
+    // leaves at least 4096 vectors (one batch of eight per thread) per piece and fills ~2 blocks per SM
+    int parts = 1;
+    if (by_block && vec)
+        while (parts < 256 && rows * parts * 2 <= (int64_t)sms * 2 && nvec % (parts * 2) == 0 &&
+               nvec / (parts * 2) >= 4096)
+            parts *= 2;
+    int32_t* partial = nullptr;
+    if (parts > 1) {
+        MB200_TRY(arena_reserve(ctx, ctx->scratch, (size_t)rows * parts * 4 + 1024));
+        partial = static_cast<int32_t*>(arena_take(ctx->scratch, (size_t)rows * parts * 4));
+    }
     prof_begin(ctx);
     if (vec && !by_block && wpr > 1) {
         const int64_t rpb = 16 / wpr;
@@ -216,12 +240,21 @@ int64_t launch_rows(DeviceCtx* ctx, const void* w, const void* x, int32_t* y, in
             rows_group_kernel<OP, true, 4><<<(unsigned)blocks, 512, 0, ctx->stream>>>(wc, x, y, rows, cols, row_bytes);
         else
             rows_group_kernel<OP, true, 2><<<(unsigned)blocks, 512, 0, ctx->stream>>>(wc, x, y, rows, cols, row_bytes);
+    } else if (by_block && parts > 1) {
+        // Few, very long rows (a long dot product is one row): each row is cut into `parts` equal
+        // pieces, one block per piece, and a second small kernel adds the pieces up in a fixed
+        // order - a single block per row would leave the other SMs idle.
+        const int64_t piece_cols = cols / parts;
+        rows_block_kernel<OP, true><<<(unsigned)(rows * parts), 512, 0, ctx->stream>>>(
+            wc, x, partial, rows * parts, piece_cols, piece_cols * ES, parts);
+        count_launch();
+        sum_parts_kernel<<<(unsigned)((rows + 127) / 128), 128, 0, ctx->stream>>>(partial, y, rows, parts);
     } else if (by_block) {
         const unsigned grid = (unsigned)rows;
         if (vec)
-            rows_block_kernel<OP, true><<<grid, 512, 0, ctx->stream>>>(wc, x, y, rows, cols, row_bytes);
+            rows_block_kernel<OP, true><<<grid, 512, 0, ctx->stream>>>(wc, x, y, rows, cols, row_bytes, 1);
         else
-            rows_block_kernel<OP, false><<<grid, 512, 0, ctx->stream>>>(wc, x, y, rows, cols, row_bytes);
+            rows_block_kernel<OP, false><<<grid, 512, 0, ctx->stream>>>(wc, x, y, rows, cols, row_bytes, 1);
     } else {
         int64_t blocks = (rows + 15) / 16;  // 16 warps per block, one row per warp, one pass
         if (blocks > (int64_t)sms * 64) blocks = (int64_t)sms * 64;

@@ -343,3 +343,26 @@ def test_pinned_host_operands_through_the_pipeline(gpu):
     hc = torch.full((m * n,), -1, dtype=torch.int32).pin_memory()
     gpu.matmul_mm_i8_v(ha, b, hc, m, k, n)               # B on the device
     assert torch.equal(hc, want.cpu())
+
+
+def test_few_very_long_rows(gpu):
+    """A long dot product is one row: it is cut into pieces, one block each, and the pieces are
+    added up in a fixed order.  Device and host operands, all three element kinds, and a length
+    that cannot be cut evenly (single-block path)."""
+    for n in (1 << 22, (1 << 22) + 4 * 37):
+        a = lcg_dev(gpu, n, 0, 77, shift=12)
+        b = lcg_dev(gpu, n, 0, 77, offset=n, shift=12)
+        ah, bh = a.cpu().numpy(), b.cpu().numpy()
+        assert gpu.dot_q16_v(a, b, n) == O.dot_q16(ah, bh), n
+        assert gpu.dot_l1_q16_v(a, b, n) == O.dot_l1_q16(ah, bh), n
+        assert gpu.dot_q16_v(ah, bh, n) == O.dot_q16(ah, bh), n
+    n = 1 << 23
+    a16 = lcg_dev(gpu, n, 2, 78)
+    b16 = lcg_dev(gpu, n, 2, 78, offset=n)
+    assert gpu.dot_i16_v(a16, b16, n) == O.dot_i16(a16.cpu().numpy(), b16.cpu().numpy())
+    rows, cols = 3, 1 << 21
+    w = lcg_dev(gpu, rows * cols, 0, 79, shift=12)
+    x = lcg_dev(gpu, cols, 0, 79, offset=rows * cols, shift=12)
+    y = torch.empty(rows, dtype=torch.int32, device="cuda")
+    gpu.gemv_q16_mt(w, x, y, rows, cols)
+    assert np.array_equal(y.cpu().numpy(), O.gemv_q16(w.cpu().numpy(), x.cpu().numpy(), rows, cols))
