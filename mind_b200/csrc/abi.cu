@@ -478,7 +478,8 @@ int64_t gemm_q16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t 
             // sequence (8 / 12 / 24 SMs: 170 / 133 / 127 us); from 1536^3 up the sequence is as fast
             // or faster (the tensor-core half is ~6 % of the work there and would idle its SMs).
             const double work = (double)m * (double)n * (double)k;
-            const int side_sms = g_q16_side_sms >= 0 ? g_q16_side_sms : (work <= 2147483648.0 ? 16 : 0);
+            // (not with a short K: there the outputs dominate, and side by side every output is an atomic)
+            const int side_sms = g_q16_side_sms >= 0 ? g_q16_side_sms : (work <= 2147483648.0 && k >= 512 ? 16 : 0);
             if (side_sms > 0 && side_sms < ctx->sm_count) {
                 MB200_CUDA(cudaMemsetAsync(dc, 0, (size_t)m * n * 4, ctx->stream));
                 MB200_CUDA(cudaEventRecord(ctx->fork_ev, ctx->stream));

@@ -73,7 +73,7 @@ struct Q16Smem {
 template <int BN, bool FULL>
 __global__ void __launch_bounds__(QTHREADS, 1)
 gemm_q16_fp64_kernel(const int32_t* __restrict__ a, const int32_t* __restrict__ b, int32_t* __restrict__ c,
-                     int m, int k, int n, int lda, int n_tiles, int k_steps, long long units) {
+                     int m, int k, int n, int lda, int n_tiles, int k_steps, long long units, int exclusive) {
     constexpr int TM = QBM / 16, TN = BN / 16;
     static_assert(TM % 4 == 0 && TN % 4 == 0, "register tile is built from 4-wide groups");
     extern __shared__ __align__(16) unsigned char q16_smem[];
@@ -191,15 +191,40 @@ gemm_q16_fp64_kernel(const int32_t* __restrict__ a, const int32_t* __restrict__ 
             __syncthreads();
         }
 
+        // A run that covers the tile's whole K, with no other kernel adding to c meanwhile, owns its
+        // outputs: plain 16-byte stores (FULL) or load-add-store (floor form).  Everything else adds
+        // with red.global.add.  With a short K nearly every run is of the first kind, and the
+        // scattered 4-byte atomics would otherwise cost several times the arithmetic.
+        const bool owns = exclusive && s_begin == 0 && s_end == k_steps;
+        const bool c_vec = (n % 4 == 0) && (reinterpret_cast<uintptr_t>(c) % 16 == 0);
 #pragma unroll
         for (int i = 0; i < TM; ++i) {
             const int r = row0 + (i / 4) * 64 + ty * 4 + (i % 4);
             if (r >= m) continue;
 #pragma unroll
-            for (int j = 0; j < TN; ++j) {
-                const int cc = col0 + (j / 4) * 64 + tx * 4 + (j % 4);
-                const uint32_t part = (uint32_t)__double2loint(facc[i][j]) + (FULL ? acc[i][j] : 0u);
-                if (cc < n) atomicAdd(reinterpret_cast<unsigned int*>(c) + (size_t)r * n + cc, part);
+            for (int g = 0; g < TN / 4; ++g) {
+                const int cc = col0 + g * 64 + tx * 4;
+                uint32_t part[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    part[j] = (uint32_t)__double2loint(facc[i][4 * g + j]) + (FULL ? acc[i][4 * g + j] : 0u);
+                unsigned int* dst = reinterpret_cast<unsigned int*>(c) + (size_t)r * n + cc;
+                if (owns && c_vec && cc + 3 < n) {
+                    uint4 o = make_uint4(part[0], part[1], part[2], part[3]);
+                    if (!FULL) {
+                        const uint4 old = *reinterpret_cast<const uint4*>(dst);
+                        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                    }
+                    *reinterpret_cast<uint4*>(dst) = o;
+                } else if (owns) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (cc + j < n) dst[j] = FULL ? part[j] : dst[j] + part[j];
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (cc + j < n) atomicAdd(dst + j, part[j]);
+                }
             }
         }
     }
@@ -207,7 +232,7 @@ gemm_q16_fp64_kernel(const int32_t* __restrict__ a, const int32_t* __restrict__ 
 
 template <int BN, bool FULL>
 int64_t launch_q16_streamk(DeviceCtx* ctx, const int32_t* a, const int32_t* b, int32_t* c, int64_t m, int64_t k,
-                           int64_t n, int max_blocks) {
+                           int64_t n, int max_blocks, bool exclusive) {
     if (m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff)
         return fail(MIND_B200_ERR_TOO_LARGE, "GEMM dimension above 2^31-1");
     constexpr int SMEM = (int)sizeof(Q16Smem<BN, FULL>);
@@ -228,7 +253,8 @@ int64_t launch_q16_streamk(DeviceCtx* ctx, const int32_t* a, const int32_t* b, i
         const unsigned grid = (unsigned)(units < cap ? units : cap);
         prof_begin(ctx);
         gemm_q16_fp64_kernel<BN, FULL><<<grid, QTHREADS, SMEM, ctx->stream>>>(
-            a + k0, b + k0 * n, c, (int)m, (int)kc, (int)n, (int)k, (int)n_tiles, (int)k_steps, (long long)units);
+            a + k0, b + k0 * n, c, (int)m, (int)kc, (int)n, (int)k, (int)n_tiles, (int)k_steps, (long long)units,
+            (exclusive && (FULL ? k0 == 0 : true)) ? 1 : 0);
         prof_end(ctx);
         count_launch();
         const int64_t rc = check_launch("gemm_q16_fp64_kernel");
@@ -247,14 +273,15 @@ bool gemm_q16_fp64_usable(const int32_t* a, const int32_t* b, int64_t k, int64_t
 // c = the whole product (c is zeroed here, then added to)
 int64_t launch_gemm_q16_fp64(DeviceCtx* ctx, const int32_t* a, const int32_t* b, int32_t* c, int64_t m,
                              int64_t k, int64_t n) {
-    return launch_q16_streamk<64, true>(ctx, a, b, c, m, k, n, 0);
+    return launch_q16_streamk<64, true>(ctx, a, b, c, m, k, n, 0, true);
 }
 
 // c += the floor half (c holds the linear half, or the linear half is being added beside this
 // kernel); max_blocks > 0 leaves the other SMs to that kernel
 int64_t launch_gemm_q16_floor_add(DeviceCtx* ctx, const int32_t* a, const int32_t* b, int32_t* c, int64_t m,
                                   int64_t k, int64_t n, int max_blocks) {
-    return launch_q16_streamk<128, false>(ctx, a, b, c, m, k, n, max_blocks);
+    // with max_blocks > 0 the tensor-core kernel adds onto c at the same time: atomics only
+    return launch_q16_streamk<128, false>(ctx, a, b, c, m, k, n, max_blocks, max_blocks <= 0);
 }
 
 }  // namespace mb200
