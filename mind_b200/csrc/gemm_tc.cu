@@ -7,7 +7,8 @@
 //                memory descriptors into TMEM accumulators, tcgen05.commit frees the
 //                stage ("empty" mbarrier) and finally publishes the accumulator;
 //   warps 2..5 : epilogue      - tcgen05.ld the accumulator (each warp its 32 TMEM
-//                lanes = 32 output rows), combine, store int32 to global.
+//                lanes = 32 output rows), combine, transpose 32 x 32 blocks through a
+//                shared-memory patch and store int32 rows to global, 128 bytes at a time.
 // Tiles are 128 rows of A by BLOCK_N rows of Bt by 128 bytes of K per stage.
 // MODE 0 (int8):  one s8 x s8 product, BLOCK_N = 256, two accumulator stages so the
 //                 epilogue of tile t overlaps the main loop of tile t + 1.
@@ -40,6 +41,7 @@ constexpr int UMMA_K = 32;              // K of one tcgen05.mma kind::i8
 constexpr int TC_THREADS = 192;
 constexpr int A_TILE_BYTES = BLOCK_M * BLOCK_K;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+constexpr int EPI_PATCH_WORDS = 32 * 33;  // per epilogue warp: a 32 x 32 block of outputs, padded rows
 
 template <int MODE, int PAIR>
 struct Cfg;
@@ -65,7 +67,6 @@ struct TcParams {
     int32_t* c;
     int m, n, k;
     int m_tiles, n_tiles;  // tile grid; an m-tile is PAIR * 128 rows
-    int vec_ok;            // C rows may be stored with 16-byte vectors
     int group_m;           // m-tiles walked together before moving on in n (L2 reuse of A panels)
     int hint_a, hint_b;    // L2 eviction policy per operand (see l2_policy)
     const int32_t* row_sums;  // int16 mode: sum of every row of A
@@ -136,6 +137,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
     const uint32_t tfull0 = bars + 16 * STAGES, tempty0 = tfull0 + 8 * ACC_STAGES;
     const uint32_t tmem_slot = tempty0 + 8 * ACC_STAGES;
     int* const misc = reinterpret_cast<int*>(smem_raw + (tmem_slot - raw));
+    const uint32_t patches0 = bars + 256;  // one 32 x 33-word patch per epilogue warp
     volatile int* const abort_s = misc + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -328,6 +330,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
     } else {
         // ---------------------------------------------------------------- epilogue
         const int q = warp & 3;  // TMEM lane quadrant this warp may read
+        uint32_t* const patch = reinterpret_cast<uint32_t*>(smem_raw + (patches0 - raw)) + (warp - 2) * EPI_PATCH_WORDS;
         uint32_t tcount = 0;
         for (int tile = tile_first; tile < total_tiles; tile += tile_step, ++tcount) {
             int tm, tn;
@@ -338,7 +341,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
             const int row = (tm * PAIR + (int)cta) * BLOCK_M + q * 32 + lane;
             const int col_tile = tn * BLOCK_N;
             const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + as * ACC_COLS;
-            int32_t* const crow = p.c + (size_t)row * (size_t)p.n;
             for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
                 if (col_tile + c0 >= p.n) break;  // warp-uniform
                 uint32_t v[32];
@@ -375,21 +377,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                             v[16 * h + j] = (hh[j] << 16) + ((hl[j] + lh[j]) << 8) + ll[j] + back;
                     }
                 }
-                if (row < p.m) {
-                    const int col = col_tile + c0;
-                    if (p.accumulate) {
+                // Lane = row in TMEM, but a store wants lane = column: the 32 x 32 block goes through
+                // this warp's shared-memory patch (row pitch 33 words: no bank conflicts either way),
+                // and every store / atomic instruction then covers one 128-byte line of a row.
+                // Straight from registers each lane wrote 16 bytes of a different row, which held
+                // output-bound shapes (short K) to a third of the write bandwidth.
+                __syncwarp();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col + j < p.n) atomicAdd(reinterpret_cast<unsigned int*>(crow) + col + j, v[j]);
-                    } else if (p.vec_ok && col + 32 <= p.n) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<uint4*>(crow + col + j) =
-                                make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col + j < p.n) crow[col + j] = (int32_t)v[j];
+                for (int j = 0; j < 32; ++j) patch[lane * 33 + j] = v[j];
+                __syncwarp();
+                const int col = col_tile + c0 + lane;
+                const int row_first = row - lane;
+                if (col < p.n) {
+                    int32_t* dst = p.c + (size_t)row_first * (size_t)p.n + col;
+#pragma unroll 8
+                    for (int r = 0; r < 32; ++r) {
+                        if (row_first + r >= p.m) break;  // warp-uniform
+                        const uint32_t x = patch[r * 33 + lane];
+                        if (p.accumulate)
+                            atomicAdd(reinterpret_cast<unsigned int*>(dst), x);
+                        else
+                            *dst = (int32_t)x;
+                        dst += p.n;
                     }
                 }
             }
@@ -465,7 +474,7 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     using cfg = Cfg<MODE, PAIR>;
     constexpr int B_ROWS = cfg::BLOCK_N / PAIR;
     constexpr int STAGE_BYTES = cfg::NA * A_TILE_BYTES + cfg::NB * B_ROWS * BLOCK_K;
-    constexpr int SMEM = cfg::STAGES * STAGE_BYTES + 1024 + 256;
+    constexpr int SMEM = cfg::STAGES * STAGE_BYTES + 1024 + 256 + 4 * EPI_PATCH_WORDS * 4;
     static_assert(SMEM <= 232448, "shared memory budget");
     if (m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff)
         return fail(MIND_B200_ERR_TOO_LARGE, "GEMM dimension above 2^31-1");
@@ -496,7 +505,6 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     p.k = (int)k;
     p.m_tiles = (int)((m + BLOCK_M * PAIR - 1) / (BLOCK_M * PAIR));
     p.n_tiles = (int)((n + cfg::BLOCK_N - 1) / cfg::BLOCK_N);
-    p.vec_ok = (n % 4 == 0) && (reinterpret_cast<uintptr_t>(c) % 16 == 0);
     p.row_sums = row_sums;
     p.accumulate = accumulate ? 1 : 0;
     p.err = ctx->err_word;
