@@ -71,6 +71,7 @@ struct TcParams {
     int hint_a, hint_b;    // L2 eviction policy per operand (see l2_policy)
     const int32_t* row_sums;  // int16 mode: sum of every row of A
     int accumulate;           // add onto C with red.global.add (C shared with a kernel running beside this one)
+    int k_splits;             // > 1: every tile's K range is cut into this many work items (accumulate is set, C zeroed)
     int* err;
 };
 
@@ -177,8 +178,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(misc);
 
-    const int total_tiles = p.m_tiles * p.n_tiles;
+    // Work items: (tile, split) with the split index fastest; a split is a contiguous range of
+    // k-blocks, never empty (the launcher sees to that).
+    const int total_tiles = p.m_tiles * p.n_tiles * p.k_splits;
     const int k_blocks = (p.k + BLOCK_K - 1) / BLOCK_K;
+    const int kb_per_split = (k_blocks + p.k_splits - 1) / p.k_splits;
     const int tile_step = gridDim.x / PAIR;
     const int tile_first = blockIdx.x / PAIR;
 
@@ -188,12 +192,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
             uint32_t it = 0;
             bool ok = true;
             const uint64_t pol_a = l2_policy(p.hint_a), pol_b = l2_policy(p.hint_b);
-            for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step) {
+            for (int item = tile_first; ok && item < total_tiles; item += tile_step) {
                 int tm, tn;
-                tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, tm, tn);
+                tile_coords(item / p.k_splits, p.m_tiles, p.n_tiles, p.group_m, tm, tn);
                 const int row_a = (tm * PAIR + (int)cta) * BLOCK_M;
                 const int row_b = tn * BLOCK_N + (int)cta * B_ROWS;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int kb0 = (item % p.k_splits) * kb_per_split;
+                const int kb1 = min(k_blocks, kb0 + kb_per_split);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
                     if (!wait_bounded(empty0 + 8 * s, ph ^ 1u, abort_s, p.err, 1)) {
                         ok = false;
@@ -262,12 +268,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
             constexpr uint64_t B_KSTEP = BMN ? (UMMA_K * 128) >> 4 : UMMA_K >> 4;
             uint32_t it = 0, tcount = 0;
             bool ok = true;
-            for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step, ++tcount) {
+            for (int item = tile_first; ok && item < total_tiles; item += tile_step, ++tcount) {
                 const uint32_t as = tcount % ACC_STAGES, aph = (tcount / ACC_STAGES) & 1u;
                 if (!wait_bounded(tempty0 + 8 * as, aph ^ 1u, abort_s, p.err, 2)) break;
                 tc_fence_after();
                 const uint32_t d0 = tmem_base + as * ACC_COLS;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int kb0 = (item % p.k_splits) * kb_per_split;
+                const int kb1 = min(k_blocks, kb0 + kb_per_split);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
                     if (!wait_bounded(full0 + 8 * s, ph, abort_s, p.err, 3)) {
                         ok = false;
@@ -280,7 +288,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                     const uint64_t db0 = BMN ? smem_desc_mn_sw128(sb, B_BOX_BYTES) : smem_desc_k_sw128(sb);
 #pragma unroll
                     for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks) {
-                        const uint32_t acc = (kb | ks) != 0 ? 1u : 0u;
+                        const uint32_t acc = (kb != kb0 || ks != 0) ? 1u : 0u;
                         const uint64_t koff = (uint64_t)((ks * UMMA_K) >> 4);
                         const uint64_t kb_off = (uint64_t)ks * B_KSTEP;
                         if (MODE == 0) {
@@ -332,9 +340,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
         const int q = warp & 3;  // TMEM lane quadrant this warp may read
         uint32_t* const patch = reinterpret_cast<uint32_t*>(smem_raw + (patches0 - raw)) + (warp - 2) * EPI_PATCH_WORDS;
         uint32_t tcount = 0;
-        for (int tile = tile_first; tile < total_tiles; tile += tile_step, ++tcount) {
+        for (int item = tile_first; item < total_tiles; item += tile_step, ++tcount) {
             int tm, tn;
-            tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, tm, tn);
+            tile_coords(item / p.k_splits, p.m_tiles, p.n_tiles, p.group_m, tm, tn);
+            const bool first_split = item % p.k_splits == 0;  // the int16 offset term goes in once
+            (void)first_split;
             const uint32_t as = tcount % ACC_STAGES, aph = (tcount / ACC_STAGES) & 1u;
             if (!wait_bounded(tfull0 + 8 * as, aph, abort_s, p.err, 4)) break;
             tc_fence_after();
@@ -363,7 +373,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                 } else {
                     // columns [0, N) hi.hi, [N, 2N) hi.lo', [2N, 3N) lo.hi, [3N, 4N) lo.lo' with
                     // lo' = lo - 128: 128 * (row sum of A) puts the 128 back (all mod 2^32)
-                    const uint32_t back = row < p.m ? 128u * (uint32_t)p.row_sums[row] : 0u;
+                    const uint32_t back = (row < p.m && first_split) ? 128u * (uint32_t)p.row_sums[row] : 0u;
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         uint32_t hh[16], hl[16], lh[16], ll[16];
@@ -524,7 +534,28 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
         done_for = ctx->device;
     }
     int units = ctx->sm_count / PAIR;  // CTAs (or CTA pairs) resident at once
-    if (total < units) units = (int)total;
+    // Fewer tiles than a quarter of the SMs and a long K: cut every tile's K range into splits, one work
+    // item each, all adding onto a zeroed C with red.global.add (sums mod 2^32 commute), so that a
+    // tall-and-skinny product (64 x 16384 x 64 is one tile) still uses the whole GPU.
+    int splits = 1;
+    const int64_t k_blocks = (k + BLOCK_K - 1) / BLOCK_K;
+    if (total * 4 <= units && k_blocks >= 16) {
+        int64_t want = units / total;
+        if (want > k_blocks / 4) want = k_blocks / 4;
+        if (want > 32) want = 32;
+        // below four splits the zeroing of C and the atomics cost what the split saves (1024^3)
+        if (want >= 4) {
+            const int64_t per = (k_blocks + want - 1) / want;
+            splits = (int)((k_blocks + per - 1) / per);  // no empty split
+        }
+    }
+    p.k_splits = splits;
+    if (splits > 1 && !p.accumulate) {
+        MB200_CUDA(cudaMemsetAsync(c, 0, (size_t)m * (size_t)n * 4, ctx->stream));
+        p.accumulate = 1;
+    }
+    const long long items = total * splits;
+    if (items < units) units = (int)items;
     if (max_ctas > 0 && PAIR == 1 && units > max_ctas) units = max_ctas;
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3((unsigned)(units * PAIR), 1, 1);

@@ -28,6 +28,8 @@ GEMM_SHAPES = [
     (127, 32, 129), (128, 128, 256), (129, 33, 255), (255, 127, 257), (256, 129, 128),
     (257, 130, 1), (1, 511, 257), (130, 513, 70), (128, 1, 256), (300, 256, 520),
     (5, 0, 9), (384, 1024, 512), (100, 2048, 36),
+    # few tiles, long K: every tile's K range is split across SMs and summed with atomics
+    (64, 4096, 64), (130, 3000, 40), (257, 1100, 300), (16, 16384, 16),
 ]
 PATHS = [3, 2, 1, 0, 4, 5]  # single CTA, CTA pairs, CUDA cores, auto, pairs / single with B transposed first
 
