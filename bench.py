@@ -98,6 +98,13 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
+    def wait_ready(self, timeout=6.0):
+        """nvidia-smi can take more than a second to print its first sample; the timed region
+        is a third of a second, so wait for the sampler before starting the work."""
+        t0 = time.perf_counter()
+        while self.proc and not self.lines and time.perf_counter() - t0 < timeout:
+            time.sleep(0.02)
+
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append((time.perf_counter(), line.strip()))
@@ -431,6 +438,7 @@ def run_mine(args, w):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()  # nvidia-smi takes a moment to come up: start it before the warm-up
+        sampler.wait_ready()
     for _ in range(args.warmup):
         if flush is not None:
             flush.fill_(1)
