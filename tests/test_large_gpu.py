@@ -272,6 +272,21 @@ def test_stability_reruns(gpu):
             if first is None:
                 first = c
             assert torch.equal(c, first), path
+    # tall-and-skinny: the K range of the single tile is split across SMs and summed with atomics
+    gpu.set_gemm_path(0)
+    m, k, n = 64, 8192, 64
+    at = lcg_dev(gpu, m * k, 1, seed)
+    bt = lcg_dev(gpu, k * n, 1, seed, offset=m * k)
+    want = torch.from_numpy(O.gemm_i8(at.cpu().numpy(), bt.cpu().numpy(), m, k, n)).cuda()
+    a16 = lcg_dev(gpu, m * k, 2, seed)
+    b16 = lcg_dev(gpu, k * n, 2, seed, offset=m * k)
+    want16 = torch.from_numpy(O.gemm_i16(a16.cpu().numpy(), b16.cpu().numpy(), m, k, n)).cuda()
+    for _ in range(128):
+        c = torch.empty(m * n, dtype=torch.int32, device="cuda")
+        gpu.matmul_mm_i8_v(at, bt, c, m, k, n)
+        assert torch.equal(c, want)
+        gpu.matmul_mm_i16(a16, b16, c, m, k, n)
+        assert torch.equal(c, want16)
 
 
 def test_cuda_graph_capture_and_replay(gpu):
