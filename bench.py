@@ -44,6 +44,9 @@ WORKLOADS = {
     "gemv_q16": dict(fn="gemv_q16_mt", m=16384, k=16384, n=1, kind=KIND_Q16, shift=15,
                      seed=0xDEADBEEF00000000 ^ ((16384 << 20) ^ 16384), metric="bit-exact Q16.16 GEMV bandwidth",
                      unit="GB/s", dtype="q16.16 (s32)", bound="hbm"),
+    "gemv_i16": dict(fn="matmul_rmajor_i16_v", m=16384, k=16384, n=1, kind=KIND_I16, shift=0,
+                     seed=0xDEADBEEF00000000 ^ ((16384 << 20) ^ 16384), metric="bit-exact int16 GEMV bandwidth",
+                     unit="GB/s", dtype="s16 x s16 -> s32 (dp2a on byte planes of x)", bound="hbm"),
 }
 ELEM_BYTES = {KIND_Q16: 4, KIND_I8: 1, KIND_I16: 2}
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel, one launch at the
@@ -55,7 +58,8 @@ NCU_TRAFFIC = {"gemm_i8": 5596628736 + 1057698048, "gemv_q16": 1073876000 + 3520
 def work_units(w, m):
     """Algorithmic work of one call over m rows, in the workload's unit numerator."""
     if w["unit"] == "GB/s":
-        return 4.0 * m * w["k"] + 4.0 * w["k"] + 4.0 * m  # matrix once + vector + output, bytes
+        es = {KIND_Q16: 4.0, KIND_I8: 1.0, KIND_I16: 2.0}[w["kind"]]
+        return es * m * w["k"] + es * w["k"] + 4.0 * m  # matrix once + vector + output, bytes
     return 2.0 * m * w["n"] * w["k"]                       # ops = 2 MKN
 
 
@@ -155,6 +159,8 @@ def cpu_call(w, a, b, rows, threads=0):
         return O.reference_gemv_q16(a, b, rows, k)
     if w["fn"] == "matmul_mm_q16_v":
         return O.baseline_gemm_q16(a, b, rows, k, n, threads)
+    if w["fn"] == "matmul_rmajor_i16_v":
+        return O.baseline_gemv_i16(a, b, rows, k, threads)
     return O.baseline_gemv_q16(a, b, rows, k, threads)
 
 
@@ -251,7 +257,7 @@ def quick_workload(name, blas, torch, stream, steps=30):
     blas.lcg_fill(a, m * k, kind, w["seed"], 0, w["shift"])
     blas.lcg_fill(b, k * n, kind, w["seed"], m * k, w["shift"])
     fn = getattr(blas, w["fn"])
-    call = (lambda: fn(a, b, c, m, k)) if w["fn"] == "gemv_q16_mt" else (lambda: fn(a, b, c, m, k, n))
+    call = (lambda: fn(a, b, c, m, k)) if n == 1 else (lambda: fn(a, b, c, m, k, n))
     flush = None
     if (m * k + k * n) * ELEM_BYTES[kind] <= 2 * L2_BYTES:
         flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device="cuda")
@@ -405,7 +411,7 @@ def run_mine(args, w):
     fn = getattr(blas, w["fn"])
 
     def step(pa, pb, pc):
-        if w["fn"] == "gemv_q16_mt":
+        if n == 1:
             fn(pa, pb, pc, rows, k)
         else:
             fn(pa, pb, pc, rows, k, n)
@@ -421,7 +427,10 @@ def run_mine(args, w):
             ah = a[s * k:(s + 2) * k].cpu().numpy()
             got = c[s * n:(s + 2) * n].cpu().numpy()
             want = {"matmul_mm_i8_v": O.gemm_i8, "matmul_mm_i16": O.gemm_i16, "matmul_mm_q16_v": O.gemm_q16}.get(w["fn"])
-            want = want(ah, bh, 2, k, n) if want else O.gemv_q16(ah, bh, 2, k)
+            if want:
+                want = want(ah, bh, 2, k, n)
+            else:
+                want = (O.gemv_i16 if w["kind"] == KIND_I16 else O.gemv_q16)(ah, bh, 2, k)
             if not np.array_equal(got, want):
                 raise SystemExit(f"rank {rank}: output differs from the oracle in rows {r0 + s}..{r0 + s + 2}; not timing a wrong kernel")
 
@@ -491,7 +500,7 @@ def run_mine(args, w):
     # Optional: the rank-ordered all-gather of the C bands over NCCL (not part of `value`: the
     # path needs no collective; reported so that "with the gather" can be read off too).
     gather_ms = None
-    if world > 1 and args.gather and w["fn"] != "gemv_q16_mt":
+    if world > 1 and args.gather and n > 1:
         from mind_b200.shard import all_gather_rows
         band_rows = -(-m // world)
         full = None
