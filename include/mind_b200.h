@@ -16,6 +16,13 @@
  * stream order).  Each pointer of a call is classified on its own, so host and
  * device operands may be mixed; a call with any host pointer is synchronous.
  *
+ * Several GPUs: like the reference's `_mt` entry points, which spread one call over the
+ * host's cores, a call whose operands are all HOST buffers is spread over the GPUs named
+ * by the environment variable MINDB200_DEVICES (a count, "4", or a list, "0,2,3"; default
+ * 1) or by mind_b200_set_devices: contiguous owner-computes bands of the M output rows,
+ * one per device, no reduction between them, so the bytes do not depend on the device
+ * count.  Calls with device pointers always run on the current device alone.
+ *
  * Results are bit-identical to the reference's rules: exact 64-bit sums truncated
  * once to int32 (two's-complement wrap, never saturation); Q16.16 products are
  * shifted right by 16 (arithmetic) BEFORE they are added.
@@ -89,19 +96,22 @@ int64_t __mind_b200_matmul_mm_i16(int64_t a, int64_t b, int64_t c, int64_t m, in
 
 /* ---- int8 GEMM that allocates nothing -----------------------------------------------------------
  * This entry point has no counterpart in the reference.  It is for hosts that cannot call
- * cudaMalloc when they need the product: a serving loop or stream callback where an allocation
- * (and the device synchronisation it may bring) is not allowed, or a process whose GPU memory is
- * wholly owned by another allocator.  Same rule, same kernels and same bytes as
- * __mind_blas_matmul_mm_i8_v, but the transposed B (and the padded A, when K % 16 != 0 or A is
- * not 16-byte aligned) live in a fixed array inside the library image instead of a buffer grown
- * with cudaMalloc, and no per-device context is created.  It calls no cudaMalloc, cudaFree,
- * cudaMallocHost or other allocating routine.
+ * cudaMalloc when they need the product: a serving loop in which an allocation (and the device
+ * synchronisation it may bring) is not allowed, or a process whose GPU memory is wholly owned
+ * by another allocator.  Same rule, same kernels and same bytes as __mind_blas_matmul_mm_i8_v,
+ * but the operand copies that call keeps in a buffer grown with cudaMalloc - B transposed, when
+ * N % 16 != 0 or B is not 16-byte aligned; A padded, when K % 16 != 0 or A is not 16-byte
+ * aligned - live in a fixed array inside the library image, and no per-device context is
+ * created.  It calls no cudaMalloc, cudaFree, cudaMallocHost or other allocating routine.
  *   - a, b, c must be DEVICE pointers of the current device (host operands would need staging
  *     memory); cuda_stream is the stream to run on (0 = legacy default stream).
- *   - limit: N*ceil16(K) + (M*ceil16(K) if A needs padding), each rounded up to 256 bytes, must
- *     not exceed MIND_B200_STATIC_SCRATCH_BYTES, else MIND_B200_ERR_TOO_LARGE.  Every GPU that
- *     loads the library holds that array until the process exits.
- *   - the call waits for its own work and then returns (it reports a kernel time-out itself).
+ *   - limit: (N*ceil16(K) if B needs transposing) + (M*ceil16(K) if A needs padding), each
+ *     rounded up to 256 bytes, must not exceed MIND_B200_STATIC_SCRATCH_BYTES, else
+ *     MIND_B200_ERR_TOO_LARGE; operands that TMA can read in place need no room.  Every GPU
+ *     that loads the library holds that array until the process exits.
+ *   - it is an ordinary synchronous host call: it waits for its own work (also when it fails
+ *     half way) and reports a kernel time-out itself.  Do not call it from a CUDA host callback
+ *     (cudaLaunchHostFunc), where CUDA calls are forbidden, nor on a stream being captured.
  *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress);
  *     make that first call before starting any stream capture on that device.
  *   - all calls share the one array, which keeps the previous call's contents (each call
@@ -134,7 +144,10 @@ int64_t gemmi8mt(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t 
 /* Message of the calling thread's last failure, or NULL (src/ffi/mod.rs:172-181). */
 const char* mind_b200_last_error(void);
 /* CUDA stream (cudaStream_t cast to int64_t; 0 = the legacy default stream) that every later
- * call on the CURRENT device uses.  Default: the legacy default stream. */
+ * call on the CURRENT device uses.  Default: the legacy default stream.  Device-pointer calls
+ * are asynchronous and share one scratch buffer per device, so the new stream is made to wait
+ * (by an event) for whatever the library has queued on the old one.  That ordering cannot be
+ * set up while either stream is being captured: there, synchronise before switching. */
 int64_t mind_b200_set_stream(int64_t cuda_stream);
 /* Blocks until the library's stream on the current device is idle; reports a kernel
  * time-out recorded since the last call (MindRuntime::synchronize, src/runtime_interface.rs:41). */
@@ -144,8 +157,25 @@ int64_t mind_b200_device_count(void);
 /* Kernels launched by this library in this process so far. */
 int64_t mind_b200_kernel_launches(void);
 /* Pre-sizes the current device's scratch (operand re-layouts) and staging (host operands)
- * buffers so that later calls allocate nothing. */
+ * buffers so that later calls allocate nothing.  CUDA graphs: a captured call records the
+ * scratch addresses it was given, so reserve the largest size (or run the largest shapes once)
+ * BEFORE capturing.  A call that would have to grow a buffer while its stream is being captured
+ * is refused with MIND_B200_ERR_INVALID (growing needs cudaMalloc and a wait); after a capture
+ * has been seen on a device, outgrown buffers are kept alive until mind_b200_shutdown, so that
+ * graphs captured earlier stay valid. */
 int64_t mind_b200_reserve(int64_t scratch_bytes, int64_t staging_bytes);
+/* How many GPUs a host-operand call may be spread over (1 = the current device only); overrides
+ * MINDB200_DEVICES.  The devices are ordinals 0 .. count-1 unless the variable gave a list.
+ * One persistent host thread per device is started on first use (the reference's pool does the
+ * same for cores, runtime-support/mind_intrinsics.c:1956-2046); fork() after that is unsupported. */
+int64_t mind_b200_set_devices(int64_t count);
+int64_t mind_b200_devices(void);
+/* Joins the device threads and frees everything the library holds on every GPU (scratch and
+ * staging buffers, streams, events, pinned words).  Also run by the library's destructor on
+ * dlclose() / exit, as the reference's runtime joins its pool
+ * (runtime-support/mind_intrinsics.c:2065-2081).  The library stays usable: the next call
+ * rebuilds what it needs.  No call may be in flight on another thread. */
+int64_t mind_b200_shutdown(void);
 /* Which kernel the int8 / int16 GEMMs use: 0 = tensor cores (tcgen05), the library picks
  * between its two kernels per call (default); 2 = tensor cores, one output tile per pair of
  * CTAs (cta_group::2); 3 = tensor cores, one CTA per tile; 4 / 5 = as 2 / 3 but B is always
@@ -154,9 +184,15 @@ int64_t mind_b200_reserve(int64_t scratch_bytes, int64_t staging_bytes);
  * (for Q16.16: the all-integer kernel); 6 / 7 = Q16.16 GEMM only: the FP64-pipe kernel alone /
  * the tensor-core hybrid at every size (default: hybrid from 2^29 products up, i.e. about 800^3);
  * 8 / 9 = the hybrid with its two halves one after the other / side by side on two streams
- * (default: side by side up to 2^31 products, where the tensor-core half is latency-bound).
- * Every path gives identical bytes. */
+ * (default: side by side up to 2^31 products, where the tensor-core half is latency-bound);
+ * 10 / 11 = int8 GEMM: the narrow-tile kernel (128 x 64 tiles, for products with few tiles)
+ * always / never (default: when the wide tiles would leave most SMs idle).
+ * Every path gives identical bytes.  The setting is process-wide and meant for tests and
+ * measurements; a call that is already running keeps the kernels it chose. */
 int64_t mind_b200_set_gemm_path(int64_t path);
+/* Measurement knob of the int8 GEMM's tile order: m-tiles walked together before moving on in
+ * N (0 = default) and the order variant (0 = default).  Every setting gives identical bytes. */
+int64_t mind_b200_set_tile_order(int64_t group_m, int64_t raster);
 /* Self-test of the bounded waits inside the GEMM kernels: launches a one-warp kernel that waits
  * (with the given limit, 1..1000 ms) on a barrier nothing will ever complete.  The expected
  * result is MIND_B200_ERR_TIMEOUT with the CUDA context still usable. */

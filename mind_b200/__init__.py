@@ -54,7 +54,8 @@ def lib() -> C.CDLL:
         for name, n in (("mind_b200_set_stream", 1), ("mind_b200_synchronize", 0),
                         ("mind_b200_device_count", 0), ("mind_b200_kernel_launches", 0),
                         ("mind_b200_reserve", 2), ("mind_b200_set_gemm_path", 1),
-                        ("mind_b200_profile", 1),
+                        ("mind_b200_profile", 1), ("mind_b200_set_devices", 1), ("mind_b200_devices", 0),
+                        ("mind_b200_shutdown", 0), ("mind_b200_set_tile_order", 2),
                         ("mind_b200_rt_deallocate", 1), ("mind_b200_rt_synchronize", 0)):
             f = getattr(L, name)
             f.argtypes, f.restype = [i64] * n, i64

@@ -135,6 +135,23 @@ def set_gemm_path(path: int) -> None:
     check(lib().mind_b200_set_gemm_path(int(path)))
 
 
+def set_tile_order(group_m: int, raster: int = 0) -> None:
+    check(lib().mind_b200_set_tile_order(int(group_m), int(raster)))
+
+
+def set_devices(count: int) -> None:
+    """GPUs a host-operand call is spread over (1 = the current device only)."""
+    check(lib().mind_b200_set_devices(int(count)))
+
+
+def devices() -> int:
+    return int(lib().mind_b200_devices())
+
+
+def shutdown() -> None:
+    check(lib().mind_b200_shutdown())
+
+
 KIND_Q16, KIND_I8, KIND_I16 = 0, 1, 2
 
 

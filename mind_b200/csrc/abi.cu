@@ -8,11 +8,9 @@
 namespace mb200 {
 namespace {
 
-std::mutex g_call_mutex;  // calls are serialised, like the reference's MT dispatch lock
-int g_gemm_path = 0;      // 0 = tensor cores, 1 = CUDA-core cross-check kernels
-bool g_force_transpose = false;  // tensor cores: always re-lay B out K-contiguous (testing)
-int g_q16_mode = 0;       // Q16.16 GEMM: 0 = pick by size, 6 = FP64-pipe kernel alone, 7 = tensor-core hybrid
-int g_q16_side_sms = -1;  // hybrid: SMs given to the tensor-core half beside the FP64 half (-1 = by size, 0 = in sequence)
+// Calls on one device are serialised by that device's lock (DeviceCtx::mu), like the
+// reference's MT dispatch lock; calls on different devices do not wait for each other.
+using DevLock = std::lock_guard<std::mutex>;
 
 // One operand of a call: where the caller keeps it and where the kernels see it.
 struct Operand {
@@ -93,14 +91,7 @@ public:
         return 0;
     }
 
-    static int64_t check_err_word(DeviceCtx* ctx) {
-        const int code = *ctx->err_host;
-        if (code == 0) return 0;
-        *ctx->err_host = 0;
-        return fail(MIND_B200_ERR_TIMEOUT,
-                    "a bounded wait inside the GEMM kernel ran out (role code %d); the output is invalid",
-                    code);
-    }
+    static int64_t check_err_word(DeviceCtx* ctx) { return ::mb200::check_err_word(ctx); }
 
 private:
     DeviceCtx* ctx_;
@@ -120,16 +111,10 @@ int64_t check_dims(int64_t m, int64_t k, int64_t n) {
 // on the library's stream.  Uploads alternate between B chunks and A bands; the first C tile
 // is on its way back after one of each has arrived, and after about two rounds the download
 // link stays busy.  C tiles are double-buffered in staging.
-struct Pipe {
-    cudaStream_t in = nullptr, out = nullptr;
-    cudaEvent_t start = nullptr, gemm_done[2] = {}, out_done[2] = {};
-    std::vector<cudaEvent_t> ready;  // uploads: A bands, then B chunks
-    bool made = false;
-};
-Pipe g_pipe[64];
+}  // namespace
 
 int64_t pipe_for(DeviceCtx* ctx, size_t n_ready, Pipe** out) {
-    Pipe& p = g_pipe[ctx->device];
+    Pipe& p = ctx->pipe;
     if (!p.made) {
         MB200_CUDA(cudaStreamCreateWithFlags(&p.in, cudaStreamNonBlocking));
         MB200_CUDA(cudaStreamCreateWithFlags(&p.out, cudaStreamNonBlocking));
@@ -138,6 +123,7 @@ int64_t pipe_for(DeviceCtx* ctx, size_t n_ready, Pipe** out) {
             MB200_CUDA(cudaEventCreateWithFlags(&p.gemm_done[i], cudaEventDisableTiming));
             MB200_CUDA(cudaEventCreateWithFlags(&p.out_done[i], cudaEventDisableTiming));
         }
+        MB200_CUDA(cudaEventCreateWithFlags(&p.b_ready, cudaEventDisableTiming));
         p.made = true;
     }
     while (p.ready.size() < n_ready) {
@@ -147,6 +133,14 @@ int64_t pipe_for(DeviceCtx* ctx, size_t n_ready, Pipe** out) {
     }
     *out = &p;
     return 0;
+}
+
+int64_t check_err_word(DeviceCtx* ctx) {
+    const int code = *ctx->err_host;
+    if (code == 0) return 0;
+    *ctx->err_host = 0;
+    return fail(MIND_B200_ERR_TIMEOUT,
+                "a bounded wait inside the GEMM kernel ran out (role code %d); the output is invalid", code);
 }
 
 // 1 = host, 0 = device of ctx, negative = error.
@@ -165,6 +159,8 @@ int64_t pointer_is_host(DeviceCtx* ctx, const void* p) {
     return at.type != cudaMemoryTypeManaged;
 }
 
+namespace {
+
 constexpr int64_t PIPE_MIN_ROWS = 1024;  // below this one band is as good as several
 
 int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const int8_t* b, bool b_host,
@@ -173,7 +169,7 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
     const int64_t band = (int64_t)align_up((size_t)((m + 7) / 8), 256);
     const int64_t bands = (m + band - 1) / band;
     // Column chunks only pay when C is downloaded, and need B readable in place per chunk.
-    const bool b_inplace_ok = !g_force_transpose && n % 16 == 0 && (b_host || reinterpret_cast<uintptr_t>(b) % 16 == 0);
+    const bool b_inplace_ok = !(tuning().force_transpose.load() != 0) && n % 16 == 0 && (b_host || reinterpret_cast<uintptr_t>(b) % 16 == 0);
     // Four, not more: a strided download slows down beside running kernels as its rows get shorter
     // (measured with a GEMM on another stream: 57 GB/s for 64 KiB rows, 48 for 16 KiB, 31 for 8 KiB).
     const int64_t chunks = (c_host && b_inplace_ok && n >= 4096 && n % 64 == 0) ? 4 : 1;
@@ -319,14 +315,12 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
 }
 
 // ------------------------------------------------------------------ GEMMs
-int64_t gemm_i8(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n) {
-    clear_error();
-    MB200_TRY(check_dims(m, k, n));
-    if (m == 0 || n == 0) return 0;
-    if (!c || (k > 0 && (!a || !b))) return fail(MIND_B200_ERR_INVALID, "null operand");
+// The *_local functions run one call on the CURRENT device (arguments already checked).
+int64_t gemm_i8_local(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n) {
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return MIND_B200_ERR_NO_DEVICE;
-    std::lock_guard<std::mutex> lock(g_call_mutex);
+    DevLock lock(ctx->mu);
+    const int g_gemm_path = tuning().gemm_path.load();
     if (k > 0 && g_gemm_path != 1 && m >= PIPE_MIN_ROWS) {
         const int64_t ah = pointer_is_host(ctx, (void*)a), bh = pointer_is_host(ctx, (void*)b),
                       ch = pointer_is_host(ctx, (void*)c);
@@ -351,7 +345,7 @@ int64_t gemm_i8(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n
         // B is read in place (N-contiguous tiles) when TMA can address it: 16-byte pitch and
         // base.  Otherwise it is transposed into K-contiguous scratch first.
         const int8_t* db = call.dev<int8_t>(ib);
-        const bool b_direct = !g_force_transpose && n % 16 == 0 && reinterpret_cast<uintptr_t>(db) % 16 == 0;
+        const bool b_direct = !(tuning().force_transpose.load() != 0) && n % 16 == 0 && reinterpret_cast<uintptr_t>(db) % 16 == 0;
         const size_t bt_bytes = b_direct ? 0 : (size_t)n * kp, ap_bytes = a_direct ? 0 : (size_t)m * kp;
         MB200_TRY(arena_reserve(ctx, ctx->scratch, align_up(bt_bytes, 1024) + align_up(ap_bytes, 1024) + 2048));
         int8_t* bt = b_direct ? nullptr : static_cast<int8_t*>(arena_take(ctx->scratch, bt_bytes));
@@ -369,15 +363,23 @@ int64_t gemm_i8(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n
     return call.end(true);
 }
 
-int64_t gemm_i16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n) {
+int64_t gemm_i8(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n) {
     clear_error();
     MB200_TRY(check_dims(m, k, n));
     if (m == 0 || n == 0) return 0;
     if (!c || (k > 0 && (!a || !b))) return fail(MIND_B200_ERR_INVALID, "null operand");
-    if ((a | b) & 1) return fail(MIND_B200_ERR_INVALID, "int16 operand is not 2-byte aligned");
+    if (k > 0 && tuning().gemm_path.load() != 1) {
+        const int64_t rc = multi_gemm_i8((const int8_t*)a, (const int8_t*)b, (int32_t*)c, m, k, n);
+        if (rc != MULTI_NOT_TAKEN) return rc;
+    }
+    return gemm_i8_local(a, b, c, m, k, n);
+}
+
+int64_t gemm_i16_local(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n) {
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return MIND_B200_ERR_NO_DEVICE;
-    std::lock_guard<std::mutex> lock(g_call_mutex);
+    DevLock lock(ctx->mu);
+    const int g_gemm_path = tuning().gemm_path.load();
     Call call(ctx);
     const int ia = call.add((void*)a, (size_t)m * k * 2, false);
     const int ib = call.add((void*)b, (size_t)k * n * 2, false);
@@ -392,7 +394,7 @@ int64_t gemm_i16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t 
         const int64_t np = (int64_t)align_up((size_t)n, 16);
         // B's limb planes keep B's own orientation ([K][np], N contiguous) unless a transposed B
         // is asked for (paths 4 / 5, and 2: the int16 kernel has no CTA-pair form).
-        const bool b_transposed = g_force_transpose || tc_pair_forced();
+        const bool b_transposed = (tuning().force_transpose.load() != 0) || tc_pair_forced();
         const size_t a_plane = align_up((size_t)m * kp, 1024);
         const size_t b_plane = align_up(b_transposed ? (size_t)n * kp : (size_t)k * np, 1024);
         const size_t sums = align_up((size_t)m * 4, 1024);
@@ -422,16 +424,29 @@ int64_t gemm_i16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t 
     return call.end(true);
 }
 
-// b_transposed: b is N x K (the identity gate's composition) instead of K x N.
-int64_t gemm_q16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n, bool b_transposed) {
+int64_t gemm_i16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n) {
     clear_error();
     MB200_TRY(check_dims(m, k, n));
     if (m == 0 || n == 0) return 0;
     if (!c || (k > 0 && (!a || !b))) return fail(MIND_B200_ERR_INVALID, "null operand");
-    if ((a | b | c) & 3) return fail(MIND_B200_ERR_INVALID, "int32 operand is not 4-byte aligned");
+    if ((a | b) & 1) return fail(MIND_B200_ERR_INVALID, "int16 operand is not 2-byte aligned");
+    if (k > 0) {
+        // row bands are independent (the reference's own thread-band rule): several devices
+        const int64_t rc = multi_banded(
+            (const void*)a, (size_t)k * 2, (const void*)b, (size_t)k * n * 2, (void*)c, (size_t)n * 4, m,
+            [=](const void* ab, void* cb, int64_t rows) { return gemm_i16_local((int64_t)ab, b, (int64_t)cb, rows, k, n); });
+        if (rc != MULTI_NOT_TAKEN) return rc;
+    }
+    return gemm_i16_local(a, b, c, m, k, n);
+}
+
+// b_transposed: b is N x K (the identity gate's composition) instead of K x N.
+int64_t gemm_q16_local(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n, bool b_transposed) {
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return MIND_B200_ERR_NO_DEVICE;
-    std::lock_guard<std::mutex> lock(g_call_mutex);
+    DevLock lock(ctx->mu);
+    const int g_gemm_path = tuning().gemm_path.load(), g_q16_mode = tuning().q16_mode.load(),
+              g_q16_side_sms = tuning().q16_side_sms.load();
     Call call(ctx);
     const int ia = call.add((void*)a, (size_t)m * k * 4, false);
     const int ib = call.add((void*)b, (size_t)k * n * 4, false);
@@ -516,18 +531,30 @@ int64_t gemm_q16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t 
     return call.end();
 }
 
+int64_t gemm_q16(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n, bool b_transposed) {
+    clear_error();
+    MB200_TRY(check_dims(m, k, n));
+    if (m == 0 || n == 0) return 0;
+    if (!c || (k > 0 && (!a || !b))) return fail(MIND_B200_ERR_INVALID, "null operand");
+    if ((a | b | c) & 3) return fail(MIND_B200_ERR_INVALID, "int32 operand is not 4-byte aligned");
+    if (k > 0) {
+        const int64_t rc = multi_banded(
+            (const void*)a, (size_t)k * 4, (const void*)b, (size_t)k * n * 4, (void*)c, (size_t)n * 4, m,
+            [=](const void* ab, void* cb, int64_t rows) {
+                return gemm_q16_local((int64_t)ab, b, (int64_t)cb, rows, k, n, b_transposed);
+            });
+        if (rc != MULTI_NOT_TAKEN) return rc;
+    }
+    return gemm_q16_local(a, b, c, m, k, n, b_transposed);
+}
+
 // ------------------------------------------------------------ row reductions
 // kind: 0 = Q16.16 matrix x vector, 1 = int16 matrix x vector.
-int64_t gemv(int kind, int64_t w, int64_t x, int64_t y, int64_t rows, int64_t cols) {
-    clear_error();
-    if (rows < 0 || cols < 0) return fail(MIND_B200_ERR_INVALID, "negative dimension");
-    if (rows == 0) return 0;
-    if (!y || (cols > 0 && (!w || !x))) return fail(MIND_B200_ERR_INVALID, "null operand");
+int64_t gemv_local(int kind, int64_t w, int64_t x, int64_t y, int64_t rows, int64_t cols) {
     const int es = kind == 0 ? 4 : 2;
-    if (((w | x) & (es - 1)) || (y & 3)) return fail(MIND_B200_ERR_INVALID, "misaligned operand");
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return MIND_B200_ERR_NO_DEVICE;
-    std::lock_guard<std::mutex> lock(g_call_mutex);
+    DevLock lock(ctx->mu);
     Call call(ctx);
     const int iw = call.add((void*)w, (size_t)rows * cols * es, false);
     const int ix = call.add((void*)x, (size_t)cols * es, false);
@@ -538,6 +565,22 @@ int64_t gemv(int kind, int64_t w, int64_t x, int64_t y, int64_t rows, int64_t co
     else
         MB200_TRY(launch_gemv_i16(ctx, call.dev<int16_t>(iw), call.dev<int16_t>(ix), call.dev<int32_t>(iy), rows, cols));
     return call.end();
+}
+
+int64_t gemv(int kind, int64_t w, int64_t x, int64_t y, int64_t rows, int64_t cols) {
+    clear_error();
+    if (rows < 0 || cols < 0) return fail(MIND_B200_ERR_INVALID, "negative dimension");
+    if (rows == 0) return 0;
+    if (!y || (cols > 0 && (!w || !x))) return fail(MIND_B200_ERR_INVALID, "null operand");
+    const int es = kind == 0 ? 4 : 2;
+    if (((w | x) & (es - 1)) || (y & 3)) return fail(MIND_B200_ERR_INVALID, "misaligned operand");
+    if (cols > 0) {
+        const int64_t rc = multi_banded(
+            (const void*)w, (size_t)cols * es, (const void*)x, (size_t)cols * es, (void*)y, 4, rows,
+            [=](const void* wb, void* yb, int64_t r) { return gemv_local(kind, (int64_t)wb, x, (int64_t)yb, r, cols); });
+        if (rc != MULTI_NOT_TAKEN) return rc;
+    }
+    return gemv_local(kind, w, x, y, rows, cols);
 }
 
 // kind: 0 = Q16.16 dot, 1 = int16 dot, 2 = Q16.16 L1 distance.  Returns the value;
@@ -552,7 +595,7 @@ int64_t dot(int kind, int64_t a, int64_t b, int64_t len) {
     }
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return 0;
-    std::lock_guard<std::mutex> lock(g_call_mutex);
+    DevLock lock(ctx->mu);
     // The kernel writes the scalar straight into mapped pinned memory: no staging, no copy back.
     Call call(ctx);
     const int ia = call.add((void*)a, (size_t)len * es, false);
@@ -612,8 +655,22 @@ int64_t mind_b200_set_stream(int64_t cuda_stream) {
     clear_error();
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return MIND_B200_ERR_NO_DEVICE;
-    std::lock_guard<std::mutex> lock(g_call_mutex);
-    ctx->stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+    DevLock lock(ctx->mu);
+    cudaStream_t next = reinterpret_cast<cudaStream_t>(cuda_stream);
+    if (next == ctx->stream) return 0;
+    // Device-pointer calls are asynchronous and share the per-device scratch, so work queued on
+    // the new stream must not start before what is still queued on the old one: the new stream
+    // waits for an event recorded on the old one.  Not while either is being captured (an event
+    // cannot cross a capture boundary): synchronise yourself before switching streams there.
+    cudaStreamCaptureStatus c0 = cudaStreamCaptureStatusNone, c1 = cudaStreamCaptureStatusNone;
+    const bool q0 = cudaStreamIsCapturing(ctx->stream, &c0) == cudaSuccess;
+    const bool q1 = cudaStreamIsCapturing(next, &c1) == cudaSuccess;
+    if (q0 && q1 && c0 == cudaStreamCaptureStatusNone && c1 == cudaStreamCaptureStatusNone) {
+        if (cudaEventRecord(ctx->order_ev, ctx->stream) == cudaSuccess)
+            cudaStreamWaitEvent(next, ctx->order_ev, 0);
+    }
+    cudaGetLastError();  // an old stream the caller has destroyed has nothing left to order after
+    ctx->stream = next;
     return 0;
 }
 
@@ -621,7 +678,7 @@ int64_t mind_b200_synchronize(void) {
     clear_error();
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return MIND_B200_ERR_NO_DEVICE;
-    std::lock_guard<std::mutex> lock(g_call_mutex);
+    DevLock lock(ctx->mu);
     MB200_CUDA(cudaStreamSynchronize(ctx->stream));
     return Call::check_err_word(ctx);
 }
@@ -634,7 +691,7 @@ int64_t mind_b200_reserve(int64_t scratch_bytes, int64_t staging_bytes) {
     if (scratch_bytes < 0 || staging_bytes < 0) return fail(MIND_B200_ERR_INVALID, "negative size");
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return MIND_B200_ERR_NO_DEVICE;
-    std::lock_guard<std::mutex> lock(g_call_mutex);
+    DevLock lock(ctx->mu);
     MB200_TRY(arena_reserve(ctx, ctx->scratch, (size_t)scratch_bytes));
     MB200_TRY(arena_reserve(ctx, ctx->staging, (size_t)staging_bytes));
     return 0;
@@ -642,18 +699,38 @@ int64_t mind_b200_reserve(int64_t scratch_bytes, int64_t staging_bytes) {
 
 int64_t mind_b200_set_gemm_path(int64_t path) {
     clear_error();
-    std::lock_guard<std::mutex> lock(g_call_mutex);
-    g_force_transpose = path == 4 || path == 5;
-    g_q16_mode = path == 6 ? 6 : (path >= 7 && path <= 9) ? 7 : 0;
-    g_q16_side_sms = path == 8 ? 0 : path == 9 ? 16 : -1;
-    switch (path) {
-        case 6: case 7: case 8: case 9: g_gemm_path = 0; return set_pair_mode(0);  // Q16.16 GEMM kernel choice only
-        case 0: g_gemm_path = 0; return set_pair_mode(0);  // tensor cores, kernel picked per call
-        case 1: g_gemm_path = 1; return set_pair_mode(0);  // CUDA cores
-        case 2: case 4: g_gemm_path = 0; return set_pair_mode(2);  // tensor cores, CTA pairs
-        case 3: case 5: g_gemm_path = 0; return set_pair_mode(1);  // tensor cores, one CTA per tile
-    }
-    return fail(MIND_B200_ERR_INVALID, "gemm path must be 0 (auto), 1 (CUDA cores), 2 / 3 (CTA pairs / single CTA), 4 / 5 (the same with B transposed first) 6 / 7 (Q16.16: FP64-pipe kernel alone / tensor-core hybrid) or 8 / 9 (the hybrid with its halves in sequence / side by side)");
+    if (path < 0 || path > 11)
+        return fail(MIND_B200_ERR_INVALID, "gemm path must be 0 (auto), 1 (CUDA cores), 2 / 3 (CTA pairs / single CTA), 4 / 5 (the same with B transposed first), 6 / 7 (Q16.16: FP64-pipe kernel alone / tensor-core hybrid), 8 / 9 (the hybrid with its halves in sequence / side by side) or 10 / 11 (int8: the narrow-tile kernel always / never)");
+    Tuning& t = tuning();
+    t.force_transpose = (path == 4 || path == 5) ? 1 : 0;
+    t.q16_mode = path == 6 ? 6 : (path >= 7 && path <= 9) ? 7 : 0;
+    t.q16_side_sms = path == 8 ? 0 : path == 9 ? 16 : -1;
+    t.small_tile = path == 10 ? 1 : (path == 0 ? -1 : 0);
+    t.gemm_path = path == 1 ? 1 : 0;
+    t.pair_mode = (path == 2 || path == 4) ? 2 : (path == 3 || path == 5) ? 1 : 0;
+    return 0;
+}
+
+int64_t mind_b200_set_tile_order(int64_t group_m, int64_t raster) {
+    clear_error();
+    if (group_m < 0 || group_m > 64 || raster < 0 || raster > 3) return fail(MIND_B200_ERR_INVALID, "bad tile order");
+    tuning().group_m = (int)group_m;
+    tuning().raster = (int)raster;
+    return 0;
+}
+
+int64_t mind_b200_set_devices(int64_t count) {
+    clear_error();
+    return multi_set_devices(count);
+}
+
+int64_t mind_b200_devices(void) { return multi_device_count(); }
+
+int64_t mind_b200_shutdown(void) {
+    clear_error();
+    multi_shutdown();
+    destroy_all_contexts();
+    return 0;
 }
 
 int64_t mind_b200_selftest_wait_timeout(int64_t limit_ms) {
@@ -661,7 +738,7 @@ int64_t mind_b200_selftest_wait_timeout(int64_t limit_ms) {
     if (limit_ms < 1 || limit_ms > 1000) return fail(MIND_B200_ERR_INVALID, "limit must be 1..1000 ms");
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return MIND_B200_ERR_NO_DEVICE;
-    std::lock_guard<std::mutex> lock(g_call_mutex);
+    DevLock lock(ctx->mu);
     MB200_TRY(launch_wait_selftest(ctx, limit_ms));
     MB200_CUDA(cudaStreamSynchronize(ctx->stream));
     return Call::check_err_word(ctx);
@@ -671,7 +748,7 @@ int64_t mind_b200_profile(int64_t enable) {
     clear_error();
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return MIND_B200_ERR_NO_DEVICE;
-    std::lock_guard<std::mutex> lock(g_call_mutex);
+    DevLock lock(ctx->mu);
     ctx->profile = enable != 0;
     ctx->prof_count = 0;
     return 0;
@@ -681,7 +758,7 @@ int64_t mind_b200_profile_read(int64_t* launches_out, double* total_ms_out) {
     clear_error();
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return MIND_B200_ERR_NO_DEVICE;
-    std::lock_guard<std::mutex> lock(g_call_mutex);
+    DevLock lock(ctx->mu);
     MB200_CUDA(cudaStreamSynchronize(ctx->stream));
     double total = 0.0;
     for (int i = 0; i < ctx->prof_count; ++i) {
@@ -702,7 +779,7 @@ int64_t mind_b200_lcg_fill(int64_t dst, int64_t n, int64_t kind, int64_t seed, i
     if (!dst) return fail(MIND_B200_ERR_INVALID, "null destination");
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return MIND_B200_ERR_NO_DEVICE;
-    std::lock_guard<std::mutex> lock(g_call_mutex);
+    DevLock lock(ctx->mu);
     const size_t es = kind == 0 ? 4 : (kind == 1 ? 1 : 2);
     Call call(ctx);
     const int id = call.add((void*)dst, (size_t)n * es, true);
@@ -719,7 +796,7 @@ int64_t mind_b200_matvec_wrap(int64_t mat, int64_t elem_bytes, int64_t rows, int
     if (elem_bytes != 1 && elem_bytes != 2 && elem_bytes != 4) return fail(MIND_B200_ERR_INVALID, "elem_bytes must be 1, 2 or 4");
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return MIND_B200_ERR_NO_DEVICE;
-    std::lock_guard<std::mutex> lock(g_call_mutex);
+    DevLock lock(ctx->mu);
     Call call(ctx);
     const int im = call.add((void*)mat, (size_t)rows * cols * elem_bytes, false);
     const int iv = call.add((void*)v, (size_t)cols * 4, false);

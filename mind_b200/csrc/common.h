@@ -7,7 +7,11 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include <atomic>
+#include <functional>
+#include <mutex>
 #include <string>
+#include <vector>
 
 #include "../../include/mind_b200.h"
 
@@ -19,7 +23,22 @@ void clear_error();
 const char* last_error_cstr();
 long long launches();
 int usable_device_count();
-int64_t set_pair_mode(int pair);
+
+// Process-wide kernel-choice knobs (mind_b200_set_gemm_path and friends).  They exist for tests
+// and measurements; each is an atomic read once per call, so a setter running beside a call on
+// another thread is a benign race: that call uses either the old or the new value, and every
+// value gives the same bytes.
+struct Tuning {
+    std::atomic<int> gemm_path{0};        // 0 = tensor cores, 1 = CUDA-core cross-check kernels
+    std::atomic<int> force_transpose{0};  // tensor cores: always re-lay B out K-contiguous
+    std::atomic<int> q16_mode{0};         // Q16.16 GEMM: 0 = by size, 6 = FP64-pipe kernel alone, 7 = hybrid
+    std::atomic<int> q16_side_sms{-1};    // hybrid: SMs of the tensor-core half beside the FP64 half (-1 = by size)
+    std::atomic<int> pair_mode{0};        // CTAs per int8 tile: 1, 2, or 0 = pick per call
+    std::atomic<int> small_tile{-1};      // int8 GEMM narrow-tile kernel: -1 = by shape, 0 = never, 1 = always
+    std::atomic<int> group_m{0};          // int8 tile order: m-tiles per group (0 = default)
+    std::atomic<int> raster{0};           // int8 tile order variant (0 = default)
+};
+Tuning& tuning();
 
 #define MB200_CUDA(expr)                                                                   \
     do {                                                                                   \
@@ -43,12 +62,31 @@ struct Arena {
     size_t used = 0;
 };
 
+// Streams and events of the host-operand pipelines (copies run beside the kernels): made on
+// first use, per device, and kept.
+struct Pipe {
+    cudaStream_t in = nullptr, out = nullptr;
+    cudaEvent_t start = nullptr, gemm_done[2] = {}, out_done[2] = {};
+    cudaEvent_t b_ready = nullptr;   // multi-device calls: this device's share of B has reached every peer
+    std::vector<cudaEvent_t> ready;  // uploads: A bands, then B chunks
+    bool made = false;
+};
+
 struct DeviceCtx {
     int device = -1;
     int sm_count = 0;
+    // Calls on one device are serialised by this lock (they share the arenas and the side
+    // streams); calls on different devices run side by side.
+    std::mutex mu;
     cudaStream_t stream = nullptr;  // the stream every launch and copy goes to
     Arena scratch;                  // operand re-layouts (transposed B, limb planes, padded A)
     Arena staging;                  // device copies of host-pointer operands
+    // Once a stream capture has been seen on this device, outgrown arena blocks are kept (a
+    // captured graph may still hold their addresses) and only freed at shutdown.
+    bool capture_seen = false;
+    std::vector<void*> retired;
+    cudaEvent_t order_ev = nullptr;  // orders a new library stream after the old one (set_stream)
+    Pipe pipe;
     int* err_word = nullptr;        // word a kernel sets when a bounded wait runs out (device view)
     int* err_host = nullptr;        // the same word, host view (mapped pinned memory)
     int* scalar_host = nullptr;     // where a kernel leaves a scalar result for the host (mapped pinned memory)
@@ -70,14 +108,37 @@ void prof_end(DeviceCtx* ctx);
 
 // Context of the CURRENT device (created on first use); nullptr + error set on failure.
 DeviceCtx* current_ctx();
+// Frees everything the library holds on every device (arenas, streams, events, mapped words).
+// Safe to call more than once; the contexts are rebuilt on the next call.
+void destroy_all_contexts();
 
 // Bump-allocates `bytes` (1024-byte aligned) from an arena, growing it if needed.
-// Growing frees the old block after a stream sync, so pointers handed out
-// earlier in the same call must be re-derived: reserve the total first.
+// Growing replaces the block (after a stream sync), so pointers handed out earlier in
+// the same call must be re-derived: reserve the total first.  Growth is refused while the
+// library's stream is being captured (it would need cudaMalloc and a synchronisation).
 int64_t arena_reserve(DeviceCtx* ctx, Arena& a, size_t total_bytes);
 void* arena_take(Arena& a, size_t bytes);
 inline void arena_reset(Arena& a) { a.used = 0; }
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// ---- host-operand pipelines and multi-device dispatch (abi.cu, multi.cu) ----
+int64_t pipe_for(DeviceCtx* ctx, size_t n_ready, Pipe** out);
+int64_t check_err_word(DeviceCtx* ctx);
+// 1 = host memory, 0 = memory of ctx's device, negative = error (memory of another device).
+int64_t pointer_is_host(DeviceCtx* ctx, const void* p);
+// Returned by the multi_* functions when the call should run on the current device alone.
+constexpr int64_t MULTI_NOT_TAKEN = INT64_MIN;
+int multi_device_count();
+int64_t multi_set_devices(int64_t count);
+void multi_shutdown();
+// int8 GEMM with host operands over several devices: device g owns row band g of A and C; B
+// goes up once in K-slices, one per device, and the devices pass the slices on to each other.
+int64_t multi_gemm_i8(const int8_t* a, const int8_t* b, int32_t* c, int64_t m, int64_t k, int64_t n);
+// Any row-banded call with host operands: `band(a_band, c_band, rows)` runs on each device with
+// that device current (a: rows of a_row_bytes, c: rows of c_row_bytes, `shared` is read by all).
+int64_t multi_banded(const void* a, size_t a_row_bytes, const void* shared, size_t shared_bytes, void* c,
+                     size_t c_row_bytes, int64_t m,
+                     const std::function<int64_t(const void*, void*, int64_t)>& band);
 
 // Kernel launch accounting (reported through mind_b200_kernel_launches()).
 void count_launch(int n = 1);

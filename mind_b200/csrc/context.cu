@@ -14,9 +14,18 @@ thread_local std::string t_error;
 thread_local bool t_has_error = false;
 std::atomic<long long> g_launches{0};
 constexpr int MAX_DEVICES = 64;
-DeviceCtx g_ctx[MAX_DEVICES];
+// The context table lives on the heap and is never destroyed by a static destructor: the
+// library's own destructor (which runs after the static ones at process exit) still walks it.
+DeviceCtx* g_ctx = nullptr;
 std::mutex g_ctx_mutex;
+Tuning g_tuning;
+DeviceCtx* ctx_table() {  // call with g_ctx_mutex held
+    if (!g_ctx) g_ctx = new DeviceCtx[MAX_DEVICES];
+    return g_ctx;
+}
 }  // namespace
+
+Tuning& tuning() { return g_tuning; }
 
 int64_t fail(int64_t code, const char* fmt, ...) {
     char buf[512];
@@ -72,7 +81,7 @@ DeviceCtx* current_ctx() {
         return nullptr;
     }
     std::lock_guard<std::mutex> lock(g_ctx_mutex);
-    DeviceCtx* ctx = &g_ctx[dev];
+    DeviceCtx* ctx = &ctx_table()[dev];
     if (ctx->device == dev) return ctx;
     int major = 0, minor = 0, sms = 0;
     cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
@@ -99,7 +108,8 @@ DeviceCtx* current_ctx() {
     // made here, not on first use: a first use could fall inside a stream capture
     if (cudaStreamCreateWithFlags(&ctx->side, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreateWithFlags(&ctx->fork_ev, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&ctx->join_ev, cudaEventDisableTiming) != cudaSuccess) {
+        cudaEventCreateWithFlags(&ctx->join_ev, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&ctx->order_ev, cudaEventDisableTiming) != cudaSuccess) {
         fail(MIND_B200_ERR_CUDA, "could not create the side stream: %s", cudaGetErrorString(cudaGetLastError()));
         return nullptr;
     }
@@ -111,10 +121,29 @@ DeviceCtx* current_ctx() {
 
 int64_t arena_reserve(DeviceCtx* ctx, Arena& a, size_t total_bytes) {
     a.used = 0;
+    // A captured graph keeps the addresses it was recorded with.  So: never allocate or wait
+    // while the stream is being captured, and once a capture has been seen on this device keep
+    // every outgrown block alive (until shutdown) instead of freeing it.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(ctx->stream, &cap) != cudaSuccess) {
+        cudaGetLastError();
+        cap = cudaStreamCaptureStatusNone;
+    }
+    const bool capturing = cap != cudaStreamCaptureStatusNone;
+    if (capturing) ctx->capture_seen = true;
     if (total_bytes <= a.cap) return 0;
+    if (capturing)
+        return fail(MIND_B200_ERR_INVALID,
+                    "this call needs %zu bytes of library scratch but only %zu are reserved, and the stream is "
+                    "being captured: call mind_b200_reserve (or run the same shapes once) before the capture",
+                    total_bytes, a.cap);
     if (a.base) {
-        MB200_CUDA(cudaStreamSynchronize(ctx->stream));
-        MB200_CUDA(cudaFree(a.base));
+        if (ctx->capture_seen) {
+            ctx->retired.push_back(a.base);
+        } else {
+            MB200_CUDA(cudaStreamSynchronize(ctx->stream));
+            MB200_CUDA(cudaFree(a.base));
+        }
         a.base = nullptr;
         a.cap = 0;
     }
@@ -138,6 +167,57 @@ void* arena_take(Arena& a, size_t bytes) {
     return a.base + off;
 }
 
+// Every CUDA call below may fail with "driver shutting down" when this runs from the library's
+// destructor at process exit; the results are ignored on purpose.
+void destroy_all_contexts() {
+    std::lock_guard<std::mutex> lock(g_ctx_mutex);
+    if (!g_ctx) return;
+    int before = -1;
+    const bool have_dev = cudaGetDevice(&before) == cudaSuccess;
+    for (int d = 0; d < MAX_DEVICES; ++d) {
+        DeviceCtx* ctx = &g_ctx[d];
+        if (ctx->device != d) continue;
+        std::lock_guard<std::mutex> dev_lock(ctx->mu);
+        if (cudaSetDevice(d) == cudaSuccess) {
+            cudaDeviceSynchronize();
+            if (ctx->scratch.base) cudaFree(ctx->scratch.base);
+            if (ctx->staging.base) cudaFree(ctx->staging.base);
+            for (void* p : ctx->retired) cudaFree(p);
+            if (ctx->err_host) cudaFreeHost(ctx->err_host);
+            if (ctx->side) cudaStreamDestroy(ctx->side);
+            for (cudaEvent_t e : {ctx->fork_ev, ctx->join_ev, ctx->order_ev})
+                if (e) cudaEventDestroy(e);
+            for (cudaEvent_t& e : ctx->prof_ev)
+                if (e) {
+                    cudaEventDestroy(e);
+                    e = nullptr;
+                }
+            Pipe& p = ctx->pipe;
+            if (p.in) cudaStreamDestroy(p.in);
+            if (p.out) cudaStreamDestroy(p.out);
+            for (cudaEvent_t e : {p.start, p.gemm_done[0], p.gemm_done[1], p.out_done[0], p.out_done[1], p.b_ready})
+                if (e) cudaEventDestroy(e);
+            for (cudaEvent_t e : p.ready) cudaEventDestroy(e);
+        }
+        cudaGetLastError();
+        ctx->scratch = Arena();
+        ctx->staging = Arena();
+        ctx->retired.clear();
+        ctx->err_host = ctx->err_word = ctx->scalar_host = nullptr;
+        ctx->scalar_dev = nullptr;
+        ctx->side = nullptr;
+        ctx->fork_ev = ctx->join_ev = ctx->order_ev = nullptr;
+        ctx->pipe = Pipe();
+        ctx->stream = nullptr;
+        ctx->profile = false;
+        ctx->prof_count = 0;
+        ctx->capture_seen = false;
+        ctx->device = -1;  // rebuilt on the next call
+    }
+    if (have_dev) cudaSetDevice(before);
+    cudaGetLastError();
+}
+
 void prof_begin(DeviceCtx* ctx) {
     if (!ctx->profile || ctx->prof_count >= DeviceCtx::PROF_RING) return;
     cudaEvent_t& e = ctx->prof_ev[2 * ctx->prof_count];
@@ -152,6 +232,13 @@ void prof_end(DeviceCtx* ctx) {
     if (!ctx->profile || ctx->prof_count >= DeviceCtx::PROF_RING) return;
     cudaEventRecord(ctx->prof_ev[2 * ctx->prof_count + 1], ctx->stream);
     ++ctx->prof_count;
+}
+
+// dlclose() and process exit: join the device threads, then give back what the library holds on
+// every GPU (the reference joins its pool the same way, runtime-support/mind_intrinsics.c:2065-2081).
+__attribute__((destructor)) static void library_unload() {
+    multi_shutdown();
+    destroy_all_contexts();
 }
 
 EncodeTiledFn encode_tiled_fn() {

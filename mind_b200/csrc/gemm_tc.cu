@@ -21,6 +21,11 @@
 //                 wrap, which equals the exact sum truncated to 32 bits.  Wrap inside
 //                 an accumulator is harmless (the tensor core does not saturate:
 //                 descriptor bit 3 is 0).  One CTA per tile.
+// MODE 3 (int8, narrow tiles): the same product with BLOCK_N = 64 and four small accumulator
+//                 stages, for shapes whose 128 x 256 tiles would leave most SMs idle (256^3 is
+//                 two such tiles but eight narrow ones, each with a quarter of the epilogue).
+//                 A B that is read in place arrives as TMA boxes of 64 bytes of N by 128 rows of
+//                 K with the 64-byte swizzle, the canonical MN-major layout of a 64-wide operand.
 // The PAIR = 2 variant (int8) runs one tile on a pair of CTAs (a 2-CTA cluster,
 // tcgen05 cta_group::2): 256 rows of A (128 per CTA) by BLOCK_N rows of Bt, of which
 // each CTA stages only its half, which halves the shared-memory traffic per MMA.
@@ -47,20 +52,24 @@ template <int MODE, int PAIR>
 struct Cfg;
 template <>
 struct Cfg<0, 1> {
-    static constexpr int BLOCK_N = 256, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 2, STAGES = 4;
+    static constexpr int BLOCK_N = 256, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 2, STAGES = 4, TMEM_COLS = 512;
 };
 template <>
 struct Cfg<1, 1> {  // int16: two accumulators of 2 x BLOCK_N columns (A high / A low times [B high | B low])
-    static constexpr int BLOCK_N = 128, NA = 2, NB = 2, NACC = 4, ACC_STAGES = 1, STAGES = 3;
+    static constexpr int BLOCK_N = 128, NA = 2, NB = 2, NACC = 4, ACC_STAGES = 1, STAGES = 3, TMEM_COLS = 512;
 };
 template <>
 struct Cfg<0, 2> {
-    static constexpr int BLOCK_N = 256, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 2, STAGES = 6;
+    static constexpr int BLOCK_N = 256, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 2, STAGES = 6, TMEM_COLS = 512;
 };
 
 template <>
 struct Cfg<2, 1> {  // linear part of the Q16.16 product: a (4 limbs) x bh (2 limbs), 4 accumulators
-    static constexpr int BLOCK_N = 128, NA = 4, NB = 2, NACC = 4, ACC_STAGES = 1, STAGES = 2;
+    static constexpr int BLOCK_N = 128, NA = 4, NB = 2, NACC = 4, ACC_STAGES = 1, STAGES = 2, TMEM_COLS = 512;
+};
+template <>
+struct Cfg<3, 1> {  // int8, narrow tiles
+    static constexpr int BLOCK_N = 64, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 4, STAGES = 4, TMEM_COLS = 256;
 };
 
 struct TcParams {
@@ -68,6 +77,7 @@ struct TcParams {
     int m, n, k;
     int m_tiles, n_tiles;  // tile grid; an m-tile is PAIR * 128 rows
     int group_m;           // m-tiles walked together before moving on in n (L2 reuse of A panels)
+    int raster;            // 1: odd groups walk n backwards, so a group starts on the B panels the last one ended on
     int hint_a, hint_b;    // L2 eviction policy per operand (see l2_policy)
     const int32_t* row_sums;  // int16 mode: sum of every row of A
     int accumulate;           // add onto C with red.global.add (C shared with a kernel running beside this one)
@@ -94,8 +104,8 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
     }
 }
 
-__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int group_m, int& tm,
-                                            int& tn) {
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int group_m, int raster,
+                                            int& tm, int& tn) {
     const int per_group = group_m * n_tiles;
     const int g = tile / per_group;
     const int r = tile - g * per_group;
@@ -103,6 +113,7 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
     const int gsize = min(group_m, m_tiles - gm0);
     tm = gm0 + r % gsize;
     tn = r / gsize;
+    if (raster == 1 && (g & 1)) tn = n_tiles - 1 - tn;
 }
 
 // BMN = false: B is given transposed (Bt[N][K], K contiguous).  BMN = true: B is used as the
@@ -116,17 +127,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                const TcParams p) {
     static_assert(MODE != 2 || (PAIR == 1 && BMN), "the Q16.16 linear-part mode is single-CTA, B in place");
     static_assert(MODE != 1 || PAIR == 1, "the int16 mode is single-CTA");
+    static_assert(MODE != 3 || PAIR == 1, "the narrow-tile mode is single-CTA");
     using cfg = Cfg<MODE, PAIR>;
     constexpr int BLOCK_N = cfg::BLOCK_N;
     constexpr int B_ROWS = BLOCK_N / PAIR;  // columns of the output (rows of Bt) this CTA stages
     constexpr int B_TILE_BYTES = B_ROWS * BLOCK_K;
-    static_assert(!BMN || B_ROWS % 128 == 0, "an MN-major B tile is made of 128-column boxes");
-    constexpr int B_BOX_BYTES = 128 * BLOCK_K;  // one MN-major box: 128 columns x 128 rows of K
+    // An MN-major B tile is made of boxes of BOX_N columns x 128 rows of K: 128 columns with the
+    // 128-byte swizzle, or the whole 64-column tile with the 64-byte swizzle.
+    constexpr int BOX_N = B_ROWS < 128 ? B_ROWS : 128;
+    static_assert(!BMN || B_ROWS % BOX_N == 0, "an MN-major B tile is made of whole boxes");
+    static_assert(BOX_N == 128 || BOX_N == 64, "box width = swizzle width");
+    constexpr int B_BOX_BYTES = BOX_N * BLOCK_K;  // one MN-major box
     constexpr int STAGE_BYTES = cfg::NA * A_TILE_BYTES + cfg::NB * B_TILE_BYTES;
     constexpr int STAGES = cfg::STAGES;
     constexpr int ACC_STAGES = cfg::ACC_STAGES;
     constexpr int ACC_COLS = cfg::NACC * BLOCK_N;  // TMEM columns per accumulator stage
-    constexpr int TMEM_COLS = 512;
+    constexpr int TMEM_COLS = cfg::TMEM_COLS;
     static_assert(ACC_COLS * ACC_STAGES <= TMEM_COLS, "TMEM overflow");
     constexpr int UMMA_M = BLOCK_M * PAIR;
 
@@ -194,7 +210,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
             const uint64_t pol_a = l2_policy(p.hint_a), pol_b = l2_policy(p.hint_b);
             for (int item = tile_first; ok && item < total_tiles; item += tile_step) {
                 int tm, tn;
-                tile_coords(item / p.k_splits, p.m_tiles, p.n_tiles, p.group_m, tm, tn);
+                tile_coords(item / p.k_splits, p.m_tiles, p.n_tiles, p.group_m, p.raster, tm, tn);
                 const int row_a = (tm * PAIR + (int)cta) * BLOCK_M;
                 const int row_b = tn * BLOCK_N + (int)cta * B_ROWS;
                 const int kb0 = (item % p.k_splits) * kb_per_split;
@@ -222,10 +238,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                             if (cfg::NB == 2) tma_load_2d(db + B_TILE_BYTES, &tm_b1, bar, kx, row_b, pol_b);
                         } else {
 #pragma unroll
-                            for (int j = 0; j < B_ROWS / 128; ++j) {
-                                tma_load_2d(db + j * B_BOX_BYTES, &tm_b0, bar, row_b + 128 * j, kx, pol_b);
+                            for (int j = 0; j < B_ROWS / BOX_N; ++j) {
+                                tma_load_2d(db + j * B_BOX_BYTES, &tm_b0, bar, row_b + BOX_N * j, kx, pol_b);
                                 if (cfg::NB == 2)
-                                    tma_load_2d(db + B_TILE_BYTES + j * B_BOX_BYTES, &tm_b1, bar, row_b + 128 * j, kx, pol_b);
+                                    tma_load_2d(db + B_TILE_BYTES + j * B_BOX_BYTES, &tm_b1, bar, row_b + BOX_N * j, kx, pol_b);
                             }
                         }
                     } else if (BMN) {
@@ -265,7 +281,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
             constexpr uint32_t ID_UU = idesc_i8(UMMA_M, BLOCK_N, false, false, BMN);
             // Descriptor step per MMA (32 of K): 32 bytes along a K-major row, or 32 K-rows of
             // 128 bytes in an MN-major tile; in units of 16 bytes.
-            constexpr uint64_t B_KSTEP = BMN ? (UMMA_K * 128) >> 4 : UMMA_K >> 4;
+            constexpr uint64_t B_KSTEP = BMN ? (UMMA_K * BOX_N) >> 4 : UMMA_K >> 4;
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             for (int item = tile_first; ok && item < total_tiles; item += tile_step, ++tcount) {
@@ -285,13 +301,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                     const uint32_t sa = tiles0 + s * STAGE_BYTES;
                     const uint32_t sb = sa + cfg::NA * A_TILE_BYTES;
                     const uint64_t da0 = smem_desc_k_sw128(sa);
-                    const uint64_t db0 = BMN ? smem_desc_mn_sw128(sb, B_BOX_BYTES) : smem_desc_k_sw128(sb);
+                    const uint64_t db0 = !BMN ? smem_desc_k_sw128(sb)
+                                         : BOX_N == 128 ? smem_desc_mn_sw128(sb, B_BOX_BYTES) : smem_desc_mn_sw64(sb);
 #pragma unroll
                     for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks) {
                         const uint32_t acc = (kb != kb0 || ks != 0) ? 1u : 0u;
                         const uint64_t koff = (uint64_t)((ks * UMMA_K) >> 4);
                         const uint64_t kb_off = (uint64_t)ks * B_KSTEP;
-                        if (MODE == 0) {
+                        if (MODE == 0 || MODE == 3) {
                             mma_i8<PAIR>(d0, da0 + koff, db0 + kb_off, ID_SS, acc);
                         } else if (MODE == 2) {
                             // a = a3*2^24 + a2*2^16 + a1*2^8 + a0 (a3 signed), bh = bh1*256 + bh0 (bh1
@@ -342,7 +359,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
         uint32_t tcount = 0;
         for (int item = tile_first; item < total_tiles; item += tile_step, ++tcount) {
             int tm, tn;
-            tile_coords(item / p.k_splits, p.m_tiles, p.n_tiles, p.group_m, tm, tn);
+            tile_coords(item / p.k_splits, p.m_tiles, p.n_tiles, p.group_m, p.raster, tm, tn);
             const bool first_split = item % p.k_splits == 0;  // the int16 offset term goes in once
             (void)first_split;
             const uint32_t as = tcount % ACC_STAGES, aph = (tcount / ACC_STAGES) & 1u;
@@ -354,7 +371,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
             for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
                 if (col_tile + c0 >= p.n) break;  // warp-uniform
                 uint32_t v[32];
-                if (MODE == 0) {
+                if (MODE == 0 || MODE == 3) {
                     tmem_ld32(t0 + c0, v);
                     tmem_ld_wait();
                 } else if (MODE == 2) {
@@ -455,24 +472,24 @@ __global__ void wait_selftest_kernel(int* err, unsigned long long limit_ns) {
 // 2-D map over a row-major 8-bit matrix [rows][k] with row pitch `pitch` bytes; the
 // box is 128 bytes of K by `box_rows` rows, written to shared memory with the
 // 128-byte swizzle.  Reads past `k` or `rows` return zeros.
+// box_bytes = 64 makes boxes of 64 bytes with the 64-byte swizzle instead (narrow MN-major B tiles).
 int64_t make_tmap(CUtensorMap* tm, const void* base, int64_t k, int64_t rows, int64_t pitch,
-                  int box_rows) {
+                  int box_rows, int box_bytes = BLOCK_K) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return fail(MIND_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)pitch};
-    cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+    cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
-                     estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     box_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(MIND_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (k=%lld rows=%lld pitch=%lld)",
                     (int)r, (long long)k, (long long)rows, (long long)pitch);
     return 0;
 }
-
-int g_pair_mode = 0;  // CTAs per tile: 1, 2 (cta_group::2 kernels), or 0 = pick per call
 
 // kp_b: row pitch of the B operand(s) in bytes: of Bt[N][K] rows (BMN = false) or of
 // B[K][N] rows (BMN = true).
@@ -483,6 +500,7 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
                   bool accumulate = false, int max_ctas = 0) {
     using cfg = Cfg<MODE, PAIR>;
     constexpr int B_ROWS = cfg::BLOCK_N / PAIR;
+    constexpr int BOX_N = B_ROWS < 128 ? B_ROWS : 128;  // width of an MN-major box = its swizzle width
     constexpr int STAGE_BYTES = cfg::NA * A_TILE_BYTES + cfg::NB * B_ROWS * BLOCK_K;
     constexpr int SMEM = cfg::STAGES * STAGE_BYTES + 1024 + 256 + 4 * EPI_PATCH_WORDS * 4;
     static_assert(SMEM <= 232448, "shared memory budget");
@@ -491,7 +509,7 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     CUtensorMap ta0, ta1, tb0, tb1;
     MB200_TRY(make_tmap(&ta0, a0, k, m, kp_a, BLOCK_M));
     if (BMN)
-        MB200_TRY(make_tmap(&tb0, b0, n, k, kp_b, BLOCK_K));  // boxes of 128 columns x 128 rows of K
+        MB200_TRY(make_tmap(&tb0, b0, n, k, kp_b, BLOCK_K, BOX_N));  // boxes of BOX_N columns x 128 rows of K
     else
         MB200_TRY(make_tmap(&tb0, b0, k, n, kp_b, B_ROWS));
     ta1 = ta0;
@@ -504,7 +522,7 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     }
     if (cfg::NB == 2) {
         if (BMN)
-            MB200_TRY(make_tmap(&tb1, b1, n, k, kp_b, BLOCK_K));
+            MB200_TRY(make_tmap(&tb1, b1, n, k, kp_b, BLOCK_K, BOX_N));
         else
             MB200_TRY(make_tmap(&tb1, b1, k, n, kp_b, B_ROWS));
     }
@@ -522,7 +540,9 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     // 16 m-tiles per group and no hints): groups of 8 m-tiles keep the group's A panels
     // (8 x 256 rows x K) L2-resident across successive waves; A is marked evict-last, B is left
     // at the normal policy (marking it evict-first throws away panels a wave still shares).
-    p.group_m = 8;
+    const int knob_group = tuning().group_m.load();
+    p.group_m = knob_group > 0 ? knob_group : 8;
+    p.raster = tuning().raster.load();
     p.hint_a = 1;
     p.hint_b = 0;
     const long long total = (long long)p.m_tiles * p.n_tiles;
@@ -602,12 +622,6 @@ int64_t launch_wait_selftest(DeviceCtx* ctx, int64_t limit_ms) {
     return check_launch("wait_selftest_kernel");
 }
 
-int64_t set_pair_mode(int pair) {
-    if (pair < 0 || pair > 2) return fail(MIND_B200_ERR_INVALID, "CTAs per tile must be 0 (auto), 1 or 2");
-    g_pair_mode = pair;
-    return 0;
-}
-
 // Measured on B200: the CTA-pair kernel is the faster int8 kernel once there is more than one
 // 128 x 256 tile per SM (3072^3 and up: +6 % to +17 %); below that one CTA per tile is as fast
 // or slightly faster and needs no cluster launch.
@@ -615,21 +629,35 @@ static bool pair_pays(const DeviceCtx* ctx, int64_t m, int64_t n) {
     return m > 128 && ((m + 127) / 128) * ((n + 255) / 256) > ctx->sm_count;
 }
 
+// Few wide tiles and a K too short to split: 128 x 64 tiles spread the product over four times
+// as many SMs, each with a quarter of the epilogue (256^3: 2 CTAs -> 8).
+static bool narrow_pays(const DeviceCtx* ctx, int64_t m, int64_t n, int64_t k) {
+    const int knob = tuning().small_tile.load();
+    if (knob >= 0) return knob == 1;
+    if (tuning().pair_mode.load() != 0) return false;  // a kernel was asked for by name
+    const int64_t wide_tiles = ((m + 127) / 128) * ((n + 255) / 256);
+    return wide_tiles * 4 <= ctx->sm_count && (k + BLOCK_K - 1) / BLOCK_K < 16;
+}
+
 int64_t launch_gemm_i8_tc(DeviceCtx* ctx, const int8_t* a, const int8_t* bt, int32_t* c, int64_t m,
                           int64_t n, int64_t k, int64_t kp_a, int64_t kp_b) {
-    const bool pair = g_pair_mode == 2 || (g_pair_mode == 0 && pair_pays(ctx, m, n));
+    if (narrow_pays(ctx, m, n, k)) return launch_tc<3, 1, false>(ctx, a, nullptr, bt, nullptr, c, m, n, k, kp_a, kp_b);
+    const int pair_mode = tuning().pair_mode.load();
+    const bool pair = pair_mode == 2 || (pair_mode == 0 && pair_pays(ctx, m, n));
     if (pair) return launch_tc<0, 2, false>(ctx, a, nullptr, bt, nullptr, c, m, n, k, kp_a, kp_b);
     return launch_tc<0, 1, false>(ctx, a, nullptr, bt, nullptr, c, m, n, k, kp_a, kp_b);
 }
 
 int64_t launch_gemm_i8_tc_bmn(DeviceCtx* ctx, const int8_t* a, const int8_t* b, int32_t* c, int64_t m,
                               int64_t n, int64_t k, int64_t kp_a, int64_t pitch_b) {
-    const bool pair = g_pair_mode == 2 || (g_pair_mode == 0 && pair_pays(ctx, m, n));
+    if (narrow_pays(ctx, m, n, k)) return launch_tc<3, 1, true>(ctx, a, nullptr, b, nullptr, c, m, n, k, kp_a, pitch_b);
+    const int pair_mode = tuning().pair_mode.load();
+    const bool pair = pair_mode == 2 || (pair_mode == 0 && pair_pays(ctx, m, n));
     if (pair) return launch_tc<0, 2, true>(ctx, a, nullptr, b, nullptr, c, m, n, k, kp_a, pitch_b);
     return launch_tc<0, 1, true>(ctx, a, nullptr, b, nullptr, c, m, n, k, kp_a, pitch_b);
 }
 
-bool tc_pair_forced() { return g_pair_mode == 2; }
+bool tc_pair_forced() { return tuning().pair_mode.load() == 2; }
 
 // Linear part of the Q16.16 GEMM on tensor cores: P[i,j] = sum_k a[i,k] * bh[k,j] mod 2^32,
 // from the four byte planes of a (a_limb[0] lowest, a_limb[3] signed) and the two byte planes

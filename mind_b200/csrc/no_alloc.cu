@@ -2,15 +2,17 @@
 //
 // Some hosts of this library cannot call cudaMalloc at the moment they need a GEMM: code
 // running inside a region where allocation is forbidden or would synchronise the device
-// (a latency-critical serving loop, a callback on a CUDA stream's host path, a process
-// whose memory pool is owned and capped by another component), or code that has handed
-// all of the GPU's memory to its own allocator.  The regular entry point
-// (__mind_blas_matmul_mm_i8_v) keeps B transposed - and A padded, when its rows are not
-// 16-byte pitched - in a scratch buffer that it grows with cudaMalloc on demand, and it
-// creates a small per-device context on first use.  The entry point in this file does the
-// same computation with the same kernels, but its scratch is a fixed array that is part of
-// the library image: nothing here calls cudaMalloc, cudaFree, cudaMallocHost or any routine
-// that allocates on the caller's behalf.
+// (a latency-critical serving loop, a process whose memory pool is owned and capped by
+// another component), or code that has handed all of the GPU's memory to its own
+// allocator.  The regular entry point (__mind_blas_matmul_mm_i8_v) keeps a transposed B
+// (when B's rows are not 16-byte pitched) and a padded A (when A's are not) in a scratch
+// buffer that it grows with cudaMalloc on demand, and it creates a small per-device
+// context on first use.  The entry point in this file does the same computation with the
+// same kernels, but its scratch is a fixed array that is part of the library image: nothing
+// here calls cudaMalloc, cudaFree, cudaMallocHost or any routine that allocates on the
+// caller's behalf.  It is an ordinary synchronous host call (it launches kernels and waits
+// for them), so it must not be made from a CUDA host callback (cudaLaunchHostFunc), where
+// CUDA calls are forbidden, nor on a stream that is being captured.
 //
 // Cost and limits: every GPU on which the library is loaded holds the array
 // (MIND_B200_STATIC_SCRATCH_BYTES = 8 MiB, plus a 256-byte header) until the process exits,
@@ -19,7 +21,7 @@
 // rewrites every byte it later reads and clears the error word first, but two calls that
 // overlap on the GPU (different streams, or different host threads racing to enqueue)
 // would overwrite each other's operands.  Calls are therefore serialised on the host by a
-// lock and each call waits for its own work before it returns.
+// lock and each call waits for its own work before it returns - also when it fails half way.
 #include <mutex>
 
 #include "common.h"
@@ -110,34 +112,62 @@ extern "C" int64_t mind_b200_matmul_mm_i8_static(int64_t a, int64_t b, int64_t c
     ctx.err_word = reinterpret_cast<int*>(base);  // header of the static array
     int32_t* dc = reinterpret_cast<int32_t*>(c);
 
+    if (m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff)
+        return fail(MIND_B200_ERR_TOO_LARGE, "GEMM dimension above 2^31-1");
+
     if (k == 0) {
         MB200_CUDA(cudaMemsetAsync(dc, 0, (size_t)m * n * 4, ctx.stream));
         MB200_CUDA(cudaStreamSynchronize(ctx.stream));
         return 0;
     }
 
+    // Same operand rules as the regular entry point: an operand whose rows TMA can address
+    // (16-byte pitch and base) is read in place and needs no scratch at all; otherwise B is
+    // transposed (N x ceil16(K)) and / or A is padded (M x ceil16(K)) into the array.
     const int64_t kp = (int64_t)align_up((size_t)k, 16);
     const int8_t* da = reinterpret_cast<const int8_t*>(a);
+    const int8_t* db = reinterpret_cast<const int8_t*>(b);
     const bool a_direct = kp == k && a % 16 == 0;
-    const size_t bt_bytes = align_up((size_t)n * kp, 256);
+    const bool b_direct = n % 16 == 0 && b % 16 == 0;
+    // sizes by division first, so that nothing can wrap (dimensions are below 2^31, kp <= 2^31 + 15)
+    const size_t cap_rows = STATIC_SCRATCH_BYTES / (size_t)kp;
+    if ((!b_direct && (size_t)n > cap_rows) || (!a_direct && (size_t)m > cap_rows))
+        return fail(MIND_B200_ERR_TOO_LARGE,
+                    "the re-laid-out operands of this shape do not fit the static scratch of %zu bytes; "
+                    "use __mind_blas_matmul_mm_i8_v for larger shapes", STATIC_SCRATCH_BYTES);
+    const size_t bt_bytes = b_direct ? 0 : align_up((size_t)n * kp, 256);
     const size_t ap_bytes = a_direct ? 0 : align_up((size_t)m * kp, 256);
     if (bt_bytes + ap_bytes > STATIC_SCRATCH_BYTES)
         return fail(MIND_B200_ERR_TOO_LARGE,
-                    "shape needs %zu scratch bytes (N*ceil16(K)%s) but the static scratch holds %zu; "
+                    "shape needs %zu scratch bytes (%s%s) but the static scratch holds %zu; "
                     "use __mind_blas_matmul_mm_i8_v for larger shapes",
-                    bt_bytes + ap_bytes, a_direct ? "" : " + M*ceil16(K) for the padded A", STATIC_SCRATCH_BYTES);
+                    bt_bytes + ap_bytes, b_direct ? "" : "N*ceil16(K) for the transposed B",
+                    a_direct ? "" : " + M*ceil16(K) for the padded A", STATIC_SCRATCH_BYTES);
     int8_t* bt = reinterpret_cast<int8_t*>(base + HEADER_BYTES);
     int8_t* ap = reinterpret_cast<int8_t*>(base + HEADER_BYTES + bt_bytes);
+
+    // From the first enqueue on, every way out waits for the stream: a later call must never
+    // rewrite the array under kernels of this one, even when this one fails half way.
+    struct Drain {
+        cudaStream_t s;
+        ~Drain() {
+            cudaStreamSynchronize(s);
+            cudaGetLastError();
+        }
+    } drain{ctx.stream};
 
     // The array keeps the last call's contents: the error word must start at zero; the
     // operand areas are fully rewritten by the re-layout kernels before the GEMM reads them.
     MB200_CUDA(cudaMemsetAsync(ctx.err_word, 0, sizeof(int), ctx.stream));
-    MB200_TRY(launch_transpose_i8(&ctx, reinterpret_cast<const int8_t*>(b), bt, k, n, kp));
+    if (!b_direct) MB200_TRY(launch_transpose_i8(&ctx, db, bt, k, n, kp));
     if (!a_direct) {
         MB200_TRY(launch_pad_rows_i8(&ctx, da, ap, m, k, kp));
         da = ap;
     }
-    MB200_TRY(launch_gemm_i8_tc(&ctx, da, bt, dc, m, n, k, kp, kp));
+    if (b_direct)
+        MB200_TRY(launch_gemm_i8_tc_bmn(&ctx, da, db, dc, m, n, k, kp, n));
+    else
+        MB200_TRY(launch_gemm_i8_tc(&ctx, da, bt, dc, m, n, k, kp, kp));
 
     int code = 0;  // pageable host word: the copy allocates nothing
     MB200_CUDA(cudaMemcpyAsync(&code, ctx.err_word, sizeof(int), cudaMemcpyDeviceToHost, ctx.stream));

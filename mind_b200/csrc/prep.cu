@@ -214,7 +214,7 @@ int64_t launch_split_i32_bytes(DeviceCtx* ctx, const int32_t* src, uint8_t* cons
     const int64_t total = rows * (cols / 4);
     if (total <= 0) return 0;
     int64_t blocks = (total + 255) / 256;
-    if (blocks > 148 * 64) blocks = 148 * 64;
+    if (blocks > ctx->sm_count * 64) blocks = ctx->sm_count * 64;
     const int4* s4 = reinterpret_cast<const int4*>(src);
     if (what == 0)
         split_i32_bytes_kernel<0><<<(unsigned)blocks, 256, 0, ctx->stream>>>(s4, planes[0], planes[1], planes[2],
@@ -255,7 +255,7 @@ int64_t launch_transpose_i32(DeviceCtx* ctx, const int32_t* src, int32_t* dst, i
 
 int64_t launch_pad_rows_i8(DeviceCtx* ctx, const int8_t* a, int8_t* ap, int64_t m, int64_t k,
                            int64_t kp) {
-    unsigned grid = (unsigned)(m < 148 * 16 ? m : 148 * 16);
+    unsigned grid = (unsigned)(m < ctx->sm_count * 16 ? m : ctx->sm_count * 16);
     pad_rows_i8_kernel<<<grid, 256, 0, ctx->stream>>>(a, ap, m, k, kp);
     count_launch();
     return check_launch("pad_rows_i8_kernel");
@@ -269,13 +269,13 @@ int64_t launch_split_rows_i16(DeviceCtx* ctx, const int16_t* a, int8_t* hi, uint
         if (row_sums && !sums_are_zero) MB200_CUDA(cudaMemsetAsync(row_sums, 0, (size_t)m * 4, ctx->stream));
         const int64_t n8 = m * k / 8;
         int64_t blocks = (n8 + 256 * 4 - 1) / (256 * 4);  // one pass: four vectors per thread
-        if (blocks > 148 * 256) blocks = 148 * 256;
+        if (blocks > ctx->sm_count * 256) blocks = ctx->sm_count * 256;
         if (blocks < 1) blocks = 1;
         split_rows_i16_vec_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(
             reinterpret_cast<const uint4*>(a), reinterpret_cast<uint2*>(hi),
             reinterpret_cast<uint2*>(lo), n8, x * 0x01010101u, row_sums, k / 8, zero_buf, zero_n);
     } else {
-        unsigned grid = (unsigned)(m < 148 * 16 ? m : 148 * 16);
+        unsigned grid = (unsigned)(m < ctx->sm_count * 16 ? m : ctx->sm_count * 16);
         if (grid < 1) grid = 1;
         split_rows_i16_kernel<<<grid, 256, 0, ctx->stream>>>(a, hi, lo, m, k, kp, x, row_sums, zero_buf, zero_n);
     }

@@ -235,6 +235,19 @@ __device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t smem_addr, uint3
     return d;
 }
 
+// The same for a tile of 64 bytes of N per K-row, stored with the 64-byte swizzle (a TMA box
+// of {64 bytes of N, rows of K} with SWIZZLE_64B): groups of 8 K-rows are 512 bytes apart.
+// The tile is a single atom in N, so the leading offset is not used.
+__device__ __forceinline__ uint64_t smem_desc_mn_sw64(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(1) << 16;                               // leading offset: unused here
+    d |= static_cast<uint64_t>(512 >> 4) << 32;                        // stride offset: next 8 K-rows
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(4) << 61;                               // layout: 64-byte swizzle
+    return d;
+}
+
 // Instruction descriptor of tcgen05.mma kind::i8: s32 accumulator, A K-major, B K-major
 // or (b_mn) MN-major, no saturation.  a_signed / b_signed pick s8 or u8.
 __host__ __device__ constexpr uint32_t idesc_i8(int m, int n, bool a_signed, bool b_signed,

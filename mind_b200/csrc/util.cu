@@ -68,7 +68,7 @@ int64_t launch_lcg_fill(DeviceCtx* ctx, void* dst, int64_t n, int kind, uint64_t
     if (n <= 0) return 0;
     const int64_t chunks = (n + LCG_CHUNK - 1) / LCG_CHUNK;
     int64_t blocks = (chunks + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > ctx->sm_count * 16) blocks = ctx->sm_count * 16;
     if (kind == 0)
         lcg_fill_kernel<0><<<(unsigned)blocks, 256, 0, ctx->stream>>>(dst, n, seed, offset, shift);
     else if (kind == 1)
@@ -85,7 +85,7 @@ int64_t launch_matvec_wrap(DeviceCtx* ctx, const void* mat, int elem_bytes, int6
                            int64_t cols, const int32_t* v, int32_t* out) {
     if (rows <= 0) return 0;
     int64_t blocks = (rows + 7) / 8;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
     if (elem_bytes == 1)
         matvec_wrap_kernel<int8_t><<<(unsigned)blocks, 256, 0, ctx->stream>>>(
             static_cast<const int8_t*>(mat), rows, cols, v, out);

@@ -217,12 +217,11 @@ def test_config5_int8_16384(gpu, path):
 
 
 def test_runtime_mirror(gpu):
-    """allocate / run_op / synchronize / deallocate (src/runtime_interface.rs:26-52)."""
+    """allocate / run_op / synchronize / deallocate (src/runtime_interface.rs:26-52), every op name."""
     import mind_b200
     L = mind_b200.lib()
     m, k, n = 48, 80, 32
     g = O.Lcg(21)
-    a, b = g.i8(m * k), g.i8(k * n)
 
     def alloc(dtype, *shape):
         h = C.c_int64(0)
@@ -230,20 +229,101 @@ def test_runtime_mirror(gpu):
         assert L.mind_b200_rt_allocate(dtype, arr, len(shape), C.byref(h)) == 0
         return h.value
 
-    ha, hb, hc = alloc(0, m, k), alloc(0, k, n), alloc(2, m, n)
-    assert L.mind_b200_rt_upload(ha, a.ctypes.data, a.nbytes) == 0
-    assert L.mind_b200_rt_upload(hb, b.ctypes.data, b.nbytes) == 0
-    ins, outs = (C.c_int64 * 2)(ha, hb), (C.c_int64 * 1)(hc)
-    assert L.mind_b200_rt_run_op(b"matmul_mm_i8_v", ins, 2, outs, 1) == 0
-    assert L.mind_b200_rt_synchronize() == 0
-    c = np.empty(m * n, dtype=np.int32)
-    assert L.mind_b200_rt_download(hc, c.ctypes.data, c.nbytes) == 0
-    assert np.array_equal(c, O.gemm_i8(a, b, m, k, n))
+    def run(op, dtype, a, b, a_shape, b_shape, out_shape):
+        ha, hb, hc = alloc(dtype, *a_shape), alloc(dtype, *b_shape), alloc(2, *out_shape)
+        assert L.mind_b200_rt_upload(ha, a.ctypes.data, a.nbytes) == 0
+        assert L.mind_b200_rt_upload(hb, b.ctypes.data, b.nbytes) == 0
+        ins, outs = (C.c_int64 * 2)(ha, hb), (C.c_int64 * 1)(hc)
+        assert L.mind_b200_rt_run_op(op, ins, 2, outs, 1) == 0, L.mind_b200_last_error()
+        assert L.mind_b200_rt_synchronize() == 0
+        c = np.empty(int(np.prod(out_shape)), dtype=np.int32)
+        assert L.mind_b200_rt_download(hc, c.ctypes.data, c.nbytes) == 0
+        return c, (ha, hb, hc), (ins, outs)
+
+    a8, b8 = g.i8(m * k), g.i8(k * n)
+    c, handles, (ins, outs) = run(b"matmul_mm_i8_v", 0, a8, b8, (m, k), (k, n), (m, n))
+    assert np.array_equal(c, O.gemm_i8(a8, b8, m, k, n))
     assert L.mind_b200_rt_run_op(b"no_such_op", ins, 2, outs, 1) == mind_b200.ERR_INVALID
     assert b"unknown op" in L.mind_b200_last_error()
-    for h in (ha, hb, hc):
+    # an op given operands of the wrong element type is refused, not run on reinterpreted bytes
+    assert L.mind_b200_rt_run_op(b"matmul_mm_q16_v", ins, 2, outs, 1) == mind_b200.ERR_INVALID
+    assert b"dtype mismatch" in L.mind_b200_last_error()
+    for h in handles:
         assert L.mind_b200_rt_deallocate(h) == 0
-    assert L.mind_b200_rt_deallocate(ha) == mind_b200.ERR_INVALID
+    assert L.mind_b200_rt_deallocate(handles[0]) == mind_b200.ERR_INVALID
+
+    aq, bq = g.q16(m * k), g.q16(k * n)
+    for op in (b"matmul_mm_q16_v", b"__mind_blas_matmul_mm_q16_mt_v"):
+        c, handles, _ = run(op, 2, aq, bq, (m, k), (k, n), (m, n))
+        assert np.array_equal(c, O.gemm_q16(aq, bq, m, k, n)), op
+        for h in handles:
+            assert L.mind_b200_rt_deallocate(h) == 0
+    a16, b16 = g.i16(m * k), g.i16(k * n)
+    c, handles, _ = run(b"__mind_b200_matmul_mm_i16", 1, a16, b16, (m, k), (k, n), (m, n))
+    assert np.array_equal(c, O.gemm_i16(a16, b16, m, k, n))
+    for h in handles:
+        assert L.mind_b200_rt_deallocate(h) == 0
+    for op in (b"gemv_q16_mt", b"matmul_rmajor_q16_v"):
+        c, handles, _ = run(op, 2, aq, bq[:k], (m, k), (k,), (m,))
+        assert np.array_equal(c, O.gemv_q16(aq, bq[:k], m, k)), op
+        for h in handles:
+            assert L.mind_b200_rt_deallocate(h) == 0
+    c, handles, _ = run(b"matmul_rmajor_i16_v", 1, a16, b16[:k], (m, k), (k,), (m,))
+    assert np.array_equal(c, O.gemv_i16(a16, b16[:k], m, k))
+    for h in handles:
+        assert L.mind_b200_rt_deallocate(h) == 0
+
+
+def test_shutdown_and_reload(gpu):
+    """The library gives back what it holds on the GPU: mind_b200_shutdown() frees it and the next
+    call rebuilds it; dlclose() runs the same teardown (the reference joins its thread pool in
+    a destructor, runtime-support/mind_intrinsics.c:2065-2081) and a fresh dlopen() works again.
+    Run in a child process, which owns its own copy of the library."""
+    import subprocess
+    import sys
+    import mind_b200
+    root = os.path.dirname(HERE)
+    script = r"""
+import ctypes as C, sys
+import numpy as np
+sys.path.insert(0, %r)
+import oracle as O
+LIB = %r
+g = O.Lcg(31)
+m, k, n = 300, 200, 136
+a, b = g.i8(m * k), g.i8(k * n)
+want = O.gemm_i8(a, b, m, k, n)
+def product(L):
+    f = L.__mind_blas_matmul_mm_i8_v
+    f.argtypes, f.restype = [C.c_int64] * 6, C.c_int64
+    c = np.zeros(m * n, dtype=np.int32)
+    assert f(a.ctypes.data, b.ctypes.data, c.ctypes.data, m, k, n) == 0
+    assert np.array_equal(c, want)
+def free_bytes():
+    import torch
+    return torch.cuda.mem_get_info(0)[0]
+L = C.CDLL(LIB)
+L.mind_b200_shutdown.restype = C.c_int64
+L.mind_b200_reserve.argtypes, L.mind_b200_reserve.restype = [C.c_int64] * 2, C.c_int64
+product(L)
+assert L.mind_b200_reserve(256 << 20, 256 << 20) == 0
+held = free_bytes()
+assert L.mind_b200_shutdown() == 0
+assert free_bytes() > held, "shutdown released no device memory"
+product(L)                      # contexts are rebuilt on demand
+assert L.mind_b200_shutdown() == 0
+assert L.mind_b200_shutdown() == 0   # twice is fine
+product(L)
+import _ctypes
+handle = L._handle
+del L
+_ctypes.dlclose(handle)         # runs the library's destructor
+L2 = C.CDLL(LIB)
+product(L2)
+print("reload ok")
+""" % (root, mind_b200.LIB_PATH)
+    r = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "reload ok" in r.stdout, r.stdout + r.stderr
 
 
 def test_stability_reruns(gpu):

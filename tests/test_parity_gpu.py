@@ -32,6 +32,7 @@ GEMM_SHAPES = [
     (64, 4096, 64), (130, 3000, 40), (257, 1100, 300), (16, 16384, 16),
 ]
 PATHS = [3, 2, 1, 0, 4, 5]  # single CTA, CTA pairs, CUDA cores, auto, pairs / single with B transposed first
+PATHS_I8 = PATHS + [10]     # int8 only: the narrow-tile kernel at every shape
 
 
 @pytest.fixture(autouse=True)
@@ -45,7 +46,7 @@ def _default_path(gpu):
 def test_golden_gemm_i8_all_paths(gpu):
     g = O.Lcg(SEED)
     a, b = g.i8(64 * 64), g.i8(64 * 64)
-    for path in PATHS:
+    for path in PATHS_I8:
         gpu.set_gemm_path(path)
         for fn in (gpu.matmul_mm_i8_v, gpu.matmul_mm_i8_mt_v):
             c = np.full(64 * 64, -1, dtype=np.int32)
@@ -102,7 +103,7 @@ def test_reference_xnode_driver_runs_unmodified(gpu):
 
 
 # ------------------------------------------------------------------ edge shapes
-@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("path", PATHS_I8)
 def test_gemm_i8_shapes(gpu, path):
     gpu.set_gemm_path(path)
     for (m, k, n) in GEMM_SHAPES:
@@ -244,7 +245,7 @@ def test_wrap_fixture_and_overflowing_i8(gpu):
     m, k, n = 128, (1 << 17) + 256, 16
     a = np.full(m * k, -128, dtype=np.int8)
     b = np.full(k * n, -128, dtype=np.int8)
-    for path in (3, 2, 4, 5):
+    for path in (3, 2, 4, 5, 10):
         gpu.set_gemm_path(path)
         c = np.empty(m * n, dtype=np.int32)
         gpu.matmul_mm_i8_v(a, b, c, m, k, n)
@@ -322,7 +323,7 @@ def test_unaligned_operands(gpu):
     """Any element-aligned address is legal input (the reference loads with alignment 1/2/4)."""
     m, k, n = 70, 48, 36
     g = O.Lcg(11)
-    for path in PATHS:
+    for path in PATHS_I8:
         gpu.set_gemm_path(path)
         abuf, bbuf = g.i8(m * k + 3), g.i8(k * n + 5)
         a, b = abuf[3:], bbuf[5:]
@@ -360,6 +361,117 @@ def test_bounded_wait_gives_up_cleanly(gpu):
     gpu.matmul_mm_i8_v(a, b, c, 256, 128, 256)
     assert np.array_equal(c, O.gemm_i8(a, b, 256, 128, 256))
     assert f(0) == mind_b200.ERR_INVALID
+
+
+def test_narrow_tile_kernel_is_the_default_for_few_tiles(gpu):
+    """Benchmark configuration 1 (int8 256^3, seed rule of benches/det_matmul_i8.rs:431-445) and
+    its neighbours run on the 128 x 64-tile kernel by default; B read in place (N % 16 == 0, the
+    64-byte-swizzled MN-major tile) and B transposed first (N % 16 != 0) must both give the
+    oracle's bytes, and the same bytes as the wide-tile kernel."""
+    for (m, k, n) in [(256, 256, 256), (512, 512, 512), (256, 1920, 64), (130, 256, 1008), (256, 256, 250)]:
+        g = O.Lcg(0xDEADBEEF00000000 ^ n)
+        a, b = g.i8(m * k), g.i8(k * n)
+        want = O.gemm_i8(a, b, m, k, n)
+        for path in (0, 10, 11):
+            gpu.set_gemm_path(path)
+            c = np.full(m * n + 8, 0x5A5A5A5A, dtype=np.int32)
+            gpu.matmul_mm_i8_v(a, b, c, m, k, n)
+            assert np.array_equal(c[: m * n], want), (path, m, k, n)
+            assert np.all(c[m * n:] == 0x5A5A5A5A)
+    e = SELF.get("gemm-i8-256x256x256")
+    if e:
+        g = O.Lcg(e["seed"])
+        a, b = g.i8(256 * 256), g.i8(256 * 256)
+        c = np.empty(256 * 256, dtype=np.int32)
+        gpu.set_gemm_path(0)
+        gpu.matmul_mm_i8_v(a, b, c, 256, 256, 256)
+        assert O.canonical_hash_i32(c) == e["sha256"]
+
+
+def test_set_stream_orders_the_new_stream_after_the_old(gpu):
+    """Device-pointer calls are asynchronous and share one scratch buffer per device.  A call
+    that re-lays B out in scratch (N % 16 != 0) is queued on stream A; the library is switched to
+    stream B at once, with no host synchronisation, and a second call with another shape rewrites
+    the same scratch.  The switch must order B after A: both results equal the oracle."""
+    import torch
+    torch.cuda.set_device(0)
+    sa, sb = torch.cuda.Stream(), torch.cuda.Stream()
+    g = O.Lcg(4242)
+    m1, k1, n1 = 1500, 2048, 1000   # transposing path, a few hundred microseconds of work
+    m2, k2, n2 = 300, 520, 200
+    a1, b1 = g.i8(m1 * k1), g.i8(k1 * n1)
+    a2, b2 = g.i8(m2 * k2), g.i8(k2 * n2)
+    want1, want2 = O.gemm_i8(a1, b1, m1, k1, n1), O.gemm_i8(a2, b2, m2, k2, n2)
+    d = lambda x: torch.from_numpy(x).cuda()
+    da1, db1, da2, db2 = d(a1), d(b1), d(a2), d(b2)
+    torch.cuda.synchronize()
+    try:
+        for rep in range(4):
+            c1 = torch.zeros(m1 * n1, dtype=torch.int32, device="cuda")
+            c2 = torch.zeros(m2 * n2, dtype=torch.int32, device="cuda")
+            torch.cuda.synchronize()
+            gpu.set_stream(sa.cuda_stream)
+            gpu.matmul_mm_i8_v(da1, db1, c1, m1, k1, n1)
+            gpu.set_stream(sb.cuda_stream)          # no synchronisation in between
+            gpu.matmul_mm_i8_v(da2, db2, c2, m2, k2, n2)
+            torch.cuda.synchronize()
+            assert np.array_equal(c1.cpu().numpy(), want1), rep
+            assert np.array_equal(c2.cpu().numpy(), want2), rep
+    finally:
+        torch.cuda.synchronize()
+        gpu.set_stream(torch.cuda.current_stream().cuda_stream)
+
+
+def test_scratch_growth_keeps_captured_graphs_valid(gpu):
+    """A captured graph holds the scratch addresses it was recorded with.  (1) A call that would
+    have to grow the scratch while its stream is being captured is refused with a clear error,
+    and the capture goes on.  (2) After a capture has been seen, a later, larger call (which
+    grows the scratch) must not free the block the graph still uses: the replay is still right."""
+    import mind_b200
+    import torch
+    torch.cuda.set_device(0)
+    side = torch.cuda.Stream()
+    g = O.Lcg(99)
+    m, k, n = 200, 300, 250                      # N % 16 != 0: B is transposed into scratch
+    a, b = g.i8(m * k), g.i8(k * n)
+    want = O.gemm_i8(a, b, m, k, n)
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    mb, kb, nb = 4000, 5000, 4100                # needs far more scratch than anything before it
+    big_a = torch.zeros(mb * kb, dtype=torch.int8, device="cuda")
+    big_b = torch.ones(kb * nb, dtype=torch.int8, device="cuda")
+    big_c = torch.empty(mb * nb, dtype=torch.int32, device="cuda")
+    out = torch.zeros(m * n, dtype=torch.int32, device="cuda")
+    graph = torch.cuda.CUDAGraph()
+    try:
+        with torch.cuda.stream(side):
+            gpu.set_stream(side.cuda_stream)
+            gpu.matmul_mm_i8_v(da, db, out, m, k, n)     # warm-up: sizes the scratch for this shape
+            torch.cuda.synchronize()
+            out.zero_()
+            with torch.cuda.graph(graph, stream=side):
+                gpu.matmul_mm_i8_v(da, db, out, m, k, n)
+                with pytest.raises(mind_b200.MindB200Error) as e:
+                    gpu.matmul_mm_i8_v(big_a, big_b, big_c, mb, kb, nb)   # would have to grow: refused
+                assert e.value.code == mind_b200.ERR_INVALID and "captured" in str(e.value)
+        gpu.set_stream(torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy(), want)
+        gpu.matmul_mm_i8_v(big_a, big_b, big_c, mb, kb, nb)               # grows the scratch now
+        gpu.synchronize()
+        assert int(big_c.abs().max()) == 0
+        big_a.fill_(1)                                                     # and overwrite it with other bytes
+        gpu.matmul_mm_i8_v(big_a, big_b, big_c, mb, kb, nb)
+        gpu.synchronize()
+        assert int(big_c.min()) == kb and int(big_c.max()) == kb
+        out.zero_()
+        graph.replay()                                                     # the old block is still alive
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy(), want)
+    finally:
+        torch.cuda.synchronize()
+        gpu.set_stream(torch.cuda.current_stream().cuda_stream)
 
 
 def test_errors_do_not_abort(gpu):
