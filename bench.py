@@ -8,10 +8,16 @@ A step is one call of the intrinsic over one set of seeded synthetic operands (t
 reference's LCG, generated on the device).  The default workload is the 16384^3 int8 GEMM,
 row-sharded over the N ranks (one process per GPU, B replicated, no collective), so the
 total work is fixed as N grows.  One JSON line is printed by rank 0.
+
+`value` is timed with operands resident in HBM.  `e2e` is the same product through ONE call
+of the intrinsic with HOST operands: at N > 1 rank 0 makes that call with the library
+spreading it over the N GPUs itself (mind_b200_set_devices), as the reference's `_mt` entry
+points spread one call over the host's cores; the other ranks wait on the host meanwhile.
 """
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
 import statistics
@@ -113,7 +119,7 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append((time.perf_counter(), line.strip()))
 
-    def stop(self):
+    def stop(self, spread=False):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -138,9 +144,13 @@ class ClockSampler:
             for name, val in zip(names, parts[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None, "power_w_max": max(power) if power else None,
-                "samples": len(sm), "window": window, "reasons": sorted(reasons)}
+        out = {"sm_mhz": statistics.median(sm) if sm else None,
+               "sm_max_mhz": max(mx) if mx else None, "power_w_max": max(power) if power else None,
+               "samples": len(sm), "window": window, "reasons": sorted(reasons)}
+        if spread and len(sm) >= 5:
+            q = sorted(sm)
+            out["sm_mhz_p10"], out["sm_mhz_p90"] = q[len(q) // 10], q[(len(q) * 9) // 10]
+        return out
 
 
 # ----------------------------------------------------------------- CPU baseline
@@ -216,6 +226,30 @@ def cpu_baseline(w, target_s=15.0):
             "host_cpus": cores}
 
 
+def cpu_baseline_vnni(w, target_s=6.0):
+    """The reference's opt-in VNNI rung (MIND_INTDOT=vnni, src/mlir/gemm_tuning.rs:225-236,
+    micro-kernel src/mlir/lowering.rs:8186) as a second, labelled CPU figure; None when the host
+    has no AVX-512 VNNI."""
+    import oracle as O
+    if not O.have_vnni():
+        return None
+    cores = O.online_cpus()
+    rows0 = min(w["m"], 64 * min(cores, 256))
+    a, b = cpu_inputs(w, rows0)
+    O.baseline_gemm_i8_vnni(a, b, rows0, w["k"], w["n"], 0)
+    t0 = time.perf_counter()
+    O.baseline_gemm_i8_vnni(a, b, rows0, w["k"], w["n"], 0)
+    dt = max(time.perf_counter() - t0, 1e-4)
+    quantum = 4 * min(cores, 256)
+    rows = min(w["m"], max(quantum, int(rows0 * target_s / dt) // quantum * quantum))
+    a, b = cpu_inputs(w, rows)
+    t0 = time.perf_counter()
+    _, used = O.baseline_gemm_i8_vnni(a, b, rows, w["k"], w["n"], 0)
+    dt = time.perf_counter() - t0
+    return {"value": round(work_units(w, rows) / dt / unit_scale(w), 4), "unit": w["unit"], "cores": used,
+            "kind": "port (vpdpbusd rung)", "sample": f"rows 0..{rows} of {w['m']}, {dt:.2f} s"}
+
+
 def run_reference(args, w):
     """The CPU implementation of the path (threaded port of the reference's kernels,
     oracle/cpu_baseline.c) on the host cores; each step is a bounded row sample."""
@@ -246,24 +280,32 @@ def run_reference(args, w):
 
 
 # ------------------------------------------------------------------- GPU arm
-def quick_workload(name, blas, torch, stream, steps=30):
-    """Device-resident timing of one of the other benchmark configurations on this GPU."""
+def quick_workload(name, blas, torch, stream, dist=None, world=1, rank=0, steps=30):
+    """Device-resident timing of one of the other benchmark configurations, row-sharded over
+    the ranks like the headline workload (each rank its band, max over ranks).  Compact: value,
+    unit, kernel_only (the compute kernels without operand re-layout) and its roofline fraction."""
+    from mind_b200.shard import row_band
     w = WORKLOADS[name]
     m, k, n, kind = w["m"], w["k"], w["n"], w["kind"]
+    r0, r1 = row_band(m, world, rank)
+    rows = max(r1 - r0, 1)
     tdt = {KIND_Q16: torch.int32, KIND_I8: torch.int8, KIND_I16: torch.int16}[kind]
-    a = torch.empty(m * k, dtype=tdt, device="cuda")
+    a = torch.empty(rows * k, dtype=tdt, device="cuda")
     b = torch.empty(k * n, dtype=tdt, device="cuda")
-    c = torch.empty(m * n, dtype=torch.int32, device="cuda")
-    blas.lcg_fill(a, m * k, kind, w["seed"], 0, w["shift"])
+    c = torch.empty(rows * n, dtype=torch.int32, device="cuda")
+    blas.lcg_fill(a, rows * k, kind, w["seed"], r0 * k, w["shift"])
     blas.lcg_fill(b, k * n, kind, w["seed"], m * k, w["shift"])
     fn = getattr(blas, w["fn"])
-    call = (lambda: fn(a, b, c, m, k)) if n == 1 else (lambda: fn(a, b, c, m, k, n))
+    call = (lambda: fn(a, b, c, rows, k)) if n == 1 else (lambda: fn(a, b, c, rows, k, n))
     flush = None
-    if (m * k + k * n) * ELEM_BYTES[kind] <= 2 * L2_BYTES:
+    if (rows * k + k * n) * ELEM_BYTES[kind] <= 2 * L2_BYTES:
         flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device="cuda")
     for _ in range(3):
         call()
     torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
     blas.profile(True)
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     for e0, e1 in evs:
@@ -275,22 +317,36 @@ def quick_workload(name, blas, torch, stream, steps=30):
     torch.cuda.synchronize()
     n_main, main_ms = blas.profile_read()
     blas.profile(False)
-    ms = sum(e0.elapsed_time(e1) for e0, e1 in evs) / steps
+    t = torch.tensor([sum(e0.elapsed_time(e1) for e0, e1 in evs) / steps, main_ms / steps], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, kernel_ms = float(t[0].item()), float(t[1].item())
     scale = unit_scale(w)
-    out = {"workload": f"{name} {m}x{k}x{n}" if n > 1 else f"{name} {m}x{k}", "metric": w["metric"],
-           "value": work_units(w, m) / (ms * 1e-3) / scale, "unit": w["unit"], "ms_per_step": ms, "steps": steps,
-           # the call's compute kernels without its operand re-layout (the Q16.16 hybrid times two per call)
-           "kernel_only": work_units(w, m) * steps / (main_ms * 1e-3) / scale if n_main and main_ms > 0 else None,
-           "kernels_per_call": n_main / steps,
-           "l2": "operands larger than L2" if flush is None else "L2 flushed between steps"}
-    peaks, src = measured_peaks()
-    if w["bound"] == "hbm" and out["kernel_only"]:
-        out["frac_of_hbm_peak"] = out["kernel_only"] / peaks["hbm_gbs"]
-        out["peak_source"] = f"{src} STREAM-style copy {peaks['hbm_gbs']} GB/s"
-    if w["fn"] == "matmul_mm_i16" and out["kernel_only"]:
-        out["frac_of_tensor_peak"] = out["kernel_only"] / (2.0 * peaks["bf16_tflops"] / 4.0)
-        out["peak_source"] = f"2 x {src} cuBLAS bf16 burst / 4 limb products"
+    out = {"value": round(work_units(w, m) / (ms * 1e-3) / scale, 2), "unit": w["unit"],
+           "kernel_only": round(work_units(w, m) / (kernel_ms * 1e-3) / scale, 2) if n_main and kernel_ms > 0 else None}
+    peaks, _ = measured_peaks()
+    peak = None
+    if w["bound"] == "hbm":
+        peak = peaks["hbm_gbs"] * world
+    elif w["fn"] == "matmul_mm_i16":
+        peak = 2.0 * peaks["bf16_tflops"] / 4.0 * world
+    elif w["bound"] == "fp64-pipe":
+        peak = fp64_peak(blas) * 2.0 / scale * world   # one FMA per MAC, 2 ops per MAC
+    if peak and out["kernel_only"]:
+        out["frac"] = round(out["kernel_only"] / peak, 3)
     return out
+
+
+_FP64_PEAK = {}
+
+
+def fp64_peak(blas):
+    """Measured FP64 FMA rate of this GPU (FMA / s): a register-only fma.rm.f64 loop inside the
+    library, timed with CUDA events (a few ms).  The Q16.16 GEMM's floor term is one such FMA per
+    product, so this is that kernel's ceiling."""
+    if "v" not in _FP64_PEAK:
+        _FP64_PEAK["v"] = max(blas.fp64_fma_peak() for _ in range(3))
+    return _FP64_PEAK["v"]
 
 
 def latency_workloads(blas, torch, stream):
@@ -300,16 +356,22 @@ def latency_workloads(blas, torch, stream):
     graph (32 per graph), which removes the host's launch cost."""
     out = {}
 
-    def per_call_us(fn, reps):
+    host_us = {}
+
+    def per_call_us(fn, reps, tag=None):
         for _ in range(5):
             fn()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
+        t0 = time.perf_counter()
         for _ in range(reps):
             fn()
+        t1 = time.perf_counter()  # the host's share: time to enqueue, before anything is waited for
         e1.record(stream)
         torch.cuda.synchronize()
+        if tag:
+            host_us[tag] = (t1 - t0) * 1e6 / reps
         return e0.elapsed_time(e1) * 1e3 / reps
 
     def graphed_us(fn, batch=32, reps=20):
@@ -338,11 +400,10 @@ def latency_workloads(blas, torch, stream):
     blas.lcg_fill(a, n * n, KIND_I8, seed, 0, 0)
     blas.lcg_fill(b, n * n, KIND_I8, seed, n * n, 0)
     call = lambda: blas.matmul_mm_i8_v(a, b, c, n, n, n)
-    us, gus = per_call_us(call, 200), graphed_us(call)
-    out["gemm_i8_256"] = {"workload": "gemm_i8 256x256x256", "us_per_call": us, "top_s": 2.0 * n ** 3 / us / 1e6,
-                          "us_per_call_cuda_graph": gus,
-                          "top_s_cuda_graph": 2.0 * n ** 3 / gus / 1e6 if isinstance(gus, float) else None,
-                          "note": "launch-latency regime: a roofline fraction is not meaningful"}
+    us, gus = per_call_us(call, 200, "i8"), graphed_us(call)
+    r3 = lambda v: round(v, 3) if isinstance(v, float) else v
+    out["gemm_i8_256"] = {"us": r3(us), "us_graph": r3(gus), "host_us": r3(host_us["i8"]),
+                          "top_s": r3(2.0 * n ** 3 / us / 1e6)}
 
     m, k, q = 11922, 384, 64
     seed = 0xDEADBEEF00000000 ^ ((m << 20) ^ k)
@@ -354,11 +415,7 @@ def latency_workloads(blas, torch, stream):
     call = lambda: blas.gemv_q16_mt(w, x, y, m, k)
     us, gus = per_call_us(call, 200), graphed_us(call)
     batched = per_call_us(lambda: blas.matmul_mm_q16_v(w, x, y, m, k, q), 50)
-    out["gemv_q16_routing"] = {"workload": f"gemv_q16 {m}x{k}", "us_per_call": us,
-                               "gb_s": (4.0 * m * k + 4 * k + 4 * m) / us / 1e3,
-                               "us_per_call_cuda_graph": gus,
-                               "batched_queries": {"queries": q, "as": f"gemm_q16 {m}x{k}x{q}", "us_per_call": batched,
-                                                   "us_per_query": batched / q}}
+    out["gemv_q16_11922x384"] = {"us": r3(us), "us_graph": r3(gus), "us_per_query_64_batched": r3(batched / q)}
     # the int16 row kernel (matmul_rmajor_i16_v) at the GEMV configuration's shape: HBM-bound too
     m = k = 16384
     w16 = torch.empty(m * k, dtype=torch.int16, device="cuda")
@@ -370,10 +427,72 @@ def latency_workloads(blas, torch, stream):
     us = per_call_us(lambda: blas.matmul_rmajor_i16_v(w16, x16, y16, m, k), 30)
     peaks, src = measured_peaks()
     gbs = (2.0 * m * k + 2 * k + 4 * m) / us / 1e3
-    out["gemv_i16"] = {"workload": f"gemv_i16 {m}x{k}", "us_per_call": us, "gb_s": gbs,
-                       "frac_of_hbm_peak": gbs / peaks["hbm_gbs"], "peak_source": f"{src} STREAM-style copy",
-                       "l2": "operands larger than L2"}
+    out["gemv_i16"] = {"value": round(gbs, 1), "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 3)}
     return out
+
+
+def whole_output_gate(w, blas, torch, a, b, c, rows, k, n, rank):
+    """Byte-identity gate on the WHOLE output of this rank before any timing (the reference's
+    benches compare the whole output with their scalar oracle, benches/det_matmul_i8.rs:310-352;
+    an O(N^3) CPU oracle is too slow at these sizes):
+      int8 / int16 GEMM  exact Freivalds check in Z/2^32, C.v == A.(B.v) for two random vectors
+                         (both sides are exact sums mod 2^32, so equality is not probabilistic in
+                         the arithmetic, only in the choice of v), plus end rows against the oracle;
+      Q16.16 GEMM        the whole matrix against the independent all-integer kernel (path 1),
+                         plus end rows against the oracle (the rule is not bilinear);
+      GEMV               every output against the CPU oracle."""
+    import oracle as O
+    es = ELEM_BYTES[w["kind"]]
+    if n == 1:
+        want = (O.gemv_i16 if w["kind"] == KIND_I16 else O.gemv_q16)(a.cpu().numpy(), b.cpu().numpy(), rows, k)
+        if not np.array_equal(c[:rows].cpu().numpy(), want):
+            raise SystemExit(f"rank {rank}: GEMV output differs from the oracle; not timing a wrong kernel")
+        return "every output vs the CPU oracle"
+    bh = b.cpu().numpy()
+    oracle_fn = {"matmul_mm_i8_v": O.gemm_i8, "matmul_mm_i16": O.gemm_i16, "matmul_mm_q16_v": O.gemm_q16}[w["fn"]]
+    for s0 in (0, rows - 2):
+        ah = a[s0 * k:(s0 + 2) * k].cpu().numpy()
+        if not np.array_equal(c[s0 * n:(s0 + 2) * n].cpu().numpy(), oracle_fn(ah, bh, 2, k, n)):
+            raise SystemExit(f"rank {rank}: rows {s0}..{s0 + 2} of this band differ from the oracle; not timing a wrong kernel")
+    if w["kind"] == KIND_Q16:
+        c2 = torch.empty_like(c)
+        blas.set_gemm_path(1)
+        blas.matmul_mm_q16_v(a, b, c2, rows, k, n)
+        blas.synchronize()
+        blas.set_gemm_path(0)
+        if not torch.equal(c[: rows * n], c2[: rows * n]):
+            raise SystemExit(f"rank {rank}: Q16.16 GEMM differs from the all-integer kernel")
+        return "whole C vs the all-integer kernel + end rows vs the CPU oracle"
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    for _ in range(2):
+        v = torch.randint(-2**31, 2**31 - 1, (n,), dtype=torch.int64, device="cuda", generator=gen).to(torch.int32)
+        bv = torch.empty(k, dtype=torch.int32, device="cuda")
+        abv = torch.empty(rows, dtype=torch.int32, device="cuda")
+        cv = torch.empty(rows, dtype=torch.int32, device="cuda")
+        blas.matvec_wrap(b, es, k, n, v, bv)
+        blas.matvec_wrap(a, es, rows, k, bv, abv)
+        blas.matvec_wrap(c, 4, rows, n, v, cv)
+        blas.synchronize()
+        if not torch.equal(abv, cv):
+            raise SystemExit(f"rank {rank}: C.v != A.(B.v) mod 2^32; not timing a wrong kernel")
+    return "exact Freivalds in Z/2^32 over the whole C (2 vectors) + end rows vs the CPU oracle"
+
+
+def output_hash(torch, dist, c, m, n, world, rank, r0, rows):
+    """sha256 of C that does not depend on the rank count: every rank hashes its band in blocks of
+    ceil(M / 8) rows (a band of 1, 2, 4 or 8 ranks is a whole number of them), rank 0 hashes the
+    block digests in row order.  Outside every timed region."""
+    block = -(-m // 8)
+    if rows % block and r0 + rows != m:
+        return None
+    host = c[: rows * n].cpu().numpy()
+    digests = b"".join(hashlib.sha256(host[i * n:min(i + block, rows) * n].tobytes()).digest()
+                       for i in range(0, rows, block))
+    if world > 1:
+        parts = [None] * world
+        dist.all_gather_object(parts, digests)
+        digests = b"".join(parts)
+    return hashlib.sha256(digests).hexdigest()
 
 
 def run_mine(args, w):
@@ -389,13 +508,17 @@ def run_mine(args, w):
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torch.distributed.run")
     torch.cuda.set_device(local)
+    host_group = None
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        host_group = dist.new_group(backend="gloo")  # waits on the host: no kernel spins on a GPU meanwhile
     if blas.device_count() == 0:
         raise SystemExit("libmind_b200 found no sm_100 device; there is no fallback to time")
     stream = torch.cuda.current_stream()
     blas.set_stream(stream.cuda_stream)
     blas.set_gemm_path(args.path)
+    if args.group_m or args.raster:
+        blas.set_tile_order(args.group_m, args.raster)
 
     m, k, n, kind = w["m"], w["k"], w["n"], w["kind"]
     es = ELEM_BYTES[kind]
@@ -410,29 +533,20 @@ def run_mine(args, w):
     blas.lcg_fill(b, k * n, kind, w["seed"], m * k, w["shift"])
     fn = getattr(blas, w["fn"])
 
-    def step(pa, pb, pc):
+    def step(pa, pb, pc, nrows=rows):
         if n == 1:
-            fn(pa, pb, pc, rows, k)
+            fn(pa, pb, pc, nrows, k)
         else:
-            fn(pa, pb, pc, rows, k, n)
+            fn(pa, pb, pc, nrows, k, n)
 
-    # Byte-identity gate before any timing (the reference's benches do the same): two rows
-    # at each end of this rank's band against the CPU oracle.
+    # Byte-identity gate before any timing, and the hash of the whole C.
     step(a, b, c)
     blas.synchronize()
+    gate = "skipped (--no-check)"
+    c_sha = None
     if rows >= 2 and not args.no_check:
-        import oracle as O
-        bh = b.cpu().numpy()
-        for s in (0, rows - 2):
-            ah = a[s * k:(s + 2) * k].cpu().numpy()
-            got = c[s * n:(s + 2) * n].cpu().numpy()
-            want = {"matmul_mm_i8_v": O.gemm_i8, "matmul_mm_i16": O.gemm_i16, "matmul_mm_q16_v": O.gemm_q16}.get(w["fn"])
-            if want:
-                want = want(ah, bh, 2, k, n)
-            else:
-                want = (O.gemv_i16 if w["kind"] == KIND_I16 else O.gemv_q16)(ah, bh, 2, k)
-            if not np.array_equal(got, want):
-                raise SystemExit(f"rank {rank}: output differs from the oracle in rows {r0 + s}..{r0 + s + 2}; not timing a wrong kernel")
+        gate = whole_output_gate(w, blas, torch, a, b, c, rows, k, n, rank)
+        c_sha = output_hash(torch, dist, c, m, n, world, rank, r0, rows)
 
     in_bytes = (rows * k + k * n) * es
     flush = None
@@ -475,34 +589,119 @@ def run_mine(args, w):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_total = float(t.item())
 
-    # End to end: the same call with HOST (pinned) operands, so every step copies this rank's
-    # A band and B to the device and C back, inside the timed region.
+    # Sustained leg: the same call back to back for some seconds (the timed region above is a
+    # burst of tens of milliseconds, over before the power cap bites), with the SM clock sampled
+    # throughout.  time x clock (cycles per step) compares runs on boxes with different caps.
+    sustained = None
+    if args.sustain > 0:
+        est = max(ms_total / args.steps, 1e-3)
+        reps = max(10, int(args.sustain * 1e3 / est))
+        s2 = ClockSampler(local)
+        if rank == 0:
+            s2.start()
+            s2.wait_ready()
+        barrier()
+        s2.mark_begin()
+        y0, y1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        y0.record(stream)
+        for _ in range(reps):
+            step(a, b, c)
+        y1.record(stream)
+        barrier()
+        s2.mark_end()
+        t = torch.tensor([y0.elapsed_time(y1)], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sus_ms = float(t.item())
+        if rank == 0:
+            ck = s2.stop(spread=True)
+            per = sus_ms / reps
+            sustained = {"seconds": round(sus_ms * 1e-3, 2), "steps": reps,
+                         "value": round(work_units(w, m) * reps / (sus_ms * 1e-3) / unit_scale(w), 1), "unit": w["unit"],
+                         "ms_per_step": round(per, 4), "sm_mhz_median": ck.get("sm_mhz"), "sm_mhz_p10": ck.get("sm_mhz_p10"),
+                         "sm_mhz_p90": ck.get("sm_mhz_p90"), "clock_samples": ck.get("samples"),
+                         "power_w_max": ck.get("power_w_max"), "reasons": ck.get("reasons"),
+                         "mcycles_per_step": round(per * 1e-3 * ck["sm_mhz"], 3) if ck.get("sm_mhz") else None,
+                         "l2": "L2 not flushed between steps" if flush is not None else "operands larger than L2"}
+
+    # End to end: the same product through ONE call with HOST (pinned) operands, so every step
+    # copies A and B to the device(s) and C back inside the timed region.  At N > 1 rank 0 makes
+    # the call and the library spreads it over the N GPUs (row bands, as the ranks above); the
+    # other ranks wait on the host.
+    e2e = e2e_pageable = None
     e2e_steps = max(1, min(args.steps, 3))
-    ha = torch.empty(a.numel(), dtype=tdt).pin_memory(); ha.copy_(a)
-    hb = torch.empty(b.numel(), dtype=tdt).pin_memory(); hb.copy_(b)
-    hc = torch.empty(c.numel(), dtype=torch.int32).pin_memory()
-    step(ha, hb, hc)  # warm-up (sizes the staging buffers)
-    barrier()
-    x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    x0.record(stream)
-    for _ in range(e2e_steps):
-        step(ha, hb, hc)  # synchronous: returns when C is back in host memory
-    x1.record(stream)
-    torch.cuda.synchronize()
-    e2e_s = x0.elapsed_time(x1) * 1e-3
-    t = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
+    del flush
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_s = float(t.item())
-    if not torch.equal(hc[: rows * n], c[: rows * n].cpu()):
-        raise SystemExit(f"rank {rank}: host-pointer call and device-pointer call disagree")
+        dist.barrier(group=host_group)
+    if rank == 0:
+        if world == 1:
+            ha = torch.empty(a.numel(), dtype=tdt).pin_memory(); ha.copy_(a)
+            full_a = a
+        else:
+            # the whole A on the host: generated band by band on this rank's GPU
+            ha = torch.empty(m * k, dtype=tdt).pin_memory()
+            band = -(-m // world)
+            tmp = torch.empty(band * k, dtype=tdt, device="cuda")
+            for s0 in range(0, m, band):
+                nr = min(band, m - s0)
+                blas.lcg_fill(tmp, nr * k, kind, w["seed"], s0 * k, w["shift"])
+                blas.synchronize()
+                ha[s0 * k:(s0 + nr) * k].copy_(tmp[: nr * k])
+            del tmp
+        hb = torch.empty(b.numel(), dtype=tdt).pin_memory(); hb.copy_(b)
+        hc = torch.empty(m * n, dtype=torch.int32).pin_memory()
+        blas.set_devices(world)
+
+        def timed_calls(pa, pb, pc, reps):
+            step(pa, pb, pc, m)  # warm-up (sizes the staging buffers, starts the device threads)
+            torch.cuda.synchronize()
+            x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            x0.record(stream)
+            for _ in range(reps):
+                step(pa, pb, pc, m)  # synchronous: returns when C is back in host memory
+            x1.record(stream)
+            torch.cuda.synchronize()
+            return x0.elapsed_time(x1) * 1e-3 / reps
+
+        per_call = timed_calls(ha, hb, hc, e2e_steps)
+        total_work = work_units(w, m)
+        e2e = {"value": total_work / per_call / unit_scale(w), "unit": w["unit"],
+               "h2d_bytes_per_step": (m * k + k * n) * es, "d2h_bytes_per_step": m * n * 4,
+               "steps": e2e_steps, "ms_per_step": round(per_call * 1e3, 3),
+               "how": "one call, pinned host operands" + (f", spread over {world} GPUs by the library" if world > 1 else "")}
+        if world == 1:
+            if not torch.equal(hc[: rows * n], c[: rows * n].cpu()):
+                raise SystemExit("host-pointer call and device-pointer call disagree")
+        else:
+            hc_band = hc[r0 * n:(r0 + rows) * n]
+            if not torch.equal(hc_band, c[: rows * n].cpu()):
+                raise SystemExit("the multi-GPU host call disagrees with rank 0's device band")
+            if c_sha is not None:
+                block = -(-m // 8)
+                dig = b"".join(hashlib.sha256(hc[i * n:min(i + block, m) * n].numpy().tobytes()).digest()
+                               for i in range(0, m, block))
+                if hashlib.sha256(dig).hexdigest() != c_sha:
+                    raise SystemExit("the multi-GPU host call's C does not hash like the ranks' C")
+        if not args.no_pageable:
+            # the same call with ordinary (pageable) heap buffers, what a Vec / malloc caller passes
+            pa, pb = ha.numpy().copy(), hb.numpy().copy()
+            pc = np.empty(m * n, dtype=np.int32)
+            per_call = timed_calls(pa, pb, pc, 1 if per_call > 0.05 else 2)
+            if not np.array_equal(pc, hc.numpy()):
+                raise SystemExit("pageable-host call and pinned-host call disagree")
+            e2e_pageable = {"value": round(total_work / per_call / unit_scale(w), 2), "unit": w["unit"],
+                            "ms_per_step": round(per_call * 1e3, 2)}
+            del pa, pb, pc
+        blas.set_devices(1)
+        del ha, hb, hc
+    if world > 1:
+        dist.barrier(group=host_group)
 
     # Optional: the rank-ordered all-gather of the C bands over NCCL (not part of `value`: the
     # path needs no collective; reported so that "with the gather" can be read off too).
     gather_ms = None
     if world > 1 and args.gather and n > 1:
         from mind_b200.shard import all_gather_rows
-        band_rows = -(-m // world)
         full = None
         for _ in range(2):
             full = all_gather_rows(c[: rows * n], m, n)
@@ -520,6 +719,17 @@ def run_mine(args, w):
             raise SystemExit(f"rank {rank}: gathered C does not hold this rank's band")
         del full
 
+    # The metric also names the Q16.16 GEMM, the GEMV and (by config) the int16 GEMM: their
+    # device-resident numbers ride along, row-sharded over the ranks like the headline workload.
+    others = None
+    if args.workload == "gemm_i8" and not args.size and not args.no_others:
+        del a, b, c
+        torch.cuda.empty_cache()
+        others = {name: quick_workload(name, blas, torch, stream, dist, world, rank)
+                  for name in ("gemm_q16", "gemv_q16", "gemm_i16")}
+        if world == 1:
+            others.update(latency_workloads(blas, torch, stream))
+
     if rank == 0:
         peaks, peak_src = measured_peaks()
         scale = unit_scale(w)
@@ -532,52 +742,52 @@ def run_mine(args, w):
             peak, peak_note = peaks["hbm_gbs"], f"{peak_src} STREAM-style copy"
         elif w["bound"] == "tensor":
             # no int8 figure is measured on this pool: the int8 tensor rate is twice bf16
-            base = peaks["bf16_tflops_sustained"] if ms_total / args.steps > 500 else peaks["bf16_tflops"]
-            peak, peak_note = 2.0 * base, f"2 x {peak_src} cuBLAS bf16 ({'sustained' if base == peaks['bf16_tflops_sustained'] else 'burst'})"
+            peak, peak_note = 2.0 * peaks["bf16_tflops"], f"2 x {peak_src} cuBLAS bf16 burst"
             if w["fn"] == "matmul_mm_i16":
                 peak, peak_note = peak / 4.0, peak_note + " / 4 limb products"
         else:
-            # not measured on this pool: derived from the FP64 pipe's issue rate, one fma per MAC
-            peak = 2.0 * 64 * 148 * 1.965e9 / scale
-            peak_note = "derived: 64 FP64 FMA / clock / SM x 148 SMs x 1.965 GHz, one FMA per MAC (no measured figure)"
+            peak = 2.0 * fp64_peak(blas) / scale
+            peak_note = "measured here: register-only fma.rm.f64 loop (one FMA per product, 2 ops)"
         roofline = {"bound": w["bound"], "achieved": achieved, "peak": peak, "unit": w["unit"],
                     "frac": (achieved / peak) if achieved and peak else None,
                     "traffic": NCU_TRAFFIC.get(args.workload) if not args.size and world == 1 else None,
                     "kernel": "gemm_tc_kernel" if w["bound"] == "tensor" else ("rows_group_kernel" if w["bound"] == "hbm" else "gemm_tc_kernel<2> + gemm_q16_fp64_kernel"),
                     "kernel_ms": main_ms / args.steps if n_main else None, "peak_source": peak_note}
-        if w["bound"] == "tensor" and achieved:
-            # for context: the same launches run back to back under the power cap, which is the
-            # regime of the sustained cuBLAS figure (`frac` stays against the burst figure)
-            sustained = 2.0 * peaks["bf16_tflops_sustained"] / (4.0 if w["fn"] == "matmul_mm_i16" else 1.0)
-            roofline["frac_of_sustained_peak"] = achieved / sustained
+        if w["bound"] == "tensor":
+            roofline["frac_of_nominal_4500"] = achieved / (4500.0 / (4.0 if w["fn"] == "matmul_mm_i16" else 1.0)) if achieved else None
+            if sustained:
+                # the sustained leg against the sustained cuBLAS figure (same regime on both sides)
+                div = 4.0 if w["fn"] == "matmul_mm_i16" else 1.0
+                sustained["frac_of_sustained_peak"] = round(sustained["value"] / world / (2.0 * peaks["bf16_tflops_sustained"] / div), 3)
+                sustained["frac_of_nominal_4500"] = round(sustained["value"] / world / (4500.0 / div), 3)
         line = {"metric": w["metric"], "value": value, "unit": w["unit"], "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": w["dtype"], "data": "synthetic",
-                "config": {"workload": f"{args.workload} {m}x{k}x{n}" if n > 1 else f"{args.workload} {m}x{k}",
-                           "sharding": f"{world} row band(s) of {-(-m // world)} rows, B replicated, no collective",
-                           "l2": "operands larger than L2" if flush is None else "L2 flushed between steps",
-                           "gemm_path": args.path, "seed": hex(w["seed"])},
-                "roofline": roofline,
-                "e2e": {"value": total_work * e2e_steps / e2e_s / scale, "unit": w["unit"],
-                        "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": rows * n * 4,
-                        "steps": e2e_steps},
-                "gpu_launches": launches, "clocks": clocks}
+                "dtype": w["dtype"], "data": "synthetic"}
+        if others is not None:
+            line["other_workloads"] = others
+        line["e2e"] = e2e
+        if e2e_pageable is not None:
+            line["e2e_pageable"] = e2e_pageable
+        line["gpu_launches"] = launches
+        line["c_sha256"] = c_sha
+        line["roofline"] = roofline
+        if sustained is not None:
+            line["sustained"] = sustained
+        line["clocks"] = clocks
+        line["config"] = {"workload": f"{args.workload} {m}x{k}x{n}" if n > 1 else f"{args.workload} {m}x{k}",
+                          "sharding": f"{world} row band(s) of {-(-m // world)} rows, B replicated, no collective",
+                          "l2": "operands larger than L2" if in_bytes > 2 * L2_BYTES else "L2 flushed between steps",
+                          "gemm_path": args.path, "seed": hex(w["seed"]), "gate": gate}
         if gather_ms is not None:
             line["all_gather_c"] = {"ms": gather_ms, "bytes_received_per_rank": m * n * 4,
                                     "note": "NCCL all-gather of the C row bands, rank order; outside `value`"}
-        if world == 1 and args.workload == "gemm_i8" and not args.size and not args.no_others:
-            # the metric also names the Q16.16 GEMM, the GEMV and (by config) the int16 GEMM:
-            # their device-resident numbers ride along (each has its own --workload run too)
-            del a, b, c, ha, hb, hc
-            torch.cuda.empty_cache()
-            line["other_workloads"] = {name: quick_workload(name, blas, torch, stream)
-                                       for name in ("gemm_q16", "gemv_q16", "gemm_i16")}
-            line["other_workloads"].update(latency_workloads(blas, torch, stream))
         line["cpu_baseline"] = cpu_baseline(w) if world == 1 and not args.no_cpu else None
+        if line["cpu_baseline"] and not args.no_cpu and w["fn"] == "matmul_mm_i8_v":
+            line["cpu_baseline_vnni"] = cpu_baseline_vnni(w)
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.barrier()
+        dist.barrier(group=host_group)
         dist.destroy_process_group()
 
 
@@ -590,9 +800,13 @@ def main():
     ap.add_argument("--workload", default="gemm_i8", choices=sorted(WORKLOADS))
     ap.add_argument("--path", type=int, default=0, help="0: auto, 2: CTA pairs, 3: one CTA per tile, 1: CUDA cores")
     ap.add_argument("--size", type=int, default=0, help="override M = K (= N) for quick runs")
+    ap.add_argument("--sustain", type=float, default=3.0, help="seconds of back-to-back calls after the timed region (0: skip)")
+    ap.add_argument("--group-m", type=int, default=0, help="int8 tile order: m-tiles per group (0: default)")
+    ap.add_argument("--raster", type=int, default=0, help="int8 tile order variant (0: default)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--no-check", action="store_true", help="skip the oracle gate before timing")
+    ap.add_argument("--no-check", action="store_true", help="skip the whole-output gate before timing")
     ap.add_argument("--no-others", action="store_true", help="skip the other configurations' ride-along numbers")
+    ap.add_argument("--no-pageable", action="store_true", help="skip the pageable-host end-to-end call")
     ap.add_argument("--gather", action="store_true", help="N > 1: also time the optional all-gather of C")
     args = ap.parse_args()
     if args.warmup < 3:

@@ -204,6 +204,11 @@ int64_t mind_b200_selftest_wait_timeout(int64_t limit_ms);
 int64_t mind_b200_profile(int64_t enable);
 int64_t mind_b200_profile_read(int64_t* launches_out, double* total_ms_out);
 
+/* Measured FP64 FMA rate of the current device (FMA per second): a register-only fma.rm.f64
+ * loop timed with CUDA events; the ceiling of the Q16.16 GEMM's per-product floor, which is one
+ * such FMA per product.  Synchronous; a few milliseconds. */
+int64_t mind_b200_fp64_fma_peak(double* fma_per_s_out);
+
 /* ---- seeded inputs and large-shape checking on the device ------------------------------------- */
 /* Fills dst (device or host pointer) with elements [offset, offset + n) of the reference's
  * generator stream (tests/cross_substrate_identity.rs:589-601): kind 0 = Q16.16 int32

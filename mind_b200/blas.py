@@ -171,6 +171,16 @@ def profile(enable: bool) -> None:
     check(lib().mind_b200_profile(1 if enable else 0))
 
 
+def fp64_fma_peak() -> float:
+    """Measured FP64 FMA rate of the current device, FMA per second."""
+    import ctypes as C
+    f = lib().mind_b200_fp64_fma_peak
+    f.argtypes, f.restype = [C.POINTER(C.c_double)], C.c_int64
+    v = C.c_double(0.0)
+    check(f(C.byref(v)))
+    return float(v.value)
+
+
 def profile_read() -> tuple[int, float]:
     """(kernels timed since the last read, their summed duration in ms)."""
     import ctypes as C

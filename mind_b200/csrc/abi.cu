@@ -28,17 +28,17 @@ public:
     explicit Call(DeviceCtx* ctx) : ctx_(ctx) {}
 
     int add(const void* p, size_t bytes, bool output) {
-        Operand o;
+        Operand& o = store_[n_];
+        o = Operand();
         o.user = const_cast<void*>(p);
         o.bytes = bytes;
         o.output = output;
-        ops_.push_back(o);
-        return (int)ops_.size() - 1;
+        return n_++;
     }
 
     int64_t begin() {
         size_t staged = 0;
-        for (auto& o : ops_) {
+        for (auto& o : Range{store_, store_ + n_}) {
             if (o.bytes == 0) continue;
             cudaPointerAttributes at;
             cudaError_t e = cudaPointerGetAttributes(&at, o.user);
@@ -60,7 +60,7 @@ public:
             }
         }
         if (any_host_) MB200_TRY(arena_reserve(ctx_, ctx_->staging, staged + 1024));
-        for (auto& o : ops_) {
+        for (auto& o : Range{store_, store_ + n_}) {
             if (o.bytes == 0) continue;
             if (!o.host) {
                 o.dev = o.user;
@@ -75,12 +75,12 @@ public:
     }
 
     template <typename T>
-    T* dev(int i) const { return static_cast<T*>(ops_[i].dev); }
+    T* dev(int i) const { return static_cast<T*>(store_[i].dev); }
 
     // Downloads outputs; with any host operand, also waits and reports kernel time-outs.
     // `waits_inside` says a kernel with bounded waits ran, whose error word must be fetched.
     int64_t end(bool waits_inside = false) {
-        for (auto& o : ops_)
+        for (auto& o : Range{store_, store_ + n_})
             if (o.host && o.output && o.bytes)
                 MB200_CUDA(cudaMemcpyAsync(o.user, o.dev, o.bytes, cudaMemcpyDeviceToHost, ctx_->stream));
         (void)waits_inside;  // the error word is host-mapped: nothing to fetch
@@ -94,8 +94,15 @@ public:
     static int64_t check_err_word(DeviceCtx* ctx) { return ::mb200::check_err_word(ctx); }
 
 private:
+    // at most four operands per call; iterated as a range
+    struct Range {
+        Operand *b, *e;
+        Operand* begin() const { return b; }
+        Operand* end() const { return e; }
+    };
     DeviceCtx* ctx_;
-    std::vector<Operand> ops_;
+    Operand store_[4];
+    int n_ = 0;
     bool any_host_ = false;
 };
 
@@ -770,6 +777,15 @@ int64_t mind_b200_profile_read(int64_t* launches_out, double* total_ms_out) {
     if (total_ms_out) *total_ms_out = total;
     ctx->prof_count = 0;
     return 0;
+}
+
+int64_t mind_b200_fp64_fma_peak(double* fma_per_s_out) {
+    clear_error();
+    if (!fma_per_s_out) return fail(MIND_B200_ERR_INVALID, "null output");
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return MIND_B200_ERR_NO_DEVICE;
+    DevLock lock(ctx->mu);
+    return measure_fp64_fma_peak(ctx, fma_per_s_out);
 }
 
 int64_t mind_b200_lcg_fill(int64_t dst, int64_t n, int64_t kind, int64_t seed, int64_t offset, int64_t shift) {

@@ -69,7 +69,7 @@ struct Cfg<2, 1> {  // linear part of the Q16.16 product: a (4 limbs) x bh (2 li
 };
 template <>
 struct Cfg<3, 1> {  // int8, narrow tiles
-    static constexpr int BLOCK_N = 64, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 4, STAGES = 4, TMEM_COLS = 256;
+    static constexpr int BLOCK_N = 64, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 4, STAGES = 3, TMEM_COLS = 256;
 };
 
 struct TcParams {
@@ -161,6 +161,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
     const uint32_t cta = PAIR == 2 ? cluster_ctarank() : 0u;
     const bool leader = cta == 0;
 
+    // The narrow-tile kernel serves launch-bound shapes: it is launched so that the next kernel
+    // in the stream may start while this one runs, and its own set-up (barriers, TMEM, tensor-map
+    // prefetch: nothing that touches global memory) overlaps the tail of the kernel before it.
+    if (MODE == 3) griddep_launch_dependents();
+
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full0 + 8 * s, 1);     // one arrive.expect_tx (by the leader, for both CTAs' bytes)
@@ -193,6 +198,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
     }
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(misc);
+    // from here on global memory is read and written: the kernel before this one must be done
+    if (MODE == 3) griddep_wait();
 
     // Work items: (tile, split) with the split index fastest; a split is a contiguous range of
     // k-blocks, never empty (the launcher sees to that).
@@ -473,8 +480,33 @@ __global__ void wait_selftest_kernel(int* err, unsigned long long limit_ns) {
 // box is 128 bytes of K by `box_rows` rows, written to shared memory with the
 // 128-byte swizzle.  Reads past `k` or `rows` return zeros.
 // box_bytes = 64 makes boxes of 64 bytes with the 64-byte swizzle instead (narrow MN-major B tiles).
+// A tensor map is a pure function of these arguments, so the last few are kept per thread:
+// launch-bound callers repeat the same operands, and an encode costs about as much as a launch.
+struct TmapKey {
+    const void* base;
+    int64_t k, rows, pitch;
+    int box_rows, box_bytes;
+    bool operator==(const TmapKey& o) const {
+        return base == o.base && k == o.k && rows == o.rows && pitch == o.pitch && box_rows == o.box_rows &&
+               box_bytes == o.box_bytes;
+    }
+};
+struct TmapCache {
+    static constexpr int N = 8;
+    TmapKey key[N];
+    CUtensorMap map[N];
+    int used = 0, next = 0;
+};
+
 int64_t make_tmap(CUtensorMap* tm, const void* base, int64_t k, int64_t rows, int64_t pitch,
                   int box_rows, int box_bytes = BLOCK_K) {
+    static thread_local TmapCache cache;
+    const TmapKey want{base, k, rows, pitch, box_rows, box_bytes};
+    for (int i = 0; i < cache.used; ++i)
+        if (cache.key[i] == want) {
+            *tm = cache.map[i];
+            return 0;
+        }
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return fail(MIND_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
@@ -488,6 +520,10 @@ int64_t make_tmap(CUtensorMap* tm, const void* base, int64_t k, int64_t rows, in
     if (r != CUDA_SUCCESS)
         return fail(MIND_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (k=%lld rows=%lld pitch=%lld)",
                     (int)r, (long long)k, (long long)rows, (long long)pitch);
+    cache.key[cache.next] = want;
+    cache.map[cache.next] = *tm;
+    cache.next = (cache.next + 1) % TmapCache::N;
+    if (cache.used < TmapCache::N) ++cache.used;
     return 0;
 }
 
@@ -582,13 +618,18 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     lc.blockDim = dim3(TC_THREADS, 1, 1);
     lc.dynamicSmemBytes = SMEM;
     lc.stream = ctx->stream;
-    cudaLaunchAttribute at[1];
+    cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = PAIR;
     at[0].val.clusterDim.y = 1;
     at[0].val.clusterDim.z = 1;
     lc.attrs = at;
     lc.numAttrs = 1;
+    if (MODE == 3) {  // see griddep_launch_dependents / griddep_wait in the kernel
+        at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[1].val.programmaticStreamSerializationAllowed = 1;
+        lc.numAttrs = 2;
+    }
     if (PAIR == 2) {
         // Not every SM need be pairable; a pair that is not resident would only start
         // after another one ends, so size the persistent grid to what fits at once.

@@ -97,6 +97,17 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap,
         : "memory");
 }
 
+// ------------------------------------------------- programmatic dependent launch
+// No-ops unless the kernel was launched with the programmatic-stream-serialization attribute.
+// launch_dependents: the next kernel in the stream may start (and run up to its own wait).
+// wait: blocks until the previous kernel has completed and its writes are visible.
+__device__ __forceinline__ void griddep_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ------------------------------------------------------------------- cluster
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;

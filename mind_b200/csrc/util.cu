@@ -61,7 +61,51 @@ __global__ void matvec_wrap_kernel(const T* __restrict__ mat, int64_t rows, int6
     }
 }
 
+// Register-only fma.rm.f64 chains (sixteen independent ones per thread): the rate the FP64 pipe
+// sustains when nothing but the FMAs is issued.  The ceiling of the Q16.16 GEMM's floor kernel.
+__global__ void fp64_fma_peak_kernel(double* __restrict__ sink, int iters, double x, double y) {
+    double acc[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[j] = 6755399441055744.0 + (double)(threadIdx.x + j);
+    const double a0 = x, a1 = x + 1.0, b0 = y, b1 = y + 0.5;
+    for (int i = 0; i < iters; ++i) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const double a = (j & 1) ? a1 : a0, b = (j & 2) ? b1 : b0;
+            asm volatile("fma.rm.f64 %0, %1, %2, %0;" : "+d"(acc[j]) : "d"(a), "d"(b));
+        }
+    }
+    double t = 0.0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) t += acc[j];
+    if (t == 12345.678) sink[0] = t;  // never true: keeps the chains alive
+}
+
 }  // namespace
+
+// FMA / s of the kernel above on the current device (CUDA events around one launch, after a
+// warm-up launch).  Synchronous.
+int64_t measure_fp64_fma_peak(DeviceCtx* ctx, double* fma_per_s) {
+    const int iters = 1 << 14, threads = 512;
+    const int blocks = ctx->sm_count;
+    cudaEvent_t e0, e1;
+    MB200_CUDA(cudaEventCreate(&e0));
+    MB200_CUDA(cudaEventCreate(&e1));
+    float ms = 0.f;
+    for (int rep = 0; rep < 2; ++rep) {
+        MB200_CUDA(cudaEventRecord(e0, ctx->stream));
+        fp64_fma_peak_kernel<<<blocks, threads, 0, ctx->stream>>>(reinterpret_cast<double*>(ctx->scalar_dev), iters, 3.0, 0.25);
+        MB200_CUDA(cudaEventRecord(e1, ctx->stream));
+        count_launch();
+        MB200_TRY(check_launch("fp64_fma_peak_kernel"));
+        MB200_CUDA(cudaEventSynchronize(e1));
+        MB200_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    *fma_per_s = ms > 0.f ? (double)blocks * threads * iters * 16.0 / (ms * 1e-3) : 0.0;
+    return 0;
+}
 
 int64_t launch_lcg_fill(DeviceCtx* ctx, void* dst, int64_t n, int kind, uint64_t seed,
                         uint64_t offset, int shift) {

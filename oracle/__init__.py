@@ -53,7 +53,7 @@ def lib() -> C.CDLL:
             getattr(L, name).restype = i64
         L.oracle_row_bands.argtypes = [i64, i64, p, p]
         L.oracle_row_bands.restype = i64
-        for name in ("baseline_gemm_i8_mt", "baseline_gemm_q16_mt", "baseline_gemm_i16_mt"):
+        for name in ("baseline_gemm_i8_mt", "baseline_gemm_i8_vnni_mt", "baseline_gemm_q16_mt", "baseline_gemm_i16_mt"):
             getattr(L, name).argtypes = [p, p, p, i64, i64, i64, i64]
             getattr(L, name).restype = i64
         for name in ("baseline_gemv_q16_mt", "baseline_gemv_i16_mt"):
@@ -221,6 +221,21 @@ def gemm_int_numpy(a, b, m, k, n):
 def baseline_gemm_i8(a, b, m, k, n, threads=0):
     c = np.empty(m * n, dtype=np.int32)
     used = lib().baseline_gemm_i8_mt(_ptr(a), _ptr(b), _ptr(c), m, k, n, threads)
+    return c, int(used)
+
+
+def have_vnni() -> bool:
+    """True when the host CPU can run the reference's opt-in vpdpbusd rung."""
+    f = lib().baseline_have_vnni
+    f.restype = C.c_int64
+    return bool(f())
+
+
+def baseline_gemm_i8_vnni(a, b, m, k, n, threads=0):
+    c = np.empty(m * n, dtype=np.int32)
+    used = lib().baseline_gemm_i8_vnni_mt(_ptr(a), _ptr(b), _ptr(c), m, k, n, threads)
+    if used < 0:
+        raise RuntimeError("this CPU has no AVX-512 VNNI")
     return c, int(used)
 
 

@@ -17,6 +17,7 @@
  *     segment, arithmetic >>16, 64-bit add (src/mlir/lowering.rs:9274-9282, :9433);
  *   - Q16.16 / int16 GEMV: one reduction per row
  *     (src/mlir/lowering.rs:9822-9996, :10723);
+ *   - int8 GEMM, second rung: the reference's opt-in VNNI path (vpdpbusd), see below;
  *   - threading: contiguous owner-computes row bands, T = min(ncpu, M, 256),
  *     band = ceil(M/T) (src/mlir/lowering.rs:10146-10205), no reduction.
  * Build with -O3 -march=x86-64-v3 (the reference's level, src/target.rs:267-272).
@@ -27,7 +28,7 @@
 #include <stdlib.h>
 #include <string.h>
 #include <unistd.h>
-#if defined(__AVX2__)
+#if defined(__x86_64__)
 #include <immintrin.h>
 #endif
 
@@ -185,6 +186,138 @@ BASELINE_EXPORT int64_t baseline_gemm_i8_mt(const int8_t *a, const int8_t *b, in
                                             int64_t k, int64_t n, int64_t threads) {
     gemm_i8_ctx g = {a, b, c, m, k, n};
     return run_bands(gemm_i8_band, &g, m, threads);
+}
+
+/* ------------------- int8 GEMM, the reference's VNNI rung ------------------ */
+/* Port of the reference's opt-in AVX-512-VNNI int8 path (MIND_INTDOT=vnni,
+ * src/mlir/gemm_tuning.rs:200-236): the same jc/ic/pc blocking with its own tile
+ * constants (I8_VNNI_MR=8, I8_VNNI_NR=32, I8_VNNI_NC=768, gemm_tuning.rs:177-195),
+ * operands packed as raw bytes in K-quads, A pre-biased by xor 0x80 at pack time
+ * (signed -> unsigned, src/mlir/lowering.rs:8191-8200), an 8 x 2-ZMM accumulator grid
+ * of vpdpbusd (src/mlir/lowering.rs:8186 emit_i8_microkernel_vnni), and the exact
+ * correction  sum a.b = sum (a+128).b - 128.sum b  with the column sums of the packed
+ * B tile taken once per jr tile (src/mlir/lowering.rs:8053 emit_i8_vnni_bsum_hoist).
+ * Every term is exact mod 2^32, so the bytes equal the AVX2 rung's.  Compiled for
+ * AVX-512 by a per-function target attribute and only run when the CPU has VNNI. */
+enum { V_MC = 1024, V_KC = 512, V_NC = 768, V_MR = 8, V_NR = 32 };
+
+BASELINE_EXPORT int64_t baseline_have_vnni(void) {
+#if defined(__x86_64__)
+    return __builtin_cpu_supports("avx512vnni") && __builtin_cpu_supports("avx512bw") ? 1 : 0;
+#else
+    return 0;
+#endif
+}
+
+#if defined(__x86_64__)
+/* B block [kc x nc] -> K-quads: bp[(q*ncp + j)*4 + h] = B[k0+4q+h][j0+j] (zero padded). */
+static void pack_b_vnni(const int8_t *b, int64_t n, int64_t k0, int64_t kc, int64_t j0, int64_t nc,
+                        int64_t ncp, int8_t *bp) {
+    int64_t kq = (kc + 3) / 4;
+    for (int64_t q = 0; q < kq; ++q)
+        for (int64_t j = 0; j < ncp; ++j)
+            for (int h = 0; h < 4; ++h) {
+                int64_t kk = 4 * q + h;
+                bp[(q * ncp + j) * 4 + h] = (kk < kc && j < nc) ? b[(k0 + kk) * n + j0 + j] : 0;
+            }
+}
+
+/* A block [mc x kc] -> K-quads per row, biased: ap[(i*kq + q)*4 + h] = A[i0+i][k0+4q+h] ^ 0x80.
+ * Padding K positions hold 0x80 (= 0 + 128); B is zero there, and the correction uses the
+ * column sums of the padded B, so they cancel. */
+static void pack_a_vnni(const int8_t *a, int64_t k, int64_t i0, int64_t mc, int64_t mcp, int64_t k0,
+                        int64_t kc, uint8_t *ap) {
+    int64_t kq = (kc + 3) / 4;
+    for (int64_t i = 0; i < mcp; ++i)
+        for (int64_t q = 0; q < kq; ++q)
+            for (int h = 0; h < 4; ++h) {
+                int64_t kk = 4 * q + h;
+                uint8_t v = (i < mc && kk < kc) ? (uint8_t)a[(i0 + i) * k + k0 + kk] : 0;
+                ap[(i * kq + q) * 4 + h] = v ^ 0x80u;
+            }
+}
+
+__attribute__((target("avx512f,avx512bw,avx512vnni")))
+static void micro_vnni(const uint8_t *ap, const int8_t *bp, int64_t kq, int64_t ncp, int64_t rows,
+                       int64_t cols, int32_t *c, int64_t ldc, int first) {
+    __m512i acc[V_MR][2], bsum[2];
+    for (int r = 0; r < V_MR; ++r) acc[r][0] = acc[r][1] = _mm512_setzero_si512();
+    bsum[0] = bsum[1] = _mm512_setzero_si512();
+    const __m512i ones = _mm512_set1_epi8(1);
+    for (int64_t q = 0; q < kq; ++q) {
+        const __m512i b0 = _mm512_loadu_si512((const void *)(bp + (q * ncp) * 4));
+        const __m512i b1 = _mm512_loadu_si512((const void *)(bp + (q * ncp + 16) * 4));
+        bsum[0] = _mm512_dpbusd_epi32(bsum[0], ones, b0);
+        bsum[1] = _mm512_dpbusd_epi32(bsum[1], ones, b1);
+        for (int r = 0; r < V_MR; ++r) {
+            int32_t quad;
+            memcpy(&quad, ap + (r * kq + q) * 4, 4);
+            const __m512i av = _mm512_set1_epi32(quad);
+            acc[r][0] = _mm512_dpbusd_epi32(acc[r][0], av, b0);
+            acc[r][1] = _mm512_dpbusd_epi32(acc[r][1], av, b1);
+        }
+    }
+    bsum[0] = _mm512_slli_epi32(bsum[0], 7);
+    bsum[1] = _mm512_slli_epi32(bsum[1], 7);
+    int32_t tile[V_MR][V_NR];
+    for (int r = 0; r < V_MR; ++r) {
+        _mm512_storeu_si512((void *)&tile[r][0], _mm512_sub_epi32(acc[r][0], bsum[0]));
+        _mm512_storeu_si512((void *)&tile[r][16], _mm512_sub_epi32(acc[r][1], bsum[1]));
+    }
+    for (int64_t r = 0; r < rows; ++r)
+        for (int64_t j = 0; j < cols; ++j) {
+            uint32_t prev = first ? 0u : (uint32_t)c[r * ldc + j];
+            c[r * ldc + j] = (int32_t)(prev + (uint32_t)tile[r][j]);
+        }
+}
+
+static void gemm_i8_vnni_band(void *vctx, int64_t rs, int64_t re) {
+    gemm_i8_ctx *g = (gemm_i8_ctx *)vctx;
+    const int64_t k = g->k, n = g->n;
+    if (n <= 0) return;
+    if (k <= 0) {
+        for (int64_t i = rs; i < re; ++i) memset(g->c + i * n, 0, (size_t)n * 4);
+        return;
+    }
+    uint8_t *ap = (uint8_t *)malloc((size_t)(V_MC + V_MR) * (V_KC + 4));
+    int8_t *bp = (int8_t *)malloc((size_t)(V_KC + 4) * (V_NC + V_NR));
+    for (int64_t jc = 0; jc < n; jc += V_NC) {
+        int64_t nc = n - jc < V_NC ? n - jc : V_NC;
+        int64_t ncp = (nc + V_NR - 1) / V_NR * V_NR;
+        for (int64_t ic = rs; ic < re; ic += V_MC) {
+            int64_t mc = re - ic < V_MC ? re - ic : V_MC;
+            int64_t mcp = (mc + V_MR - 1) / V_MR * V_MR;
+            for (int64_t pc = 0; pc < k; pc += V_KC) {
+                int64_t kc = k - pc < V_KC ? k - pc : V_KC;
+                int64_t kq = (kc + 3) / 4;
+                pack_b_vnni(g->b, n, pc, kc, jc, nc, ncp, bp);
+                pack_a_vnni(g->a, k, ic, mc, mcp, pc, kc, ap);
+                for (int64_t jr = 0; jr < nc; jr += V_NR)
+                    for (int64_t ir = 0; ir < mc; ir += V_MR) {
+                        int64_t rows = mc - ir < V_MR ? mc - ir : V_MR;
+                        int64_t cols = nc - jr < V_NR ? nc - jr : V_NR;
+                        micro_vnni(ap + ir * kq * 4, bp + jr * 4, kq, ncp, rows, cols,
+                                   g->c + (ic + ir) * n + jc + jr, n, pc == 0);
+                    }
+            }
+        }
+    }
+    free(ap);
+    free(bp);
+}
+#endif
+
+/* C = A.B for int8 operands on the VNNI rung; returns the threads used, or -1 without VNNI. */
+BASELINE_EXPORT int64_t baseline_gemm_i8_vnni_mt(const int8_t *a, const int8_t *b, int32_t *c, int64_t m,
+                                                 int64_t k, int64_t n, int64_t threads) {
+#if defined(__x86_64__)
+    if (!baseline_have_vnni()) return -1;
+    gemm_i8_ctx g = {a, b, c, m, k, n};
+    return run_bands(gemm_i8_vnni_band, &g, m, threads);
+#else
+    (void)a; (void)b; (void)c; (void)m; (void)k; (void)n; (void)threads;
+    return -1;
+#endif
 }
 
 /* ------------------------------ Q16.16 GEMM ------------------------------- */

@@ -430,6 +430,8 @@ def test_scratch_growth_keeps_captured_graphs_valid(gpu):
     import mind_b200
     import torch
     torch.cuda.set_device(0)
+    gpu.shutdown()                               # start from empty scratch, whatever ran before
+    gpu.set_stream(torch.cuda.current_stream().cuda_stream)
     side = torch.cuda.Stream()
     g = O.Lcg(99)
     m, k, n = 200, 300, 250                      # N % 16 != 0: B is transposed into scratch
