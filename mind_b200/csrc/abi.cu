@@ -501,7 +501,12 @@ int64_t gemm_q16_local(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, in
             // or faster (the tensor-core half is ~6 % of the work there and would idle its SMs).
             const double work = (double)m * (double)n * (double)k;
             // (not with a short K: there the outputs dominate, and side by side every output is an atomic)
-            const int side_sms = g_q16_side_sms >= 0 ? g_q16_side_sms : (work <= 2147483648.0 && k >= 512 ? 16 : 0);
+            (void)work;
+            // Default: in sequence.  Side by side (16 SMs for the tensor-core half, both halves adding
+            // onto a zeroed c with atomics) was the faster form while that half ran 128-column tiles
+            // (64 CTAs at 1024^3); with 64-column tiles it is short enough to go first on every SM,
+            // and the FP64 half then owns c: no zeroing, plain stores where a run covers a tile's K.
+            const int side_sms = g_q16_side_sms >= 0 ? g_q16_side_sms : 0;
             if (side_sms > 0 && side_sms < ctx->sm_count) {
                 MB200_CUDA(cudaMemsetAsync(dc, 0, (size_t)m * n * 4, ctx->stream));
                 MB200_CUDA(cudaEventRecord(ctx->fork_ev, ctx->stream));

@@ -68,6 +68,10 @@ struct Cfg<2, 1> {  // linear part of the Q16.16 product: a (4 limbs) x bh (2 li
     static constexpr int BLOCK_N = 128, NA = 4, NB = 2, NACC = 4, ACC_STAGES = 1, STAGES = 2, TMEM_COLS = 512;
 };
 template <>
+struct Cfg<4, 1> {  // the same with 64-column tiles: twice the CTAs for mid-sized products, two accumulator stages
+    static constexpr int BLOCK_N = 64, NA = 4, NB = 2, NACC = 4, ACC_STAGES = 2, STAGES = 2, TMEM_COLS = 512;
+};
+template <>
 struct Cfg<3, 1> {  // int8, narrow tiles
     static constexpr int BLOCK_N = 64, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 4, STAGES = 3, TMEM_COLS = 256;
 };
@@ -125,7 +129,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                const __grid_constant__ CUtensorMap tm_a2, const __grid_constant__ CUtensorMap tm_a3,
                const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
                const TcParams p) {
-    static_assert(MODE != 2 || (PAIR == 1 && BMN), "the Q16.16 linear-part mode is single-CTA, B in place");
+    constexpr bool Q16LIN = MODE == 2 || MODE == 4;  // linear part of the Q16.16 product (wide / narrow tiles)
+    static_assert(!Q16LIN || (PAIR == 1 && BMN), "the Q16.16 linear-part mode is single-CTA, B in place");
     static_assert(MODE != 1 || PAIR == 1, "the int16 mode is single-CTA");
     static_assert(MODE != 3 || PAIR == 1, "the narrow-tile mode is single-CTA");
     using cfg = Cfg<MODE, PAIR>;
@@ -317,7 +322,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                         const uint64_t kb_off = (uint64_t)ks * B_KSTEP;
                         if (MODE == 0 || MODE == 3) {
                             mma_i8<PAIR>(d0, da0 + koff, db0 + kb_off, ID_SS, acc);
-                        } else if (MODE == 2) {
+                        } else if (Q16LIN) {
                             // a = a3*2^24 + a2*2^16 + a1*2^8 + a0 (a3 signed), bh = bh1*256 + bh0 (bh1
                             // signed); accumulator s collects the limb products of weight 2^(8s).
                             const uint64_t a0d = da0 + koff;
@@ -325,7 +330,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                             const uint64_t a2d = smem_desc_k_sw128(sa + 2 * A_TILE_BYTES) + koff;
                             const uint64_t a3d = smem_desc_k_sw128(sa + 3 * A_TILE_BYTES) + koff;
                             const uint64_t b0d = db0 + kb_off;
-                            const uint64_t b1d = smem_desc_mn_sw128(sb + B_TILE_BYTES, B_BOX_BYTES) + kb_off;
+                            const uint64_t b1d = (BOX_N == 128 ? smem_desc_mn_sw128(sb + B_TILE_BYTES, B_BOX_BYTES)
+                                                               : smem_desc_mn_sw64(sb + B_TILE_BYTES)) + kb_off;
                             mma_i8<PAIR>(d0, a0d, b0d, ID_UU, acc);                  // a0.bh0      -> s0
                             mma_i8<PAIR>(d0 + BLOCK_N, a0d, b1d, ID_US, acc);        // a0.bh1      -> s1
                             mma_i8<PAIR>(d0 + BLOCK_N, a1d, b0d, ID_UU, 1u);         // a1.bh0      -> s1
@@ -381,7 +387,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                 if (MODE == 0 || MODE == 3) {
                     tmem_ld32(t0 + c0, v);
                     tmem_ld_wait();
-                } else if (MODE == 2) {
+                } else if (Q16LIN) {
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         uint32_t s0[16], s1[16], s2[16], s3[16];
@@ -708,6 +714,10 @@ bool tc_pair_forced() { return tuning().pair_mode.load() == 2; }
 int64_t launch_gemm_q16_linear_tc(DeviceCtx* ctx, const uint8_t* const a_limb[4], const uint8_t* const bh_limb[2],
                                   int32_t* p_out, int64_t m, int64_t n, int64_t k, int64_t kp_a,
                                   int64_t pitch_b, bool accumulate, int max_ctas) {
+    // fewer 128 x 128 tiles than SMs: 64-column tiles put twice as many CTAs on a latency-bound product
+    if (max_ctas <= 0 && ((m + 127) / 128) * ((n + 127) / 128) < ctx->sm_count)
+        return launch_tc<4, 1, true>(ctx, a_limb[0], a_limb[1], bh_limb[0], bh_limb[1], p_out, m, n, k, kp_a,
+                                     pitch_b, a_limb[2], a_limb[3], nullptr, accumulate, max_ctas);
     return launch_tc<2, 1, true>(ctx, a_limb[0], a_limb[1], bh_limb[0], bh_limb[1], p_out, m, n, k, kp_a,
                                  pitch_b, a_limb[2], a_limb[3], nullptr, accumulate, max_ctas);
 }
