@@ -438,7 +438,7 @@ def latency_workloads(blas, torch, stream):
     return out
 
 
-def whole_output_gate(w, blas, torch, a, b, c, rows, k, n, rank):
+def whole_output_gate(w, blas, torch, a, b, c, rows, k, n, rank, path=0):
     """Byte-identity gate on the WHOLE output of this rank before any timing (the reference's
     benches compare the whole output with their scalar oracle, benches/det_matmul_i8.rs:310-352;
     an O(N^3) CPU oracle is too slow at these sizes):
@@ -466,7 +466,7 @@ def whole_output_gate(w, blas, torch, a, b, c, rows, k, n, rank):
         blas.set_gemm_path(1)
         blas.matmul_mm_q16_v(a, b, c2, rows, k, n)
         blas.synchronize()
-        blas.set_gemm_path(0)
+        blas.set_gemm_path(path)
         if not torch.equal(c[: rows * n], c2[: rows * n]):
             raise SystemExit(f"rank {rank}: Q16.16 GEMM differs from the all-integer kernel")
         return "whole C vs the all-integer kernel + end rows vs the CPU oracle"
@@ -552,7 +552,7 @@ def run_mine(args, w):
     gate = "skipped (--no-check)"
     c_sha = None
     if rows >= 2 and not args.no_check:
-        gate = whole_output_gate(w, blas, torch, a, b, c, rows, k, n, rank)
+        gate = whole_output_gate(w, blas, torch, a, b, c, rows, k, n, rank, args.path)
         c_sha = output_hash(torch, dist, c, m, n, world, rank, r0, rows)
 
     in_bytes = (rows * k + k * n) * es

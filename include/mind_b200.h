@@ -206,8 +206,9 @@ int64_t mind_b200_profile_read(int64_t* launches_out, double* total_ms_out);
 
 /* Measured FP64 FMA rate of the current device (FMA per second): a register-only fma.rm.f64
  * loop timed with CUDA events; the ceiling of the Q16.16 GEMM's per-product floor, which is one
- * such FMA per product.  Synchronous; a few milliseconds. */
-int64_t mind_b200_fp64_fma_peak(double* fma_per_s_out);
+ * such FMA per product.  sm_mhz_out (may be NULL) receives the SM clock the loop ran at (cycle
+ * counter over wall clock inside the kernel).  Synchronous; a few milliseconds. */
+int64_t mind_b200_fp64_fma_peak(double* fma_per_s_out, double* sm_mhz_out);
 
 /* ---- seeded inputs and large-shape checking on the device ------------------------------------- */
 /* Fills dst (device or host pointer) with elements [offset, offset + n) of the reference's
@@ -227,6 +228,10 @@ int64_t mind_b200_matvec_wrap(int64_t mat, int64_t elem_bytes, int64_t rows, int
  * shapes are taken from the handles.  All return 0 or a negative code. */
 int64_t mind_b200_rt_allocate(int64_t dtype, const int64_t* shape, int64_t rank, int64_t* handle_out);
 int64_t mind_b200_rt_deallocate(int64_t handle);
+/* The reference's DType has no int8 / int16 (src/types/mod.rs:32-47): a MindRuntime shim
+ * allocates such operands as int32 buffers whose last dimension is the row length in bytes / 4
+ * and re-tags them with the element type the op reads (same bytes, last dimension rescaled). */
+int64_t mind_b200_rt_retag(int64_t handle, int64_t dtype);
 int64_t mind_b200_rt_upload(int64_t handle, const void* host_src, int64_t bytes);
 int64_t mind_b200_rt_download(int64_t handle, void* host_dst, int64_t bytes);
 int64_t mind_b200_rt_device_ptr(int64_t handle, int64_t* ptr_out);

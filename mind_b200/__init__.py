@@ -56,7 +56,7 @@ def lib() -> C.CDLL:
                         ("mind_b200_reserve", 2), ("mind_b200_set_gemm_path", 1),
                         ("mind_b200_profile", 1), ("mind_b200_set_devices", 1), ("mind_b200_devices", 0),
                         ("mind_b200_shutdown", 0), ("mind_b200_set_tile_order", 2),
-                        ("mind_b200_rt_deallocate", 1), ("mind_b200_rt_synchronize", 0)):
+                        ("mind_b200_rt_deallocate", 1), ("mind_b200_rt_retag", 2), ("mind_b200_rt_synchronize", 0)):
             f = getattr(L, name)
             f.argtypes, f.restype = [i64] * n, i64
         pi64 = C.POINTER(i64)

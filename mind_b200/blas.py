@@ -171,14 +171,15 @@ def profile(enable: bool) -> None:
     check(lib().mind_b200_profile(1 if enable else 0))
 
 
-def fp64_fma_peak() -> float:
-    """Measured FP64 FMA rate of the current device, FMA per second."""
+def fp64_fma_peak(with_clock: bool = False):
+    """Measured FP64 FMA rate of the current device, FMA per second (and, with_clock, the SM clock
+    in MHz the measuring loop ran at)."""
     import ctypes as C
     f = lib().mind_b200_fp64_fma_peak
-    f.argtypes, f.restype = [C.POINTER(C.c_double)], C.c_int64
-    v = C.c_double(0.0)
-    check(f(C.byref(v)))
-    return float(v.value)
+    f.argtypes, f.restype = [C.POINTER(C.c_double), C.POINTER(C.c_double)], C.c_int64
+    v, mhz = C.c_double(0.0), C.c_double(0.0)
+    check(f(C.byref(v), C.byref(mhz)))
+    return (float(v.value), float(mhz.value)) if with_clock else float(v.value)
 
 
 def profile_read() -> tuple[int, float]:

@@ -496,17 +496,14 @@ int64_t gemm_q16_local(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, in
             // k-blocks per tile, fewer tiles than SMs) and the FP64 half takes five times as long, so
             // the two run side by side: c is zeroed, the byte split and the tensor-core kernel go to
             // a second stream on 16 SMs, the FP64 kernel keeps the rest, and both add onto c with
-            // red.global.add (sums mod 2^32 commute).  Measured at 1024^3: 122 us against 135 us in
+            // red.global.add (sums mod 2^32 commute).  Measured at 1024^3: 113 us against 121 us in
             // sequence (8 / 12 / 24 SMs: 170 / 133 / 127 us); from 1536^3 up the sequence is as fast
-            // or faster (the tensor-core half is ~6 % of the work there and would idle its SMs).
+            // or faster (the tensor-core half is ~6 % of the work there and would idle its SMs).  In
+            // sequence the tensor-core half runs 64-column tiles when it has fewer 128 x 128 tiles
+            // than SMs (135 -> 121 us at 1024^3, 787 -> 756 us at 2048^3).
             const double work = (double)m * (double)n * (double)k;
             // (not with a short K: there the outputs dominate, and side by side every output is an atomic)
-            (void)work;
-            // Default: in sequence.  Side by side (16 SMs for the tensor-core half, both halves adding
-            // onto a zeroed c with atomics) was the faster form while that half ran 128-column tiles
-            // (64 CTAs at 1024^3); with 64-column tiles it is short enough to go first on every SM,
-            // and the FP64 half then owns c: no zeroing, plain stores where a run covers a tile's K.
-            const int side_sms = g_q16_side_sms >= 0 ? g_q16_side_sms : 0;
+            const int side_sms = g_q16_side_sms >= 0 ? g_q16_side_sms : (work <= 2147483648.0 && k >= 512 ? 16 : 0);
             if (side_sms > 0 && side_sms < ctx->sm_count) {
                 MB200_CUDA(cudaMemsetAsync(dc, 0, (size_t)m * n * 4, ctx->stream));
                 MB200_CUDA(cudaEventRecord(ctx->fork_ev, ctx->stream));
@@ -784,13 +781,13 @@ int64_t mind_b200_profile_read(int64_t* launches_out, double* total_ms_out) {
     return 0;
 }
 
-int64_t mind_b200_fp64_fma_peak(double* fma_per_s_out) {
+int64_t mind_b200_fp64_fma_peak(double* fma_per_s_out, double* sm_mhz_out) {
     clear_error();
     if (!fma_per_s_out) return fail(MIND_B200_ERR_INVALID, "null output");
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return MIND_B200_ERR_NO_DEVICE;
     DevLock lock(ctx->mu);
-    return measure_fp64_fma_peak(ctx, fma_per_s_out);
+    return measure_fp64_fma_peak(ctx, fma_per_s_out, sm_mhz_out);
 }
 
 int64_t mind_b200_lcg_fill(int64_t dst, int64_t n, int64_t kind, int64_t seed, int64_t offset, int64_t shift) {

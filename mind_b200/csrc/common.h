@@ -217,7 +217,7 @@ int64_t launch_dist_l1_q16(DeviceCtx* ctx, const int32_t* a, const int32_t* b, i
                            int64_t len);
 int64_t launch_lcg_fill(DeviceCtx* ctx, void* dst, int64_t n, int kind, uint64_t seed,
                         uint64_t offset, int shift);
-int64_t measure_fp64_fma_peak(DeviceCtx* ctx, double* fma_per_s);
+int64_t measure_fp64_fma_peak(DeviceCtx* ctx, double* fma_per_s, double* sm_mhz);
 int64_t launch_matvec_wrap(DeviceCtx* ctx, const void* mat, int elem_bytes, int64_t rows,
                            int64_t cols, const int32_t* v, int32_t* out);
 

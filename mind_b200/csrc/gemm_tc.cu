@@ -9,6 +9,10 @@
 //   warps 2..5 : epilogue      - tcgen05.ld the accumulator (each warp its 32 TMEM
 //                lanes = 32 output rows), combine, transpose 32 x 32 blocks through a
 //                shared-memory patch and store int32 rows to global, 128 bytes at a time.
+//                The modes with four accumulators per tile (int16, Q16.16 linear part) fill
+//                all of TMEM, so their epilogue cannot overlap the next main loop: they run
+//                eight epilogue warps (warps 2..9, two per lane quadrant, half the columns
+//                each) to halve that exposed time.
 // Tiles are 128 rows of A by BLOCK_N rows of Bt by 128 bytes of K per stage.
 // MODE 0 (int8):  one s8 x s8 product, BLOCK_N = 256, two accumulator stages so the
 //                 epilogue of tile t overlaps the main loop of tile t + 1.
@@ -43,7 +47,7 @@ namespace {
 constexpr int BLOCK_M = 128;            // rows of A per CTA
 constexpr int BLOCK_K = 128;            // bytes (= 8-bit elements) of K per stage
 constexpr int UMMA_K = 32;              // K of one tcgen05.mma kind::i8
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 192;  // TMA warp + MMA warp + four epilogue warps (see epi_warps)
 constexpr int A_TILE_BYTES = BLOCK_M * BLOCK_K;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 constexpr int EPI_PATCH_WORDS = 32 * 33;  // per epilogue warp: a 32 x 32 block of outputs, padded rows
@@ -75,6 +79,12 @@ template <>
 struct Cfg<3, 1> {  // int8, narrow tiles
     static constexpr int BLOCK_N = 64, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 4, STAGES = 3, TMEM_COLS = 256;
 };
+
+// Epilogue warps of a mode: four, or eight where a tile has four accumulators to drain.
+template <int MODE, int PAIR>
+__host__ __device__ constexpr int epi_warps() { return Cfg<MODE, PAIR>::NACC == 4 ? 8 : 4; }
+template <int MODE, int PAIR>
+__host__ __device__ constexpr int tc_threads() { return 64 + 32 * epi_warps<MODE, PAIR>(); }
 
 struct TcParams {
     int32_t* c;
@@ -124,7 +134,7 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
 // caller has it (B[K][N], N contiguous = "MN-major"); its tiles are TMA boxes of 128 bytes of N
 // by 128 rows of K, and the MMA reads them through an MN-major descriptor - no transpose pass.
 template <int MODE, int PAIR, bool BMN>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(tc_threads<MODE, PAIR>(), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
                const __grid_constant__ CUtensorMap tm_a2, const __grid_constant__ CUtensorMap tm_a3,
                const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
@@ -150,6 +160,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
     constexpr int TMEM_COLS = cfg::TMEM_COLS;
     static_assert(ACC_COLS * ACC_STAGES <= TMEM_COLS, "TMEM overflow");
     constexpr int UMMA_M = BLOCK_M * PAIR;
+    constexpr int EPI_WARPS = epi_warps<MODE, PAIR>();
+    constexpr int EPI_GROUPS = EPI_WARPS / 4;         // warps per TMEM lane quadrant
+    constexpr int EPI_COLS = BLOCK_N / EPI_GROUPS;    // output columns each of them drains
+    static_assert(EPI_COLS % 32 == 0, "an epilogue warp drains whole 32-column blocks");
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -178,7 +192,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
         }
         for (int s = 0; s < ACC_STAGES; ++s) {
             mbar_init(tfull0 + 8 * s, 1);           // one tcgen05.commit
-            mbar_init(tempty0 + 8 * s, 4 * PAIR);   // one arrive per epilogue warp (of both CTAs)
+            mbar_init(tempty0 + 8 * s, EPI_WARPS * PAIR);   // one arrive per epilogue warp (of both CTAs)
         }
         misc[1] = 0;
         fence_mbar_init();
@@ -368,6 +382,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
     } else {
         // ---------------------------------------------------------------- epilogue
         const int q = warp & 3;  // TMEM lane quadrant this warp may read
+        const int c_first = ((warp - 2) / 4) * EPI_COLS;  // its share of the tile's columns
         uint32_t* const patch = reinterpret_cast<uint32_t*>(smem_raw + (patches0 - raw)) + (warp - 2) * EPI_PATCH_WORDS;
         uint32_t tcount = 0;
         for (int item = tile_first; item < total_tiles; item += tile_step, ++tcount) {
@@ -376,12 +391,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
             const bool first_split = item % p.k_splits == 0;  // the int16 offset term goes in once
             (void)first_split;
             const uint32_t as = tcount % ACC_STAGES, aph = (tcount / ACC_STAGES) & 1u;
+            const int row = (tm * PAIR + (int)cta) * BLOCK_M + q * 32 + lane;
+            // int16: 128 * (row sum of A) puts back the 128 taken off B's low plane.  Fetched before
+            // the wait for the accumulator, so that the load's latency hides behind the main loop.
+            uint32_t back = 0u;
+            if (MODE == 1 && row < p.m && first_split) back = 128u * (uint32_t)__ldg(p.row_sums + row);
             if (!wait_bounded(tfull0 + 8 * as, aph, abort_s, p.err, 4)) break;
             tc_fence_after();
-            const int row = (tm * PAIR + (int)cta) * BLOCK_M + q * 32 + lane;
             const int col_tile = tn * BLOCK_N;
             const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + as * ACC_COLS;
-            for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
+            for (int c0 = c_first; c0 < c_first + EPI_COLS; c0 += 32) {
                 if (col_tile + c0 >= p.n) break;  // warp-uniform
                 uint32_t v[32];
                 if (MODE == 0 || MODE == 3) {
@@ -402,8 +421,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                     }
                 } else {
                     // columns [0, N) hi.hi, [N, 2N) hi.lo', [2N, 3N) lo.hi, [3N, 4N) lo.lo' with
-                    // lo' = lo - 128: 128 * (row sum of A) puts the 128 back (all mod 2^32)
-                    const uint32_t back = (row < p.m && first_split) ? 128u * (uint32_t)p.row_sums[row] : 0u;
+                    // lo' = lo - 128: `back` puts the 128 back (all mod 2^32)
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         uint32_t hh[16], hl[16], lh[16], ll[16];
@@ -544,7 +562,7 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     constexpr int B_ROWS = cfg::BLOCK_N / PAIR;
     constexpr int BOX_N = B_ROWS < 128 ? B_ROWS : 128;  // width of an MN-major box = its swizzle width
     constexpr int STAGE_BYTES = cfg::NA * A_TILE_BYTES + cfg::NB * B_ROWS * BLOCK_K;
-    constexpr int SMEM = cfg::STAGES * STAGE_BYTES + 1024 + 256 + 4 * EPI_PATCH_WORDS * 4;
+    constexpr int SMEM = cfg::STAGES * STAGE_BYTES + 1024 + 256 + epi_warps<MODE, PAIR>() * EPI_PATCH_WORDS * 4;
     static_assert(SMEM <= 232448, "shared memory budget");
     if (m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff)
         return fail(MIND_B200_ERR_TOO_LARGE, "GEMM dimension above 2^31-1");
@@ -621,7 +639,7 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     if (max_ctas > 0 && PAIR == 1 && units > max_ctas) units = max_ctas;
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3((unsigned)(units * PAIR), 1, 1);
-    lc.blockDim = dim3(TC_THREADS, 1, 1);
+    lc.blockDim = dim3(tc_threads<MODE, PAIR>(), 1, 1);
     lc.dynamicSmemBytes = SMEM;
     lc.stream = ctx->stream;
     cudaLaunchAttribute at[2];

@@ -83,6 +83,26 @@ int64_t mind_b200_rt_deallocate(int64_t handle) {
     return 0;
 }
 
+// The reference's DType has no int8 / int16 (src/types/mod.rs:32-47), so a MindRuntime shim
+// allocates such operands as int32-tagged byte buffers whose last dimension is the row length in
+// bytes / 4.  This re-tags a buffer as the element type an op reads: same bytes, last dimension
+// rescaled (x 4 for int8, x 2 for int16 when coming from int32).
+int64_t mind_b200_rt_retag(int64_t handle, int64_t dtype) {
+    clear_error();
+    if (dtype < 0 || dtype > 2) return fail(MIND_B200_ERR_INVALID, "rt_retag: dtype must be 0 (i8), 1 (i16) or 2 (i32)");
+    std::lock_guard<std::mutex> lock(g_rt_mutex);
+    Tensor* t = find(handle);
+    if (!t) return fail(MIND_B200_ERR_INVALID, "rt_retag: unknown handle %lld", (long long)handle);
+    if (t->dtype == (int)dtype) return 0;
+    if (t->shape.empty()) return fail(MIND_B200_ERR_INVALID, "rt_retag: a scalar cannot be re-tagged");
+    const int64_t row_bytes = t->shape.back() * elem_size(t->dtype);
+    if (row_bytes % elem_size((int)dtype))
+        return fail(MIND_B200_ERR_INVALID, "rt_retag: a row of %lld bytes is not a whole number of elements", (long long)row_bytes);
+    t->shape.back() = row_bytes / elem_size((int)dtype);
+    t->dtype = (int)dtype;
+    return 0;
+}
+
 int64_t mind_b200_rt_upload(int64_t handle, const void* host_src, int64_t bytes) {
     clear_error();
     DeviceCtx* ctx = current_ctx();

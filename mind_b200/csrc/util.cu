@@ -61,40 +61,64 @@ __global__ void matvec_wrap_kernel(const T* __restrict__ mat, int64_t rows, int6
     }
 }
 
-// Register-only fma.rm.f64 chains (sixteen independent ones per thread): the rate the FP64 pipe
-// sustains when nothing but the FMAs is issued.  The ceiling of the Q16.16 GEMM's floor kernel.
-__global__ void fp64_fma_peak_kernel(double* __restrict__ sink, int iters, double x, double y) {
-    double acc[16];
+// Register-only fma.rm.f64 chains: the rate the FP64 pipe sustains when nothing but the FMAs is
+// issued.  The ceiling of the Q16.16 GEMM's floor kernel.  Thirty-two independent chains per
+// thread, laid out as that kernel's register tile is (an 8 x 4 outer product: every operand
+// register feeds several FMAs in a row), which is the form the pipe runs fastest.
+__global__ void fp64_fma_peak_kernel(double* __restrict__ sink, int iters, double x, double y,
+                                     unsigned long long* __restrict__ clocks) {
+    unsigned long long c0 = 0, t0 = 0;
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        c0 = clock64();
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    }
+    double acc[8][4], a[8], b[4];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) acc[j] = 6755399441055744.0 + (double)(threadIdx.x + j);
-    const double a0 = x, a1 = x + 1.0, b0 = y, b1 = y + 0.5;
-    for (int i = 0; i < iters; ++i) {
+    for (int i = 0; i < 8; ++i) {
+        a[i] = x + (double)i;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const double a = (j & 1) ? a1 : a0, b = (j & 2) ? b1 : b0;
-            asm volatile("fma.rm.f64 %0, %1, %2, %0;" : "+d"(acc[j]) : "d"(a), "d"(b));
-        }
+        for (int j = 0; j < 4; ++j) acc[i][j] = 6755399441055744.0 + (double)(threadIdx.x + 4 * i + j);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) b[j] = y + 0.25 * (double)j;
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                asm volatile("fma.rm.f64 %0, %1, %2, %0;" : "+d"(acc[i][j]) : "d"(a[i]), "d"(b[j]));
     }
     double t = 0.0;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) t += acc[j];
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) t += acc[i][j];
     if (t == 12345.678) sink[0] = t;  // never true: keeps the chains alive
+    if (blockIdx.x == 0 && threadIdx.x == 0) {  // SM cycles and nanoseconds this block took: the clock it ran at
+        unsigned long long t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        clocks[0] = clock64() - c0;
+        clocks[1] = t1 - t0;
+    }
 }
 
 }  // namespace
 
 // FMA / s of the kernel above on the current device (CUDA events around one launch, after a
 // warm-up launch).  Synchronous.
-int64_t measure_fp64_fma_peak(DeviceCtx* ctx, double* fma_per_s) {
-    const int iters = 1 << 14, threads = 512;
+int64_t measure_fp64_fma_peak(DeviceCtx* ctx, double* fma_per_s, double* sm_mhz) {
+    const int iters = 1 << 13, threads = 256;
     const int blocks = ctx->sm_count;
+    unsigned long long* clocks = nullptr;
+    MB200_CUDA(cudaMalloc(&clocks, 2 * sizeof(unsigned long long) + sizeof(double)));
+    double* sink = reinterpret_cast<double*>(clocks + 2);
     cudaEvent_t e0, e1;
     MB200_CUDA(cudaEventCreate(&e0));
     MB200_CUDA(cudaEventCreate(&e1));
     float ms = 0.f;
     for (int rep = 0; rep < 2; ++rep) {
         MB200_CUDA(cudaEventRecord(e0, ctx->stream));
-        fp64_fma_peak_kernel<<<blocks, threads, 0, ctx->stream>>>(reinterpret_cast<double*>(ctx->scalar_dev), iters, 3.0, 0.25);
+        fp64_fma_peak_kernel<<<blocks, threads, 0, ctx->stream>>>(sink, iters, 3.0, 0.25, clocks);
         MB200_CUDA(cudaEventRecord(e1, ctx->stream));
         count_launch();
         MB200_TRY(check_launch("fp64_fma_peak_kernel"));
@@ -103,7 +127,11 @@ int64_t measure_fp64_fma_peak(DeviceCtx* ctx, double* fma_per_s) {
     }
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
-    *fma_per_s = ms > 0.f ? (double)blocks * threads * iters * 16.0 / (ms * 1e-3) : 0.0;
+    unsigned long long h[2] = {0, 0};
+    MB200_CUDA(cudaMemcpy(h, clocks, sizeof h, cudaMemcpyDeviceToHost));
+    cudaFree(clocks);
+    *fma_per_s = ms > 0.f ? (double)blocks * threads * iters * 32.0 / (ms * 1e-3) : 0.0;
+    if (sm_mhz) *sm_mhz = h[1] ? (double)h[0] * 1e3 / (double)h[1] : 0.0;
     return 0;
 }
 

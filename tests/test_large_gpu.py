@@ -252,6 +252,22 @@ def test_runtime_mirror(gpu):
         assert L.mind_b200_rt_deallocate(h) == 0
     assert L.mind_b200_rt_deallocate(handles[0]) == mind_b200.ERR_INVALID
 
+    # what a MindRuntime shim does (the reference's DType has no int8): int32-tagged byte buffers,
+    # last dimension = row bytes / 4, re-tagged as int8 for the op
+    ha, hb, hc = alloc(2, m, k // 4), alloc(2, k, n // 4), alloc(2, m, n)
+    assert L.mind_b200_rt_upload(ha, a8.ctypes.data, a8.nbytes) == 0
+    assert L.mind_b200_rt_upload(hb, b8.ctypes.data, b8.nbytes) == 0
+    assert L.mind_b200_rt_retag(ha, 0) == 0 and L.mind_b200_rt_retag(hb, 0) == 0
+    assert L.mind_b200_rt_retag(ha, 0) == 0                      # already int8: nothing to do
+    ins, outs = (C.c_int64 * 2)(ha, hb), (C.c_int64 * 1)(hc)
+    assert L.mind_b200_rt_run_op(b"matmul_mm_i8_mt_v", ins, 2, outs, 1) == 0, L.mind_b200_last_error()
+    c = np.empty(m * n, dtype=np.int32)
+    assert L.mind_b200_rt_download(hc, c.ctypes.data, c.nbytes) == 0
+    assert np.array_equal(c, O.gemm_i8(a8, b8, m, k, n))
+    assert L.mind_b200_rt_retag(hc, 7) == mind_b200.ERR_INVALID
+    for h in (ha, hb, hc):
+        assert L.mind_b200_rt_deallocate(h) == 0
+
     aq, bq = g.q16(m * k), g.q16(k * n)
     for op in (b"matmul_mm_q16_v", b"__mind_blas_matmul_mm_q16_mt_v"):
         c, handles, _ = run(op, 2, aq, bq, (m, k), (k, n), (m, n))
