@@ -18,8 +18,10 @@ struct Operand {
     size_t bytes = 0;
     bool output = false;
     bool host = false;
+    bool staged = false;  // pageable and large: moved by the staging threads
     void* dev = nullptr;
 };
+constexpr size_t STAGED_MIN_BYTES = (size_t)8 << 20;
 
 // Classifies each operand, gives host operands a device copy in the staging arena,
 // uploads inputs before the kernels and downloads outputs after them.
@@ -68,8 +70,22 @@ public:
             }
             o.dev = arena_take(ctx_->staging, o.bytes);
             if (!o.dev) return fail(MIND_B200_ERR_CUDA, "staging arena exhausted");
-            if (!o.output)
+            // a large pageable operand goes through the staging threads' pinned slots (several
+            // cores copy, the DMAs overlap them) instead of the driver's one-thread staging
+            o.staged = o.bytes >= STAGED_MIN_BYTES && host_pointer_is_pageable(o.user) && stager_start();
+            if (o.output) continue;
+            if (o.staged) {
+                const size_t row = (size_t)1 << 20, rows = o.bytes / row, rest = o.bytes - rows * row;
+                StageGroup body, tail;
+                char* dst = static_cast<char*>(o.dev);
+                const char* src = static_cast<const char*>(o.user);
+                stage_upload(ctx_->device, dst, row, src, row, row, rows, ctx_->stream, &body, nullptr, &status_);
+                if (rest) stage_upload(ctx_->device, dst + rows * row, rest, src + rows * row, rest, rest, 1, ctx_->stream, &tail, nullptr, &status_);
+                body.wait();
+                tail.wait();  // every DMA is queued on the stream: the kernels that follow see the data
+            } else {
                 MB200_CUDA(cudaMemcpyAsync(o.dev, o.user, o.bytes, cudaMemcpyHostToDevice, ctx_->stream));
+            }
         }
         return 0;
     }
@@ -80,15 +96,36 @@ public:
     // Downloads outputs; with any host operand, also waits and reports kernel time-outs.
     // `waits_inside` says a kernel with bounded waits ran, whose error word must be fetched.
     int64_t end(bool waits_inside = false) {
+        bool any_staged = false;
         for (auto& o : Range{store_, store_ + n_})
-            if (o.host && o.output && o.bytes)
-                MB200_CUDA(cudaMemcpyAsync(o.user, o.dev, o.bytes, cudaMemcpyDeviceToHost, ctx_->stream));
+            if (o.host && o.output && o.bytes) {
+                if (o.staged) {
+                    StageGroup g;
+                    stage_download(ctx_->device, static_cast<char*>(o.user), static_cast<const char*>(o.dev), o.bytes,
+                                   ctx_->stream, &g, nullptr, &status_);
+                    g.wait();
+                    any_staged = true;
+                } else {
+                    MB200_CUDA(cudaMemcpyAsync(o.user, o.dev, o.bytes, cudaMemcpyDeviceToHost, ctx_->stream));
+                }
+            }
         (void)waits_inside;  // the error word is host-mapped: nothing to fetch
         if (any_host_) {
+            if (any_staged) stager_drain();
             MB200_CUDA(cudaStreamSynchronize(ctx_->stream));
+            if (status_.failed.load()) return fail(MIND_B200_ERR_CUDA, "a staged copy of a pageable host operand failed");
             return check_err_word(ctx_);
         }
         return 0;
+    }
+
+    ~Call() {
+        // a call that failed half way may still have staged chunks in flight that point into it
+        for (auto& o : Range{store_, store_ + n_})
+            if (o.staged) {
+                stager_drain();
+                break;
+            }
     }
 
     static int64_t check_err_word(DeviceCtx* ctx) { return ::mb200::check_err_word(ctx); }
@@ -104,6 +141,7 @@ private:
     Operand store_[4];
     int n_ = 0;
     bool any_host_ = false;
+    StageStatus status_;
 };
 
 int64_t check_dims(int64_t m, int64_t k, int64_t n) {
@@ -175,11 +213,19 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
     const int64_t kp = (int64_t)align_up((size_t)k, 16);
     const int64_t band = (int64_t)align_up((size_t)((m + 7) / 8), 256);
     const int64_t bands = (m + band - 1) / band;
+    // Pageable host operands (an ordinary malloc / Vec) go through the staging threads' pinned
+    // slots instead of the driver's own one-thread staging; page-locked ones are copied directly.
+    const bool row_fits = (size_t)kp <= stager_slot_bytes() && (size_t)n * 4 <= stager_slot_bytes();
+    const bool a_page = a_host && row_fits && host_pointer_is_pageable(a);
+    const bool b_page = b_host && row_fits && host_pointer_is_pageable(b);
+    const bool c_page = c_host && row_fits && host_pointer_is_pageable(c);
+    const bool staged = (a_page || b_page || c_page) && stager_start();
     // Column chunks only pay when C is downloaded, and need B readable in place per chunk.
     const bool b_inplace_ok = !(tuning().force_transpose.load() != 0) && n % 16 == 0 && (b_host || reinterpret_cast<uintptr_t>(b) % 16 == 0);
     // Four, not more: a strided download slows down beside running kernels as its rows get shorter
     // (measured with a GEMM on another stream: 57 GB/s for 64 KiB rows, 48 for 16 KiB, 31 for 8 KiB).
-    const int64_t chunks = (c_host && b_inplace_ok && n >= 4096 && n % 64 == 0) ? 4 : 1;
+    // (staged copies move whole rows: one chunk)
+    const int64_t chunks = (c_host && b_inplace_ok && n >= 4096 && n % 64 == 0 && !staged) ? 4 : 1;
     const int64_t nj = n / chunks;  // columns per chunk (a multiple of 16 when chunks > 1)
     Pipe* pp = nullptr;
     MB200_TRY(pipe_for(ctx, (size_t)(bands + chunks), &pp));
@@ -240,34 +286,71 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
         }
     }
 
+    // Host-side completion of staged copies: one group per upload (its event is recorded by the
+    // staging thread that queues its last chunk) and one per C slot.  Before the library's
+    // stream is told to wait for such an event, this thread waits until it has been recorded.
+    StageStatus stage_status;
+    std::vector<StageGroup> up_groups(staged ? (size_t)(bands + chunks) : 0);
+    StageGroup out_groups[nslot];
+    // Whatever happens below, no staging thread may still hold pointers into this call.
+    struct DrainGuard {
+        bool on;
+        ~DrainGuard() {
+            if (on) stager_drain();
+        }
+    } drain_guard{staged};
+    const int device = ctx->device;
+
     // ---- uploads, all queued now on the in-stream in that order
     for (const Step& u : uploads) {
         if (!u.is_a) {
             const int64_t j = u.idx;
+            cudaEvent_t ev = P.ready[bands + j];
+            if (staged && b_page) {  // chunks == 1
+                cudaStream_t in = P.in;
+                stage_upload(device, reinterpret_cast<char*>(b_stage), (size_t)n, reinterpret_cast<const char*>(b),
+                             (size_t)n, (size_t)n, (size_t)k, in, &up_groups[bands + j],
+                             [ev, in] { cudaEventRecord(ev, in); }, &stage_status);
+                continue;
+            }
             if (chunks == 1)
                 MB200_CUDA(cudaMemcpyAsync(b_stage, b, (size_t)k * n, cudaMemcpyHostToDevice, P.in));
             else
                 MB200_CUDA(cudaMemcpy2DAsync(b_stage + (size_t)j * k * nj, (size_t)nj, b + (size_t)j * nj, (size_t)n,
                                              (size_t)nj, (size_t)k, cudaMemcpyHostToDevice, P.in));
-            MB200_CUDA(cudaEventRecord(P.ready[bands + j], P.in));
+            MB200_CUDA(cudaEventRecord(ev, P.in));
         } else {
             const int64_t i = u.idx;
             const int64_t r0 = i * band, rows = (m - r0 < band) ? m - r0 : band;
             int8_t* dst = a_stage + (size_t)r0 * kp;
             const int8_t* src = a + (size_t)r0 * k;
+            cudaEvent_t ev = P.ready[i];
+            if (staged && a_page) {
+                cudaStream_t in = P.in;
+                stage_upload(device, reinterpret_cast<char*>(dst), (size_t)kp, reinterpret_cast<const char*>(src),
+                             (size_t)k, (size_t)k, (size_t)rows, in, &up_groups[i],
+                             [ev, in] { cudaEventRecord(ev, in); }, &stage_status);
+                continue;
+            }
             if (kp == k)
                 MB200_CUDA(cudaMemcpyAsync(dst, src, (size_t)rows * k, cudaMemcpyHostToDevice, P.in));
             else  // pad to a 16-byte pitch on the way: the pad bytes are never read
                 MB200_CUDA(cudaMemcpy2DAsync(dst, (size_t)kp, src, (size_t)k, (size_t)k, (size_t)rows,
                                              cudaMemcpyHostToDevice, P.in));
-            MB200_CUDA(cudaEventRecord(P.ready[i], P.in));
+            MB200_CUDA(cudaEventRecord(ev, P.in));
         }
     }
+    auto upload_recorded = [&](int64_t idx) {  // host wait: the event of upload `idx` exists on its stream
+        if (staged) up_groups[(size_t)idx].wait();
+    };
 
     // ---- one-off re-layouts on the library's stream
     int8_t* bt = nullptr;
     if (!b_direct) {  // chunks == 1 here
-        if (b_host) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.ready[bands], 0));
+        if (b_host) {
+            upload_recorded(bands);
+            MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.ready[bands], 0));
+        }
         bt = static_cast<int8_t*>(arena_take(ctx->scratch, bt_bytes));
         MB200_TRY(launch_transpose_i8(ctx, b_chunk(0), bt, k, n, kp));
     }
@@ -288,14 +371,19 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
         const int s = (int)(t % nslot);
         const int64_t r0 = i * band, rows = (m - r0 < band) ? m - r0 : band;
         if (b_host && b_direct && !b_waited[j]) {
+            upload_recorded(bands + j);
             MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.ready[bands + j], 0));
             b_waited[j] = 1;
         }
         if (a_host && !a_waited[i]) {
+            upload_recorded(i);
             MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.ready[i], 0));
             a_waited[i] = 1;
         }
-        if (c_host && t >= nslot) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.out_done[s], 0));  // slot free
+        if (c_host && t >= nslot) {  // slot free
+            out_groups[s].wait();
+            MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.out_done[s], 0));
+        }
         int32_t* c_tile = c_host ? c_slot[s] : c + (size_t)r0 * n;  // a device C is never cut into chunks
         const int8_t* a_band = a_dev + (size_t)r0 * a_pitch;
         if (b_direct)
@@ -306,18 +394,31 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
             MB200_CUDA(cudaEventRecord(P.gemm_done[s], ctx->stream));
             MB200_CUDA(cudaStreamWaitEvent(P.out, P.gemm_done[s], 0));
             int32_t* dst = c + (size_t)r0 * n + (size_t)j * nj;
-            if (chunks == 1)
-                MB200_CUDA(cudaMemcpyAsync(dst, c_slot[s], (size_t)rows * n * 4, cudaMemcpyDeviceToHost, P.out));
-            else
-                MB200_CUDA(cudaMemcpy2DAsync(dst, (size_t)n * 4, c_slot[s], (size_t)nj * 4, (size_t)nj * 4,
-                                             (size_t)rows, cudaMemcpyDeviceToHost, P.out));
-            MB200_CUDA(cudaEventRecord(P.out_done[s], P.out));
+            if (staged && c_page) {  // chunks == 1: whole rows, contiguous on both sides
+                cudaEvent_t ev = P.out_done[s];
+                cudaStream_t out = P.out;
+                stage_download(device, reinterpret_cast<char*>(dst), reinterpret_cast<const char*>(c_slot[s]),
+                               (size_t)rows * n * 4, out, &out_groups[s], [ev, out] { cudaEventRecord(ev, out); },
+                               &stage_status);
+            } else {
+                if (chunks == 1)
+                    MB200_CUDA(cudaMemcpyAsync(dst, c_slot[s], (size_t)rows * n * 4, cudaMemcpyDeviceToHost, P.out));
+                else
+                    MB200_CUDA(cudaMemcpy2DAsync(dst, (size_t)n * 4, c_slot[s], (size_t)nj * 4, (size_t)nj * 4,
+                                                 (size_t)rows, cudaMemcpyDeviceToHost, P.out));
+                MB200_CUDA(cudaEventRecord(P.out_done[s], P.out));
+            }
         }
         ++t;
     }
     if (c_host)
-        for (int s = 0; s < nslot && s < t; ++s) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.out_done[s], 0));
+        for (int s = 0; s < nslot && s < t; ++s) {
+            out_groups[s].wait();
+            MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.out_done[s], 0));
+        }
+    if (staged) stager_drain();  // the last chunks are in the caller's buffer
     MB200_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (stage_status.failed.load()) return fail(MIND_B200_ERR_CUDA, "a staged copy of a pageable host operand failed");
     return Call::check_err_word(ctx);
 }
 
@@ -420,11 +521,17 @@ int64_t gemm_i16_local(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, in
             MB200_TRY(launch_split_transpose_i16(ctx, call.dev<int16_t>(ib), b_hi, b_lo, k, n, kp));
             MB200_TRY(launch_gemm_i16_tc(ctx, a_hi, a_lo, b_hi, b_lo, a_sums, call.dev<int32_t>(ic), m, n, k, kp));
         } else {
-            // B first: its launch also clears the row sums that A's launch then adds into
-            MB200_TRY(launch_split_rows_i16(ctx, call.dev<int16_t>(ib), b_hi, b_lo, k, n, np, true, nullptr, false,
-                                            a_sums, m));
-            MB200_TRY(launch_split_rows_i16(ctx, call.dev<int16_t>(ia), a_hi, a_lo, m, k, kp, false, a_sums, true,
-                                            nullptr, 0));
+            if (split_i16_pair_usable(call.dev<int16_t>(ia), k, call.dev<int16_t>(ib), n)) {
+                // dense, 16-divisible operands: one launch splits both and stores the row sums
+                MB200_TRY(launch_split_i16_pair(ctx, call.dev<int16_t>(ia), a_hi, a_lo, a_sums, m, k,
+                                                call.dev<int16_t>(ib), b_hi, b_lo, n));
+            } else {
+                // B first: its launch also clears the row sums that A's launch then adds into
+                MB200_TRY(launch_split_rows_i16(ctx, call.dev<int16_t>(ib), b_hi, b_lo, k, n, np, true, nullptr, false,
+                                                a_sums, m));
+                MB200_TRY(launch_split_rows_i16(ctx, call.dev<int16_t>(ia), a_hi, a_lo, m, k, kp, false, a_sums, true,
+                                                nullptr, 0));
+            }
             MB200_TRY(launch_gemm_i16_tc_bmn(ctx, a_hi, a_lo, b_hi, b_lo, a_sums, call.dev<int32_t>(ic), m, n, k, kp, np));
         }
     }
@@ -738,6 +845,7 @@ int64_t mind_b200_devices(void) { return multi_device_count(); }
 int64_t mind_b200_shutdown(void) {
     clear_error();
     multi_shutdown();
+    stager_shutdown();
     destroy_all_contexts();
     return 0;
 }

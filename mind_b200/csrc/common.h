@@ -8,6 +8,7 @@
 #include <stdint.h>
 
 #include <atomic>
+#include <condition_variable>
 #include <functional>
 #include <mutex>
 #include <string>
@@ -140,6 +141,34 @@ int64_t multi_banded(const void* a, size_t a_row_bytes, const void* shared, size
                      size_t c_row_bytes, int64_t m,
                      const std::function<int64_t(const void*, void*, int64_t)>& band);
 
+// ---- pageable host operands through pinned slots (staging.cu) ----
+// A set of chunk copies handed to the staging threads; `last` runs on whichever thread finishes
+// the set (it records the CUDA event the consumers wait for), wait() blocks the submitting
+// thread until that has happened.  A group that was never armed counts as done.
+struct StageGroup {
+    std::mutex mu;
+    std::condition_variable cv;
+    int left = 0;
+    bool done = true;
+    std::function<void()> last;
+    void arm(int chunks, std::function<void()> on_last);
+    void finish_one();
+    void wait();
+};
+struct StageStatus {
+    std::atomic<int> failed{0};
+    void fail(const char*) { failed = 1; }
+};
+bool stager_start();     // pins the slots and starts the threads (first pageable call); false if it cannot
+size_t stager_slot_bytes();  // a staged row (its device pitch) must fit one slot
+void stager_drain();     // every chunk submitted so far has reached its destination
+void stager_shutdown();
+bool host_pointer_is_pageable(const void* p);
+void stage_upload(int device, char* dst, size_t dpitch, const char* src, size_t spitch, size_t width, size_t rows,
+                  cudaStream_t stream, StageGroup* group, std::function<void()> on_last, StageStatus* status);
+void stage_download(int device, char* dst, const char* src, size_t bytes, cudaStream_t stream, StageGroup* group,
+                    std::function<void()> on_last, StageStatus* status);
+
 // Kernel launch accounting (reported through mind_b200_kernel_launches()).
 void count_launch(int n = 1);
 
@@ -196,6 +225,10 @@ int64_t launch_pad_rows_i8(DeviceCtx* ctx, const int8_t* a, int8_t* ap, int64_t 
 int64_t launch_split_rows_i16(DeviceCtx* ctx, const int16_t* a, int8_t* hi, uint8_t* lo, int64_t m,
                               int64_t k, int64_t kp, bool lo_minus_128, int32_t* row_sums, bool sums_are_zero,
                               int32_t* zero_buf, int64_t zero_n);
+// Both operands of the int16 GEMM in one launch (dense rows, K % 16 == 0, N % 16 == 0, aligned bases).
+bool split_i16_pair_usable(const int16_t* a, int64_t k, const int16_t* b, int64_t n);
+int64_t launch_split_i16_pair(DeviceCtx* ctx, const int16_t* a, int8_t* a_hi, uint8_t* a_lo, int32_t* a_row_sums,
+                              int64_t m, int64_t k, const int16_t* b, int8_t* b_hi, uint8_t* b_lo, int64_t n);
 int64_t launch_split_transpose_i16(DeviceCtx* ctx, const int16_t* b, int8_t* bt_hi, uint8_t* bt_lo,
                                    int64_t k, int64_t n, int64_t kp);
 // CUDA-core kernels.

@@ -238,6 +238,7 @@ void prof_end(DeviceCtx* ctx) {
 // every GPU (the reference joins its pool the same way, runtime-support/mind_intrinsics.c:2065-2081).
 __attribute__((destructor)) static void library_unload() {
     multi_shutdown();
+    stager_shutdown();
     destroy_all_contexts();
 }
 

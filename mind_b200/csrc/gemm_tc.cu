@@ -643,17 +643,21 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     lc.dynamicSmemBytes = SMEM;
     lc.stream = ctx->stream;
     cudaLaunchAttribute at[2];
-    at[0].id = cudaLaunchAttributeClusterDimension;
-    at[0].val.clusterDim.x = PAIR;
-    at[0].val.clusterDim.y = 1;
-    at[0].val.clusterDim.z = 1;
-    lc.attrs = at;
-    lc.numAttrs = 1;
-    if (MODE == 3) {  // see griddep_launch_dependents / griddep_wait in the kernel
-        at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        at[1].val.programmaticStreamSerializationAllowed = 1;
-        lc.numAttrs = 2;
+    int n_at = 0;
+    if (PAIR == 2) {
+        at[n_at].id = cudaLaunchAttributeClusterDimension;
+        at[n_at].val.clusterDim.x = PAIR;
+        at[n_at].val.clusterDim.y = 1;
+        at[n_at].val.clusterDim.z = 1;
+        ++n_at;
     }
+    if (MODE == 3) {  // see griddep_launch_dependents / griddep_wait in the kernel
+        at[n_at].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[n_at].val.programmaticStreamSerializationAllowed = 1;
+        ++n_at;
+    }
+    lc.attrs = at;
+    lc.numAttrs = n_at;
     if (PAIR == 2) {
         // Not every SM need be pairable; a pair that is not resident would only start
         // after another one ends, so size the persistent grid to what fits at once.

@@ -176,6 +176,97 @@ __global__ void split_rows_i16_vec_kernel(const uint4* __restrict__ a, uint2* __
     }
 }
 
+// Both operands of the int16 GEMM split in ONE launch, each row owned by a group of G threads
+// (a warp for short rows, the whole block for long ones), so that a row sum is a plain store:
+// no atomics, nothing to clear first.  A thread takes 16 consecutive int16 (two 16-byte loads
+// that bypass L1 and are marked evict-first in L2: the input is read once, while the planes
+// written here are read again by the GEMM right away and should stay in L2) and stores 16 bytes
+// to each plane.  Needs K % 16 == 0, dense rows and 16-byte aligned bases.
+struct SplitJob {
+    const uint4* src;
+    uint4* hi;
+    uint4* lo;
+    int64_t rows, pairs_per_row;  // a pair = two 16-byte vectors = 16 elements
+    uint32_t lo_xor4;
+    int32_t* row_sums;
+    int n_blocks;
+    int group;  // threads that share a row: 32 (short rows) or 256
+};
+
+__device__ __forceinline__ uint64_t evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint4 ld_once(const uint4* p, uint64_t policy) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p), "l"(policy));
+    return v;
+}
+
+__global__ void __launch_bounds__(256) split_i16_fused_kernel(const SplitJob j0, const SplitJob j1) {
+    __shared__ int warp_part[8];
+    const bool first = (int)blockIdx.x < j0.n_blocks;
+    const SplitJob& job = first ? j0 : j1;
+    const int b = first ? (int)blockIdx.x : (int)blockIdx.x - j0.n_blocks;
+    const int G = job.group, GROUPS = 256 / G;  // uniform over the block
+    const int g = threadIdx.x / G, t = threadIdx.x % G;
+    const int64_t ppr = job.pairs_per_row;
+    const uint64_t once = evict_first_policy();
+    for (int64_t row = (int64_t)b * GROUPS + g; row < job.rows; row += (int64_t)job.n_blocks * GROUPS) {
+        int sum = 0;
+        const uint4* src = job.src + row * ppr * 2;
+        uint4* hi = job.hi + row * ppr;
+        uint4* lo = job.lo + row * ppr;
+        for (int64_t p0 = t; p0 < ppr; p0 += 2 * G) {
+            const int64_t p1 = p0 + G;
+            const bool two = p1 < ppr;
+            uint4 v[4];
+            v[0] = ld_once(src + 2 * p0, once);
+            v[1] = ld_once(src + 2 * p0 + 1, once);
+            if (two) {
+                v[2] = ld_once(src + 2 * p1, once);
+                v[3] = ld_once(src + 2 * p1 + 1, once);
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                if (u == 1 && !two) break;
+                const uint4 x = v[2 * u], y = v[2 * u + 1];
+                const uint4 h = make_uint4(__byte_perm(x.x, x.y, 0x7531), __byte_perm(x.z, x.w, 0x7531),
+                                           __byte_perm(y.x, y.y, 0x7531), __byte_perm(y.z, y.w, 0x7531));
+                const uint4 l = make_uint4(__byte_perm(x.x, x.y, 0x6420), __byte_perm(x.z, x.w, 0x6420),
+                                           __byte_perm(y.x, y.y, 0x6420), __byte_perm(y.z, y.w, 0x6420));
+                const int64_t p = u ? p1 : p0;
+                hi[p] = h;
+                lo[p] = make_uint4(l.x ^ job.lo_xor4, l.y ^ job.lo_xor4, l.z ^ job.lo_xor4, l.w ^ job.lo_xor4);
+                if (job.row_sums)
+                    sum += 256 * (__dp4a((int)h.x, 0x01010101, 0) + __dp4a((int)h.y, 0x01010101, 0) +
+                                  __dp4a((int)h.z, 0x01010101, 0) + __dp4a((int)h.w, 0x01010101, 0)) +
+                           (int)(__dp4a(l.x, 0x01010101u, 0u) + __dp4a(l.y, 0x01010101u, 0u) +
+                                 __dp4a(l.z, 0x01010101u, 0u) + __dp4a(l.w, 0x01010101u, 0u));
+            }
+        }
+        if (job.row_sums) {  // uniform per group; for G = 256 the whole block walks the same rows
+            sum = __reduce_add_sync(0xffffffffu, sum);
+            if (G == 32) {
+                if (t == 0) job.row_sums[row] = sum;
+            } else {
+                if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = sum;
+                __syncthreads();
+                if (threadIdx.x == 0) {
+                    int total = 0;
+#pragma unroll
+                    for (int w = 0; w < 8; ++w) total += warp_part[w];
+                    job.row_sums[row] = total;
+                }
+                __syncthreads();
+            }
+        }
+    }
+}
+
 // int32 matrix [rows][cols] -> byte planes [rows][pitch] (cols % 4 == 0, 16-byte aligned source).
 // WHAT = 0: the four bytes of each element (plane 3 holds the signed top byte);
 // WHAT = 1: the two bytes of (element >> 16), i.e. planes 0 / 1 = bytes 2 / 3 of the element.
@@ -259,6 +350,40 @@ int64_t launch_pad_rows_i8(DeviceCtx* ctx, const int8_t* a, int8_t* ap, int64_t 
     pad_rows_i8_kernel<<<grid, 256, 0, ctx->stream>>>(a, ap, m, k, kp);
     count_launch();
     return check_launch("pad_rows_i8_kernel");
+}
+
+bool split_i16_pair_usable(const int16_t* a, int64_t k, const int16_t* b, int64_t n) {
+    return k % 16 == 0 && n % 16 == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0 &&
+           reinterpret_cast<uintptr_t>(b) % 16 == 0;
+}
+
+// A (m x k, plain low plane, row sums) and B (k x n, low plane minus 128) in one launch; the
+// planes keep each operand's own orientation and pitch (k resp. n).
+int64_t launch_split_i16_pair(DeviceCtx* ctx, const int16_t* a, int8_t* a_hi, uint8_t* a_lo, int32_t* a_row_sums,
+                              int64_t m, int64_t k, const int16_t* b, int8_t* b_hi, uint8_t* b_lo, int64_t n) {
+    auto job = [&](const int16_t* src, int8_t* hi, uint8_t* lo, int64_t rows, int64_t cols, uint32_t x, int32_t* sums) {
+        SplitJob j;
+        j.src = reinterpret_cast<const uint4*>(src);
+        j.hi = reinterpret_cast<uint4*>(hi);
+        j.lo = reinterpret_cast<uint4*>(lo);
+        j.rows = rows;
+        j.pairs_per_row = cols / 16;
+        j.lo_xor4 = x * 0x01010101u;
+        j.row_sums = sums;
+        j.group = j.pairs_per_row <= 64 ? 32 : 256;  // a warp per short row, the block per long one
+        const int groups = 256 / j.group;
+        int64_t blocks = (rows + groups - 1) / groups;
+        const int64_t cap = (int64_t)ctx->sm_count * 16;
+        j.n_blocks = (int)(blocks < cap ? blocks : cap);
+        if (j.n_blocks < 1) j.n_blocks = 1;
+        return j;
+    };
+    const SplitJob ja = job(a, a_hi, a_lo, m, k, 0u, a_row_sums);
+    const SplitJob jb = job(b, b_hi, b_lo, k, n, 0x80u, nullptr);
+    const unsigned grid = (unsigned)(ja.n_blocks + jb.n_blocks);
+    split_i16_fused_kernel<<<grid, 256, 0, ctx->stream>>>(ja, jb);
+    count_launch();
+    return check_launch("split_i16_fused_kernel");
 }
 
 int64_t launch_split_rows_i16(DeviceCtx* ctx, const int16_t* a, int8_t* hi, uint8_t* lo, int64_t m,
