@@ -218,7 +218,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(misc);
     // from here on global memory is read and written: the kernel before this one must be done
-    if (MODE == 3) griddep_wait();
+    // (int16: that kernel is the limb split, whose tail this kernel's set-up overlaps)
+    if (MODE == 3 || MODE == 1) griddep_wait();
 
     // Work items: (tile, split) with the split index fastest; a split is a contiguous range of
     // k-blocks, never empty (the launcher sees to that).
@@ -600,9 +601,12 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     // 16 m-tiles per group and no hints): groups of 8 m-tiles keep the group's A panels
     // (8 x 256 rows x K) L2-resident across successive waves; A is marked evict-last, B is left
     // at the normal policy (marking it evict-first throws away panels a wave still shares).
-    const int knob_group = tuning().group_m.load();
+    // Odd groups walk N backwards (a group starts on the B panels the last one ended on): 6 % fewer
+    // DRAM reads again at 16384^3 (ncu, one launch each: 6.16 -> 5.77 GB; groups of 4 / 6 / 12 / 16
+    // m-tiles read 7.7 - 8.8 / 6.3 - 6.9 / 6.1 - 6.2 / 6.1 GB).
+    const int knob_group = tuning().group_m.load(), knob_raster = tuning().raster.load();
     p.group_m = knob_group > 0 ? knob_group : 8;
-    p.raster = tuning().raster.load();
+    p.raster = knob_raster == 0 ? 1 : (knob_raster == 2 ? 0 : knob_raster);  // 0 = default, 2 = always forwards
     p.hint_a = 1;
     p.hint_b = 0;
     const long long total = (long long)p.m_tiles * p.n_tiles;
@@ -651,7 +655,7 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
         at[n_at].val.clusterDim.z = 1;
         ++n_at;
     }
-    if (MODE == 3) {  // see griddep_launch_dependents / griddep_wait in the kernel
+    if (MODE == 3 || MODE == 1) {  // see griddep_launch_dependents / griddep_wait in the kernel
         at[n_at].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         at[n_at].val.programmaticStreamSerializationAllowed = 1;
         ++n_at;

@@ -208,6 +208,8 @@ __device__ __forceinline__ uint4 ld_once(const uint4* p, uint64_t policy) {
 
 __global__ void __launch_bounds__(256) split_i16_fused_kernel(const SplitJob j0, const SplitJob j1) {
     __shared__ int warp_part[8];
+    // the GEMM that follows is launched so that it may start (up to its own wait) while this runs
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const bool first = (int)blockIdx.x < j0.n_blocks;
     const SplitJob& job = first ? j0 : j1;
     const int b = first ? (int)blockIdx.x : (int)blockIdx.x - j0.n_blocks;
@@ -372,14 +374,29 @@ int64_t launch_split_i16_pair(DeviceCtx* ctx, const int16_t* a, int8_t* a_hi, ui
         j.row_sums = sums;
         j.group = j.pairs_per_row <= 64 ? 32 : 256;  // a warp per short row, the block per long one
         const int groups = 256 / j.group;
-        int64_t blocks = (rows + groups - 1) / groups;
-        const int64_t cap = (int64_t)ctx->sm_count * 16;
-        j.n_blocks = (int)(blocks < cap ? blocks : cap);
+        j.n_blocks = (int)((rows + groups - 1) / groups);  // capped below: one wave for both jobs
         if (j.n_blocks < 1) j.n_blocks = 1;
         return j;
     };
-    const SplitJob ja = job(a, a_hi, a_lo, m, k, 0u, a_row_sums);
-    const SplitJob jb = job(b, b_hi, b_lo, k, n, 0x80u, nullptr);
+    SplitJob ja = job(a, a_hi, a_lo, m, k, 0u, a_row_sums);
+    SplitJob jb = job(b, b_hi, b_lo, k, n, 0x80u, nullptr);
+    // One wave: eight blocks per SM in all, shared between the operands by their sizes, each
+    // block walking several rows (a second wave would run at a fraction of the bandwidth).
+    const int64_t wave = (int64_t)ctx->sm_count * 8;
+    if ((int64_t)ja.n_blocks + jb.n_blocks > wave) {
+        const double wa = (double)m * k, wb = (double)k * n;
+        int64_t na = (int64_t)((double)wave * wa / (wa + wb));
+        if (na < 1) na = 1;
+        if (na > wave - 1) na = wave - 1;
+        if (na > ja.n_blocks) na = ja.n_blocks;
+        int64_t nb = wave - na;
+        if (nb > jb.n_blocks) {
+            nb = jb.n_blocks;
+            na = wave - nb < ja.n_blocks ? wave - nb : ja.n_blocks;
+        }
+        ja.n_blocks = (int)na;
+        jb.n_blocks = (int)nb;
+    }
     const unsigned grid = (unsigned)(ja.n_blocks + jb.n_blocks);
     split_i16_fused_kernel<<<grid, 256, 0, ctx->stream>>>(ja, jb);
     count_launch();
