@@ -438,6 +438,58 @@ def latency_workloads(blas, torch, stream):
     return out
 
 
+def probe_links(max_gpus, up_mib=64, down_mib=128, reps=8):
+    """The host-link ceiling that bounds `e2e`: pinned host <-> device copies on 1, 2, 4 ... GPUs at
+    once from ONE process (one thread and two streams per GPU, upload and download running
+    together, like the library's multi-GPU path), timed with CUDA events per device, slowest
+    device counted.  Prints one JSON line per GPU count."""
+    import torch
+    have = torch.cuda.device_count()
+    counts = [g for g in (1, 2, 4, 8, 16) if g <= min(max_gpus, have)]
+    for g in counts:
+        results = [None] * g
+        ready = threading.Barrier(g)
+
+        def work(d):
+            torch.cuda.set_device(d)
+            hin = torch.empty(up_mib << 20, dtype=torch.uint8).pin_memory()
+            hout = torch.empty(down_mib << 20, dtype=torch.uint8).pin_memory()
+            din = torch.empty(up_mib << 20, dtype=torch.uint8, device=f"cuda:{d}")
+            dout = torch.empty(down_mib << 20, dtype=torch.uint8, device=f"cuda:{d}")
+            s_up, s_down = torch.cuda.Stream(d), torch.cuda.Stream(d)
+            out = {}
+            for mode in ("up", "down", "both"):
+                for timed in (False, True):
+                    torch.cuda.synchronize(d)
+                    ready.wait()
+                    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+                    ev[0].record(s_up); ev[2].record(s_down)
+                    for _ in range(reps if timed else 1):
+                        if mode != "down":
+                            with torch.cuda.stream(s_up):
+                                din.copy_(hin, non_blocking=True)
+                        if mode != "up":
+                            with torch.cuda.stream(s_down):
+                                hout.copy_(dout, non_blocking=True)
+                    ev[1].record(s_up); ev[3].record(s_down)
+                    torch.cuda.synchronize(d)
+                    if timed:
+                        out[mode] = max(ev[0].elapsed_time(ev[1]), ev[2].elapsed_time(ev[3])) / reps
+            results[d] = out
+
+        threads = [threading.Thread(target=work, args=(d,)) for d in range(g)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        line = {"probe": "pinned host link", "gpus": g, "up_mib_per_gpu": up_mib, "down_mib_per_gpu": down_mib}
+        for mode, nbytes in (("up", up_mib), ("down", down_mib), ("both", up_mib + down_mib)):
+            worst = max(r[mode] for r in results)
+            line[f"{mode}_ms"] = round(worst, 3)
+            line[f"{mode}_gb_s_aggregate"] = round(g * (nbytes << 20) / (worst * 1e-3) / 1e9, 1)
+        print(json.dumps(line), flush=True)
+
+
 def whole_output_gate(w, blas, torch, a, b, c, rows, k, n, rank, path=0):
     """Byte-identity gate on the WHOLE output of this rank before any timing (the reference's
     benches compare the whole output with their scalar oracle, benches/det_matmul_i8.rs:310-352;
@@ -815,7 +867,12 @@ def main():
     ap.add_argument("--no-others", action="store_true", help="skip the other configurations' ride-along numbers")
     ap.add_argument("--no-pageable", action="store_true", help="skip the pageable-host end-to-end call")
     ap.add_argument("--gather", action="store_true", help="N > 1: also time the optional all-gather of C")
+    ap.add_argument("--probe-links", type=int, default=0, metavar="G",
+                    help="instead of the bench: pinned host<->device copy ceiling on 1, 2, 4 ... G GPUs at once")
     args = ap.parse_args()
+    if args.probe_links:
+        probe_links(args.probe_links)
+        return
     if args.warmup < 3:
         args.warmup = 3
     w = dict(WORKLOADS[args.workload])

@@ -186,7 +186,8 @@ int64_t mind_b200_shutdown(void);
  * 8 / 9 = the hybrid with its two halves one after the other / side by side on two streams
  * (default: side by side up to 2^31 products, where the tensor-core half is latency-bound);
  * 10 / 11 = int8 GEMM: the narrow-tile kernel (128 x 64 tiles, for products with few tiles)
- * always / never (default: when the wide tiles would leave most SMs idle).
+ * always / never (default: when the wide tiles would leave most SMs idle); 12 / 13 = int8 GEMM:
+ * the kernel with 256 x 512 tiles on CTA pairs always / never (default: for long K and many tiles).
  * Every path gives identical bytes.  The setting is process-wide and meant for tests and
  * measurements; a call that is already running keeps the kernels it chose. */
 int64_t mind_b200_set_gemm_path(int64_t path);

@@ -815,13 +815,14 @@ int64_t mind_b200_reserve(int64_t scratch_bytes, int64_t staging_bytes) {
 
 int64_t mind_b200_set_gemm_path(int64_t path) {
     clear_error();
-    if (path < 0 || path > 11)
-        return fail(MIND_B200_ERR_INVALID, "gemm path must be 0 (auto), 1 (CUDA cores), 2 / 3 (CTA pairs / single CTA), 4 / 5 (the same with B transposed first), 6 / 7 (Q16.16: FP64-pipe kernel alone / tensor-core hybrid), 8 / 9 (the hybrid with its halves in sequence / side by side) or 10 / 11 (int8: the narrow-tile kernel always / never)");
+    if (path < 0 || path > 13)
+        return fail(MIND_B200_ERR_INVALID, "gemm path must be 0 (auto), 1 (CUDA cores), 2 / 3 (CTA pairs / single CTA), 4 / 5 (the same with B transposed first), 6 / 7 (Q16.16: FP64-pipe kernel alone / tensor-core hybrid), 8 / 9 (the hybrid with its halves in sequence / side by side) 10 / 11 (int8: the narrow-tile kernel always / never) or 12 / 13 (int8: the 256 x 512-tile pair kernel always / never)");
     Tuning& t = tuning();
     t.force_transpose = (path == 4 || path == 5) ? 1 : 0;
     t.q16_mode = path == 6 ? 6 : (path >= 7 && path <= 9) ? 7 : 0;
     t.q16_side_sms = path == 8 ? 0 : path == 9 ? 16 : -1;
     t.small_tile = path == 10 ? 1 : (path == 0 ? -1 : 0);
+    t.wide_pair = path == 12 ? 1 : (path == 0 ? -1 : 0);
     t.gemm_path = path == 1 ? 1 : 0;
     t.pair_mode = (path == 2 || path == 4) ? 2 : (path == 3 || path == 5) ? 1 : 0;
     return 0;
@@ -830,6 +831,7 @@ int64_t mind_b200_set_gemm_path(int64_t path) {
 int64_t mind_b200_set_tile_order(int64_t group_m, int64_t raster) {
     clear_error();
     if (group_m < 0 || group_m > 64 || raster < 0 || raster > 3) return fail(MIND_B200_ERR_INVALID, "bad tile order");
+    // (raster 3 = default order, with the 256 x 512 kernel's epilogue in its transposing form: a measurement knob)
     tuning().group_m = (int)group_m;
     tuning().raster = (int)raster;
     return 0;

@@ -36,6 +36,7 @@ struct Tuning {
     std::atomic<int> q16_side_sms{-1};    // hybrid: SMs of the tensor-core half beside the FP64 half (-1 = by size)
     std::atomic<int> pair_mode{0};        // CTAs per int8 tile: 1, 2, or 0 = pick per call
     std::atomic<int> small_tile{-1};      // int8 GEMM narrow-tile kernel: -1 = by shape, 0 = never, 1 = always
+    std::atomic<int> wide_pair{-1};       // int8 GEMM 256 x 512-tile pair kernel: -1 = by shape, 0 = never, 1 = always
     std::atomic<int> group_m{0};          // int8 tile order: m-tiles per group (0 = default)
     std::atomic<int> raster{0};           // int8 tile order variant (0 = default)
 };

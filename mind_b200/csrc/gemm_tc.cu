@@ -30,6 +30,11 @@
 //                 two such tiles but eight narrow ones, each with a quarter of the epilogue).
 //                 A B that is read in place arrives as TMA boxes of 64 bytes of N by 128 rows of
 //                 K with the 64-byte swizzle, the canonical MN-major layout of a 64-wide operand.
+// MODE 5 (int8, CTA pair, 256 x 512 tiles): two MMAs of N = 256 per 32 of K read the same A
+//                 slab, so a pair moves 48 KB per 128 of K for twice the work of MODE 0's 32 KB:
+//                 a quarter less L2 -> shared-memory traffic per product, and the same bytes in
+//                 flight cover a third more latency.  The 512 columns fill TMEM, so the epilogue
+//                 (eight warps) does not overlap the next main loop: for long K only.
 // The PAIR = 2 variant (int8) runs one tile on a pair of CTAs (a 2-CTA cluster,
 // tcgen05 cta_group::2): 256 rows of A (128 per CTA) by BLOCK_N rows of Bt, of which
 // each CTA stages only its half, which halves the shared-memory traffic per MMA.
@@ -50,39 +55,45 @@ constexpr int UMMA_K = 32;              // K of one tcgen05.mma kind::i8
 constexpr int TC_THREADS = 192;  // TMA warp + MMA warp + four epilogue warps (see epi_warps)
 constexpr int A_TILE_BYTES = BLOCK_M * BLOCK_K;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
-constexpr int EPI_PATCH_WORDS = 32 * 33;  // per epilogue warp: a 32 x 32 block of outputs, padded rows
+constexpr int EPI_PATCH_WORDS = 32 * 32;  // per epilogue warp: a 32 x 32 block of outputs (4 KiB, 1024-byte aligned)
 
 template <int MODE, int PAIR>
 struct Cfg;
 template <>
 struct Cfg<0, 1> {
-    static constexpr int BLOCK_N = 256, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 2, STAGES = 4, TMEM_COLS = 512;
+    static constexpr int BLOCK_N = 256, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 2, STAGES = 4, TMEM_COLS = 512, NSUB = 1;
 };
 template <>
 struct Cfg<1, 1> {  // int16: two accumulators of 2 x BLOCK_N columns (A high / A low times [B high | B low])
-    static constexpr int BLOCK_N = 128, NA = 2, NB = 2, NACC = 4, ACC_STAGES = 1, STAGES = 3, TMEM_COLS = 512;
+    static constexpr int BLOCK_N = 128, NA = 2, NB = 2, NACC = 4, ACC_STAGES = 1, STAGES = 3, TMEM_COLS = 512, NSUB = 1;
 };
 template <>
 struct Cfg<0, 2> {
-    static constexpr int BLOCK_N = 256, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 2, STAGES = 6, TMEM_COLS = 512;
+    static constexpr int BLOCK_N = 256, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 2, STAGES = 6, TMEM_COLS = 512, NSUB = 1;
 };
 
 template <>
 struct Cfg<2, 1> {  // linear part of the Q16.16 product: a (4 limbs) x bh (2 limbs), 4 accumulators
-    static constexpr int BLOCK_N = 128, NA = 4, NB = 2, NACC = 4, ACC_STAGES = 1, STAGES = 2, TMEM_COLS = 512;
+    static constexpr int BLOCK_N = 128, NA = 4, NB = 2, NACC = 4, ACC_STAGES = 1, STAGES = 2, TMEM_COLS = 512, NSUB = 1;
 };
 template <>
 struct Cfg<4, 1> {  // the same with 64-column tiles: twice the CTAs for mid-sized products, two accumulator stages
-    static constexpr int BLOCK_N = 64, NA = 4, NB = 2, NACC = 4, ACC_STAGES = 2, STAGES = 2, TMEM_COLS = 512;
+    static constexpr int BLOCK_N = 64, NA = 4, NB = 2, NACC = 4, ACC_STAGES = 2, STAGES = 2, TMEM_COLS = 512, NSUB = 1;
 };
 template <>
 struct Cfg<3, 1> {  // int8, narrow tiles
-    static constexpr int BLOCK_N = 64, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 4, STAGES = 3, TMEM_COLS = 256;
+    static constexpr int BLOCK_N = 64, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 4, STAGES = 3, TMEM_COLS = 256, NSUB = 1;
+};
+template <>
+struct Cfg<5, 2> {  // int8, 256 x 512 tiles on a CTA pair: two MMAs of N = 256 share every A slab
+    static constexpr int BLOCK_N = 512, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 1, STAGES = 4, TMEM_COLS = 512, NSUB = 2;
 };
 
 // Epilogue warps of a mode: four, or eight where a tile has four accumulators to drain.
 template <int MODE, int PAIR>
-__host__ __device__ constexpr int epi_warps() { return Cfg<MODE, PAIR>::NACC == 4 ? 8 : 4; }
+__host__ __device__ constexpr int epi_warps() {
+    return (Cfg<MODE, PAIR>::NACC == 4 || Cfg<MODE, PAIR>::BLOCK_N == 512) ? 8 : 4;
+}
 template <int MODE, int PAIR>
 __host__ __device__ constexpr int tc_threads() { return 64 + 32 * epi_warps<MODE, PAIR>(); }
 
@@ -96,6 +107,7 @@ struct TcParams {
     const int32_t* row_sums;  // int16 mode: sum of every row of A
     int accumulate;           // add onto C with red.global.add (C shared with a kernel running beside this one)
     int k_splits;             // > 1: every tile's K range is cut into this many work items (accumulate is set, C zeroed)
+    int tma_store;            // the epilogue hands its 32 x 32 blocks to TMA stores (C 16-byte aligned, N % 4 == 0, no accumulate)
     int* err;
 };
 
@@ -138,11 +150,12 @@ __global__ void __launch_bounds__(tc_threads<MODE, PAIR>(), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
                const __grid_constant__ CUtensorMap tm_a2, const __grid_constant__ CUtensorMap tm_a3,
                const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
-               const TcParams p) {
+               const __grid_constant__ CUtensorMap tm_c, const TcParams p) {
     constexpr bool Q16LIN = MODE == 2 || MODE == 4;  // linear part of the Q16.16 product (wide / narrow tiles)
     static_assert(!Q16LIN || (PAIR == 1 && BMN), "the Q16.16 linear-part mode is single-CTA, B in place");
     static_assert(MODE != 1 || PAIR == 1, "the int16 mode is single-CTA");
     static_assert(MODE != 3 || PAIR == 1, "the narrow-tile mode is single-CTA");
+    static_assert(MODE != 5 || PAIR == 2, "the 256 x 512 mode runs on a CTA pair");
     using cfg = Cfg<MODE, PAIR>;
     constexpr int BLOCK_N = cfg::BLOCK_N;
     constexpr int B_ROWS = BLOCK_N / PAIR;  // columns of the output (rows of Bt) this CTA stages
@@ -153,6 +166,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
     static_assert(!BMN || B_ROWS % BOX_N == 0, "an MN-major B tile is made of whole boxes");
     static_assert(BOX_N == 128 || BOX_N == 64, "box width = swizzle width");
     constexpr int B_BOX_BYTES = BOX_N * BLOCK_K;  // one MN-major box
+    // N sub-tiles of a stage (one MMA each per 32 of K, all reading the same A slab); a sub-tile
+    // is UMMA_N columns of the output, of which this CTA stages SUB_ROWS.
+    constexpr int NSUB = cfg::NSUB;
+    constexpr int UMMA_N = BLOCK_N / NSUB;
+    constexpr int SUB_ROWS = B_ROWS / NSUB;
+    constexpr int SUB_TILE_BYTES = SUB_ROWS * BLOCK_K;
+    static_assert(NSUB == 1 || (PAIR == 2 && SUB_ROWS == 128), "sub-tiles are single 128-column boxes of a CTA pair");
     constexpr int STAGE_BYTES = cfg::NA * A_TILE_BYTES + cfg::NB * B_TILE_BYTES;
     constexpr int STAGES = cfg::STAGES;
     constexpr int ACC_STAGES = cfg::ACC_STAGES;
@@ -173,7 +193,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
     const uint32_t tfull0 = bars + 16 * STAGES, tempty0 = tfull0 + 8 * ACC_STAGES;
     const uint32_t tmem_slot = tempty0 + 8 * ACC_STAGES;
     int* const misc = reinterpret_cast<int*>(smem_raw + (tmem_slot - raw));
-    const uint32_t patches0 = bars + 256;  // one 32 x 33-word patch per epilogue warp
+    const uint32_t patches0 = bars + 1024;  // one 32 x 32-word patch per epilogue warp, 1024-byte aligned
     volatile int* const abort_s = misc + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -279,10 +299,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                         const uint32_t db = dst + cfg::NA * A_TILE_BYTES;
 #pragma unroll
                         for (int j = 0; j < B_ROWS / 128; ++j) {
-                            tma_load_2d_pair(db + j * B_BOX_BYTES, &tm_b0, bar, row_b + 128 * j, kx, pol_b);
+                            // with sub-tiles, box j is this CTA's 128 columns of sub-tile j
+                            const int col = NSUB == 1 ? row_b + 128 * j : tn * BLOCK_N + j * UMMA_N + (int)cta * SUB_ROWS;
+                            tma_load_2d_pair(db + j * B_BOX_BYTES, &tm_b0, bar, col, kx, pol_b);
                             if (cfg::NB == 2)
-                                tma_load_2d_pair(db + B_TILE_BYTES + j * B_BOX_BYTES, &tm_b1, bar, row_b + 128 * j, kx, pol_b);
+                                tma_load_2d_pair(db + B_TILE_BYTES + j * B_BOX_BYTES, &tm_b1, bar, col, kx, pol_b);
                         }
+                    } else if (NSUB == 2) {
+                        const uint32_t bar = mapa(full0 + 8 * s, 0);
+                        if (leader) mbar_arrive_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
+                        tma_load_2d_pair(dst, &tm_a0, bar, kx, row_a, pol_a);
+                        const uint32_t db = dst + cfg::NA * A_TILE_BYTES;
+#pragma unroll
+                        for (int j = 0; j < NSUB; ++j)
+                            tma_load_2d_pair(db + j * SUB_TILE_BYTES, &tm_b0, bar, kx,
+                                             tn * BLOCK_N + j * UMMA_N + (int)cta * SUB_ROWS, pol_b);
                     } else {
                         // Both CTAs' copies complete on the LEADER's full barrier (it alone issues
                         // MMAs).  Only the leader arrives, expecting the bytes of both; the peer's
@@ -302,10 +333,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
     } else if (warp == 1) {
         // -------------------------------------------------------------- MMA issuer
         if (lane == 0 && leader) {
-            constexpr uint32_t ID_SS = idesc_i8(UMMA_M, BLOCK_N, true, true, BMN);
-            constexpr uint32_t ID_SU = idesc_i8(UMMA_M, BLOCK_N, true, false, BMN);
-            constexpr uint32_t ID_US = idesc_i8(UMMA_M, BLOCK_N, false, true, BMN);
-            constexpr uint32_t ID_UU = idesc_i8(UMMA_M, BLOCK_N, false, false, BMN);
+            constexpr uint32_t ID_SS = idesc_i8(UMMA_M, UMMA_N, true, true, BMN);
+            constexpr uint32_t ID_SU = idesc_i8(UMMA_M, UMMA_N, true, false, BMN);
+            constexpr uint32_t ID_US = idesc_i8(UMMA_M, UMMA_N, false, true, BMN);
+            constexpr uint32_t ID_UU = idesc_i8(UMMA_M, UMMA_N, false, false, BMN);
             // Descriptor step per MMA (32 of K): 32 bytes along a K-major row, or 32 K-rows of
             // 128 bytes in an MN-major tile; in units of 16 bytes.
             constexpr uint64_t B_KSTEP = BMN ? (UMMA_K * BOX_N) >> 4 : UMMA_K >> 4;
@@ -335,7 +366,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                         const uint32_t acc = (kb != kb0 || ks != 0) ? 1u : 0u;
                         const uint64_t koff = (uint64_t)((ks * UMMA_K) >> 4);
                         const uint64_t kb_off = (uint64_t)ks * B_KSTEP;
-                        if (MODE == 0 || MODE == 3) {
+                        if (MODE == 5) {
+#pragma unroll
+                            for (int j = 0; j < NSUB; ++j) {
+                                const uint32_t sbj = sb + j * SUB_TILE_BYTES;
+                                const uint64_t dbj = BMN ? smem_desc_mn_sw128(sbj, B_BOX_BYTES) : smem_desc_k_sw128(sbj);
+                                mma_i8<PAIR>(d0 + j * UMMA_N, da0 + koff, dbj + kb_off, ID_SS, acc);
+                            }
+                        } else if (MODE == 0 || MODE == 3) {
                             mma_i8<PAIR>(d0, da0 + koff, db0 + kb_off, ID_SS, acc);
                         } else if (Q16LIN) {
                             // a = a3*2^24 + a2*2^16 + a1*2^8 + a0 (a3 signed), bh = bh1*256 + bh0 (bh1
@@ -385,6 +423,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
         const int q = warp & 3;  // TMEM lane quadrant this warp may read
         const int c_first = ((warp - 2) / 4) * EPI_COLS;  // its share of the tile's columns
         uint32_t* const patch = reinterpret_cast<uint32_t*>(smem_raw + (patches0 - raw)) + (warp - 2) * EPI_PATCH_WORDS;
+        const uint32_t patch_addr = patches0 + (uint32_t)(warp - 2) * (EPI_PATCH_WORDS * 4);
         uint32_t tcount = 0;
         for (int item = tile_first; item < total_tiles; item += tile_step, ++tcount) {
             int tm, tn;
@@ -404,7 +443,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
             for (int c0 = c_first; c0 < c_first + EPI_COLS; c0 += 32) {
                 if (col_tile + c0 >= p.n) break;  // warp-uniform
                 uint32_t v[32];
-                if (MODE == 0 || MODE == 3) {
+                if (MODE == 0 || MODE == 3 || MODE == 5) {
                     tmem_ld32(t0 + c0, v);
                     tmem_ld_wait();
                 } else if (Q16LIN) {
@@ -436,14 +475,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                             v[16 * h + j] = (hh[j] << 16) + ((hl[j] + lh[j]) << 8) + ll[j] + back;
                     }
                 }
+                if (p.tma_store && row - lane < p.m) {  // (a block wholly below the matrix has nothing to store)
+                    // The block goes to this warp's patch as 32 rows of 128 bytes in the 128-byte
+                    // swizzle (lane = row; its eight 16-byte pieces land on eight different bank
+                    // groups), and ONE bulk tensor store writes it out: nine instructions per block
+                    // instead of ninety-six, and rows / columns past the matrix edge are clipped by
+                    // the hardware.  The patch is reused once the previous store has read it.
+                    if (lane == 0) bulk_wait_group_read<0>();
+                    __syncwarp();
+                    const uint32_t prow = patch_addr + (uint32_t)lane * 128u;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        st_shared_v4(prow + (uint32_t)((j ^ (lane & 7)) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tm_c, patch_addr, col_tile + c0, row - lane);
+                        bulk_commit_group();
+                    }
+                    continue;
+                }
+                if (p.tma_store) continue;
                 // Lane = row in TMEM, but a store wants lane = column: the 32 x 32 block goes through
-                // this warp's shared-memory patch (row pitch 33 words: no bank conflicts either way),
-                // and every store / atomic instruction then covers one 128-byte line of a row.
-                // Straight from registers each lane wrote 16 bytes of a different row, which held
-                // output-bound shapes (short K) to a third of the write bandwidth.
+                // this warp's shared-memory patch (word j of row l at l * 32 + (j ^ l): no bank
+                // conflicts either way), and every store / atomic instruction then covers one
+                // 128-byte line of a row.  Straight from registers each lane wrote 16 bytes of a
+                // different row, which held output-bound shapes (short K) to a third of the write
+                // bandwidth.
                 __syncwarp();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) patch[lane * 33 + j] = v[j];
+                for (int j = 0; j < 32; ++j) patch[lane * 32 + (j ^ lane)] = v[j];
                 __syncwarp();
                 const int col = col_tile + c0 + lane;
                 const int row_first = row - lane;
@@ -452,7 +513,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
 #pragma unroll 8
                     for (int r = 0; r < 32; ++r) {
                         if (row_first + r >= p.m) break;  // warp-uniform
-                        const uint32_t x = patch[r * 33 + lane];
+                        const uint32_t x = patch[r * 32 + (lane ^ r)];
                         if (p.accumulate)
                             atomicAdd(reinterpret_cast<unsigned int*>(dst), x);
                         else
@@ -470,6 +531,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                     mbar_arrive_cluster(tempty0 + 8 * as, 0);
             }
         }
+        if (lane == 0) bulk_wait_group<0>();  // this warp's tensor stores have left shared memory and landed
     }
 
     // ------------------------------------------------------------------ teardown
@@ -523,6 +585,35 @@ struct TmapCache {
     int used = 0, next = 0;
 };
 
+// Map over the int32 output C[m][n] for the epilogue's stores: boxes of 32 columns (128 bytes) by
+// 32 rows, read from shared memory in the 128-byte swizzle.  Needs a 16-byte aligned base and
+// N % 4 == 0 (the caller checks).
+int64_t make_tmap_c(CUtensorMap* tm, int32_t* c, int64_t n, int64_t m) {
+    static thread_local TmapCache cache;
+    const TmapKey want{c, n, m, n * 4, 32, -32};
+    for (int i = 0; i < cache.used; ++i)
+        if (cache.key[i] == want) {
+            *tm = cache.map[i];
+            return 0;
+        }
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(MIND_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)m};
+    cuuint64_t strides[1] = {(cuuint64_t)n * 4};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, c, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(MIND_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed for the output with CUresult %d (n=%lld m=%lld)",
+                    (int)r, (long long)n, (long long)m);
+    cache.key[cache.next] = want;
+    cache.map[cache.next] = *tm;
+    cache.next = (cache.next + 1) % TmapCache::N;
+    if (cache.used < TmapCache::N) ++cache.used;
+    return 0;
+}
+
 int64_t make_tmap(CUtensorMap* tm, const void* base, int64_t k, int64_t rows, int64_t pitch,
                   int box_rows, int box_bytes = BLOCK_K) {
     static thread_local TmapCache cache;
@@ -563,7 +654,7 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     constexpr int B_ROWS = cfg::BLOCK_N / PAIR;
     constexpr int BOX_N = B_ROWS < 128 ? B_ROWS : 128;  // width of an MN-major box = its swizzle width
     constexpr int STAGE_BYTES = cfg::NA * A_TILE_BYTES + cfg::NB * B_ROWS * BLOCK_K;
-    constexpr int SMEM = cfg::STAGES * STAGE_BYTES + 1024 + 256 + epi_warps<MODE, PAIR>() * EPI_PATCH_WORDS * 4;
+    constexpr int SMEM = cfg::STAGES * STAGE_BYTES + 1024 + 1024 + epi_warps<MODE, PAIR>() * EPI_PATCH_WORDS * 4;
     static_assert(SMEM <= 232448, "shared memory budget");
     if (m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff)
         return fail(MIND_B200_ERR_TOO_LARGE, "GEMM dimension above 2^31-1");
@@ -572,7 +663,7 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     if (BMN)
         MB200_TRY(make_tmap(&tb0, b0, n, k, kp_b, BLOCK_K, BOX_N));  // boxes of BOX_N columns x 128 rows of K
     else
-        MB200_TRY(make_tmap(&tb0, b0, k, n, kp_b, B_ROWS));
+        MB200_TRY(make_tmap(&tb0, b0, k, n, kp_b, B_ROWS / cfg::NSUB));
     ta1 = ta0;
     tb1 = tb0;
     CUtensorMap ta2 = ta0, ta3 = ta0;
@@ -606,7 +697,7 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     // m-tiles read 7.7 - 8.8 / 6.3 - 6.9 / 6.1 - 6.2 / 6.1 GB).
     const int knob_group = tuning().group_m.load(), knob_raster = tuning().raster.load();
     p.group_m = knob_group > 0 ? knob_group : 8;
-    p.raster = knob_raster == 0 ? 1 : (knob_raster == 2 ? 0 : knob_raster);  // 0 = default, 2 = always forwards
+    p.raster = knob_raster == 2 ? 0 : 1;  // 0 = default (1), 2 = every group forwards, 3 = default order (see direct_store)
     p.hint_a = 1;
     p.hint_b = 0;
     const long long total = (long long)p.m_tiles * p.n_tiles;
@@ -638,6 +729,12 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
         MB200_CUDA(cudaMemsetAsync(c, 0, (size_t)m * (size_t)n * 4, ctx->stream));
         p.accumulate = 1;
     }
+    // Epilogue through TMA stores where the hardware can address C (16-byte base and pitch) and
+    // nothing else adds onto it meanwhile; otherwise plain row stores / atomics.
+    p.tma_store = (!p.accumulate && n % 4 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0 &&
+                   tuning().raster.load() != 3) ? 1 : 0;
+    CUtensorMap tc = ta0;
+    if (p.tma_store) MB200_TRY(make_tmap_c(&tc, c, n, m));
     const long long items = total * splits;
     if (items < units) units = (int)items;
     if (max_ctas > 0 && PAIR == 1 && units > max_ctas) units = max_ctas;
@@ -681,7 +778,7 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
         }
     }
     prof_begin(ctx);
-    MB200_CUDA(cudaLaunchKernelEx(&lc, kern, ta0, ta1, ta2, ta3, tb0, tb1, p));
+    MB200_CUDA(cudaLaunchKernelEx(&lc, kern, ta0, ta1, ta2, ta3, tb0, tb1, tc, p));
     prof_end(ctx);
     count_launch();
     return check_launch("gemm_tc_kernel");
@@ -712,9 +809,19 @@ static bool narrow_pays(const DeviceCtx* ctx, int64_t m, int64_t n, int64_t k) {
     return wide_tiles * 4 <= ctx->sm_count && (k + BLOCK_K - 1) / BLOCK_K < 16;
 }
 
+// 256 x 512 tiles on CTA pairs: their epilogue is not overlapped, so only where a tile's main
+// loop is long (K) and there are tiles enough to keep every pair busy for several rounds.
+static bool wide_pair_pays(const DeviceCtx* ctx, int64_t m, int64_t n, int64_t k) {
+    const int knob = tuning().wide_pair.load();
+    if (knob >= 0) return knob == 1;
+    if (tuning().pair_mode.load() != 0) return false;
+    return k >= 16384 && ((m + 255) / 256) * ((n + 511) / 512) >= 4 * (ctx->sm_count / 2);
+}
+
 int64_t launch_gemm_i8_tc(DeviceCtx* ctx, const int8_t* a, const int8_t* bt, int32_t* c, int64_t m,
                           int64_t n, int64_t k, int64_t kp_a, int64_t kp_b) {
     if (narrow_pays(ctx, m, n, k)) return launch_tc<3, 1, false>(ctx, a, nullptr, bt, nullptr, c, m, n, k, kp_a, kp_b);
+    if (wide_pair_pays(ctx, m, n, k)) return launch_tc<5, 2, false>(ctx, a, nullptr, bt, nullptr, c, m, n, k, kp_a, kp_b);
     const int pair_mode = tuning().pair_mode.load();
     const bool pair = pair_mode == 2 || (pair_mode == 0 && pair_pays(ctx, m, n));
     if (pair) return launch_tc<0, 2, false>(ctx, a, nullptr, bt, nullptr, c, m, n, k, kp_a, kp_b);
@@ -724,6 +831,7 @@ int64_t launch_gemm_i8_tc(DeviceCtx* ctx, const int8_t* a, const int8_t* bt, int
 int64_t launch_gemm_i8_tc_bmn(DeviceCtx* ctx, const int8_t* a, const int8_t* b, int32_t* c, int64_t m,
                               int64_t n, int64_t k, int64_t kp_a, int64_t pitch_b) {
     if (narrow_pays(ctx, m, n, k)) return launch_tc<3, 1, true>(ctx, a, nullptr, b, nullptr, c, m, n, k, kp_a, pitch_b);
+    if (wide_pair_pays(ctx, m, n, k)) return launch_tc<5, 2, true>(ctx, a, nullptr, b, nullptr, c, m, n, k, kp_a, pitch_b);
     const int pair_mode = tuning().pair_mode.load();
     const bool pair = pair_mode == 2 || (pair_mode == 0 && pair_pays(ctx, m, n));
     if (pair) return launch_tc<0, 2, true>(ctx, a, nullptr, b, nullptr, c, m, n, k, kp_a, pitch_b);

@@ -97,6 +97,33 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap,
         : "memory");
 }
 
+// 2-D tiled store, this CTA's shared memory -> global (rows and columns outside the tensor are
+// clipped by the hardware).  Completion is tracked by the issuing thread's bulk async-group.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int32_t x, int32_t y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Until at most N of this thread's bulk groups still have to READ their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Until at most N of this thread's bulk groups are still in flight at all.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+// Makes this thread's earlier shared-memory writes visible to the TMA engine (async proxy).
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 // ------------------------------------------------- programmatic dependent launch
 // No-ops unless the kernel was launched with the programmatic-stream-serialization attribute.
 // launch_dependents: the next kernel in the stream may start (and run up to its own wait).

@@ -32,7 +32,7 @@ GEMM_SHAPES = [
     (64, 4096, 64), (130, 3000, 40), (257, 1100, 300), (16, 16384, 16),
 ]
 PATHS = [3, 2, 1, 0, 4, 5]  # single CTA, CTA pairs, CUDA cores, auto, pairs / single with B transposed first
-PATHS_I8 = PATHS + [10]     # int8 only: the narrow-tile kernel at every shape
+PATHS_I8 = PATHS + [10, 12]  # int8 only: the narrow-tile kernel / the 256 x 512-tile pair kernel at every shape
 
 
 @pytest.fixture(autouse=True)
@@ -245,7 +245,7 @@ def test_wrap_fixture_and_overflowing_i8(gpu):
     m, k, n = 128, (1 << 17) + 256, 16
     a = np.full(m * k, -128, dtype=np.int8)
     b = np.full(k * n, -128, dtype=np.int8)
-    for path in (3, 2, 4, 5, 10):
+    for path in (3, 2, 4, 5, 10, 12):
         gpu.set_gemm_path(path)
         c = np.empty(m * n, dtype=np.int32)
         gpu.matmul_mm_i8_v(a, b, c, m, k, n)
