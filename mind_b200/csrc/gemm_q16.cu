@@ -56,24 +56,10 @@ __device__ __forceinline__ double fma_rm(double a, double b, double c) {
     asm("fma.rm.f64 %0, %1, %2, %3;" : "=d"(d) : "d"(a), "d"(b), "d"(c));
     return d;
 }
-// high word of the binary64 value (v & 0xffff) * 2^-16, built with integer instructions (the
-// int -> double conversion runs at a quarter of the FMA rate on the pipe the FMAs need): the
-// value is 1.m * 2^(e - 16) with e the position of the leading one of the 16-bit field, and its
-// at most 15 mantissa bits all land in the high word.
+// high word of the binary64 value (v & 0xffff) * 2^-16: the exponent drops by 16, zero stays zero
 __device__ __forceinline__ int32_t q16_low_hi_word(int32_t v) {
-    const uint32_t bl = (uint32_t)v & 0xffffu;
-    if (!bl) return 0;
-    const int e = 31 - __clz((int)bl);  // 0 .. 15
-    return (int32_t)(((uint32_t)(1023 - 16 + e) << 20) | ((bl << (20 - e)) & 0xFFFFFu));
-}
-__device__ __forceinline__ int32_t q16_low_hi_word_old(int32_t v) {
     const int32_t bl = v & 0xffff;
     return bl ? __double2hiint(__int2double_rn(bl)) - (16 << 20) : 0;
-}
-// int32 -> binary64 without the conversion instruction: 2^52 + (x + 2^31) is the bit pattern
-// (0x43300000, x ^ 0x80000000); one exact subtraction takes the offset off again.
-__device__ __forceinline__ double i32_to_f64(int32_t x) {
-    return __hiloint2double(0x43300000, x ^ (int32_t)0x80000000) - 4503601774854144.0;
 }
 
 template <int BN, bool FULL>
@@ -87,7 +73,7 @@ struct Q16Smem {
 template <int BN, bool FULL>
 __global__ void __launch_bounds__(QTHREADS, 1)
 gemm_q16_fp64_kernel(const int32_t* __restrict__ a, const int32_t* __restrict__ b, int32_t* __restrict__ c,
-                     int m, int k, int n, int lda, int n_tiles, int k_steps, long long units, int exclusive, int conv_old) {
+                     int m, int k, int n, int lda, int n_tiles, int k_steps, long long units, int exclusive) {
     constexpr int TM = QBM / 16, TN = BN / 16;
     static_assert(TM % 4 == 0 && TN % 4 == 0, "register tile is built from 4-wide groups");
     extern __shared__ __align__(16) unsigned char q16_smem[];
@@ -122,13 +108,8 @@ gemm_q16_fp64_kernel(const int32_t* __restrict__ a, const int32_t* __restrict__ 
                 sm.as[buf][kq][r] = ra[i].x; sm.as[buf][kq + 1][r] = ra[i].y;
                 sm.as[buf][kq + 2][r] = ra[i].z; sm.as[buf][kq + 3][r] = ra[i].w;
             }
-            if (conv_old) {
-                sm.ad[buf][kq][r] = __int2double_rn(ra[i].x); sm.ad[buf][kq + 1][r] = __int2double_rn(ra[i].y);
-                sm.ad[buf][kq + 2][r] = __int2double_rn(ra[i].z); sm.ad[buf][kq + 3][r] = __int2double_rn(ra[i].w);
-            } else {
-                sm.ad[buf][kq][r] = i32_to_f64(ra[i].x); sm.ad[buf][kq + 1][r] = i32_to_f64(ra[i].y);
-                sm.ad[buf][kq + 2][r] = i32_to_f64(ra[i].z); sm.ad[buf][kq + 3][r] = i32_to_f64(ra[i].w);
-            }
+            sm.ad[buf][kq][r] = __int2double_rn(ra[i].x); sm.ad[buf][kq + 1][r] = __int2double_rn(ra[i].y);
+            sm.ad[buf][kq + 2][r] = __int2double_rn(ra[i].z); sm.ad[buf][kq + 3][r] = __int2double_rn(ra[i].w);
         }
 #pragma unroll
         for (int i = 0; i < B_VEC; ++i) {
@@ -137,12 +118,8 @@ gemm_q16_fp64_kernel(const int32_t* __restrict__ a, const int32_t* __restrict__ 
             if (FULL)
                 *reinterpret_cast<int4*>(&sm.bh[buf][kq][cc]) =
                     make_int4(rb[i].x >> 16, rb[i].y >> 16, rb[i].z >> 16, rb[i].w >> 16);
-            if (conv_old)
-                *reinterpret_cast<int4*>(&sm.bw[buf][kq][cc]) = make_int4(
-                    q16_low_hi_word_old(rb[i].x), q16_low_hi_word_old(rb[i].y), q16_low_hi_word_old(rb[i].z), q16_low_hi_word_old(rb[i].w));
-            else
-                *reinterpret_cast<int4*>(&sm.bw[buf][kq][cc]) = make_int4(
-                    q16_low_hi_word(rb[i].x), q16_low_hi_word(rb[i].y), q16_low_hi_word(rb[i].z), q16_low_hi_word(rb[i].w));
+            *reinterpret_cast<int4*>(&sm.bw[buf][kq][cc]) = make_int4(
+                q16_low_hi_word(rb[i].x), q16_low_hi_word(rb[i].y), q16_low_hi_word(rb[i].z), q16_low_hi_word(rb[i].w));
         }
     };
 
@@ -277,7 +254,7 @@ int64_t launch_q16_streamk(DeviceCtx* ctx, const int32_t* a, const int32_t* b, i
         prof_begin(ctx);
         gemm_q16_fp64_kernel<BN, FULL><<<grid, QTHREADS, SMEM, ctx->stream>>>(
             a + k0, b + k0 * n, c, (int)m, (int)kc, (int)n, (int)k, (int)n_tiles, (int)k_steps, (long long)units,
-            (exclusive && (FULL ? k0 == 0 : true)) ? 1 : 0, tuning().raster.load() == 3 ? 1 : 0);
+            (exclusive && (FULL ? k0 == 0 : true)) ? 1 : 0);
         prof_end(ctx);
         count_launch();
         const int64_t rc = check_launch("gemm_q16_fp64_kernel");
