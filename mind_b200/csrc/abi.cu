@@ -234,7 +234,8 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
     // staging: all of B (as dense chunks), all of A (pitch kp), two C tiles
     const size_t sb = b_host ? align_up((size_t)k * n, 1024) : 0;
     const size_t sa = a_host ? align_up((size_t)m * kp, 1024) : 0;
-    const size_t sc = c_host ? align_up((size_t)band * nj * 4, 1024) : 0;
+    // (with column chunks, the bands that arrive after all of B are multiplied full-width: see below)
+    const size_t sc = c_host ? align_up((size_t)band * n * 4, 1024) : 0;
     constexpr int nslot = 2;
     MB200_TRY(arena_reserve(ctx, ctx->staging, sb + sa + nslot * sc + 8192));
     int8_t* b_stage = b_host ? static_cast<int8_t*>(arena_take(ctx->staging, sb)) : nullptr;
@@ -243,12 +244,11 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
     for (int s = 0; s < nslot; ++s)
         if (c_host) c_slot[s] = static_cast<int32_t*>(arena_take(ctx->staging, sc));
 
-    // B as the kernels will see it: chunk j is dense [k][nj] in staging (host B), or a column
-    // window of the caller's device B (pitch n).
-    const int64_t b_pitch = b_host ? nj : n;
-    auto b_chunk = [&](int64_t j) -> const int8_t* {
-        return b_host ? b_stage + (size_t)j * k * nj : b + (size_t)j * nj;
-    };
+    // B as the kernels will see it: a K x N matrix of pitch n (the staged copy of a host B, or the
+    // caller's device B); chunk j is its column window [j * nj, (j + 1) * nj).
+    const int64_t b_pitch = n;
+    const int8_t* b_dev = b_host ? b_stage : b;
+    auto b_chunk = [&](int64_t j) -> const int8_t* { return b_dev + (size_t)j * nj; };
     const bool b_direct = b_inplace_ok;  // with a host B the staged chunks are 1024-byte aligned
     const bool a_dev_direct = a_host || (kp == k && reinterpret_cast<uintptr_t>(a) % 16 == 0);
     const size_t bt_bytes = b_direct ? 0 : (size_t)n * kp, ap_bytes = a_dev_direct ? 0 : (size_t)m * kp;
@@ -264,13 +264,20 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
     // finished uploads grows as a square (t bands and t chunks give t^2 tiles: the download link
     // is fed after about two rounds, instead of after all of A as with "every band, then the
     // next chunk"); operands that are already on the device count as uploaded from the start.
+    // A band that arrives when all of B is already there is multiplied full-width (chunk -1): its
+    // C rows go back as one contiguous copy, which keeps the full link rate beside running kernels
+    // where the strided chunk copies lose a sixth of it (16384^3: the second half of C).
     struct Step { bool is_a; int64_t idx; };
     std::vector<Step> uploads;
     std::vector<std::pair<int64_t, int64_t>> tiles;  // (band, chunk) in the order they become possible
     {
         int64_t ia = a_host ? 0 : bands, jb = b_host ? 0 : chunks;
-        for (int64_t j = 0; j < jb; ++j)
-            for (int64_t i = 0; i < ia; ++i) tiles.emplace_back(i, j);
+        if (jb == chunks && chunks > 1) {
+            for (int64_t i = 0; i < ia; ++i) tiles.emplace_back(i, -1);
+        } else {
+            for (int64_t j = 0; j < jb; ++j)
+                for (int64_t i = 0; i < ia; ++i) tiles.emplace_back(i, j);
+        }
         while (ia < bands || jb < chunks) {
             // B first (no product needs only A), then whichever operand is behind in proportion
             const bool take_b = jb < chunks && (ia == bands || jb == 0 || jb * bands < ia * chunks);
@@ -280,7 +287,11 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
                 ++jb;
             } else {
                 uploads.push_back({true, ia});
-                for (int64_t j = 0; j < jb; ++j) tiles.emplace_back(ia, j);
+                if (jb == chunks && chunks > 1) {
+                    tiles.emplace_back(ia, -1);
+                } else {
+                    for (int64_t j = 0; j < jb; ++j) tiles.emplace_back(ia, j);
+                }
                 ++ia;
             }
         }
@@ -315,8 +326,8 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
             }
             if (chunks == 1)
                 MB200_CUDA(cudaMemcpyAsync(b_stage, b, (size_t)k * n, cudaMemcpyHostToDevice, P.in));
-            else
-                MB200_CUDA(cudaMemcpy2DAsync(b_stage + (size_t)j * k * nj, (size_t)nj, b + (size_t)j * nj, (size_t)n,
+            else  // a column window of the staged K x N copy
+                MB200_CUDA(cudaMemcpy2DAsync(b_stage + (size_t)j * nj, (size_t)n, b + (size_t)j * nj, (size_t)n,
                                              (size_t)nj, (size_t)k, cudaMemcpyHostToDevice, P.in));
             MB200_CUDA(cudaEventRecord(ev, P.in));
         } else {
@@ -368,13 +379,15 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
     std::vector<char> a_waited((size_t)bands, 0), b_waited((size_t)chunks, 0);
     for (const auto& ij : tiles) {
         const int64_t i = ij.first, j = ij.second;
+        const bool full = j < 0;  // every chunk of B is in: one product over all N columns
         const int s = (int)(t % nslot);
         const int64_t r0 = i * band, rows = (m - r0 < band) ? m - r0 : band;
-        if (b_host && b_direct && !b_waited[j]) {
-            upload_recorded(bands + j);
-            MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.ready[bands + j], 0));
-            b_waited[j] = 1;
-        }
+        for (int64_t jj = full ? 0 : j; jj < (full ? chunks : j + 1); ++jj)
+            if (b_host && b_direct && !b_waited[jj]) {
+                upload_recorded(bands + jj);
+                MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.ready[bands + jj], 0));
+                b_waited[jj] = 1;
+            }
         if (a_host && !a_waited[i]) {
             upload_recorded(i);
             MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P.ready[i], 0));
@@ -387,13 +400,14 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
         int32_t* c_tile = c_host ? c_slot[s] : c + (size_t)r0 * n;  // a device C is never cut into chunks
         const int8_t* a_band = a_dev + (size_t)r0 * a_pitch;
         if (b_direct)
-            MB200_TRY(launch_gemm_i8_tc_bmn(ctx, a_band, b_chunk(j), c_tile, rows, nj, k, a_pitch, b_pitch));
+            MB200_TRY(launch_gemm_i8_tc_bmn(ctx, a_band, full ? b_dev : b_chunk(j), c_tile, rows, full ? n : nj, k,
+                                            a_pitch, b_pitch));
         else
             MB200_TRY(launch_gemm_i8_tc(ctx, a_band, bt, c_tile, rows, n, k, a_pitch, kp));
         if (c_host) {
             MB200_CUDA(cudaEventRecord(P.gemm_done[s], ctx->stream));
             MB200_CUDA(cudaStreamWaitEvent(P.out, P.gemm_done[s], 0));
-            int32_t* dst = c + (size_t)r0 * n + (size_t)j * nj;
+            int32_t* dst = c + (size_t)r0 * n + (full ? 0 : (size_t)j * nj);
             if (staged && c_page) {  // chunks == 1: whole rows, contiguous on both sides
                 cudaEvent_t ev = P.out_done[s];
                 cudaStream_t out = P.out;
@@ -401,7 +415,7 @@ int64_t gemm_i8_pipelined(DeviceCtx* ctx, const int8_t* a, bool a_host, const in
                                (size_t)rows * n * 4, out, &out_groups[s], [ev, out] { cudaEventRecord(ev, out); },
                                &stage_status);
             } else {
-                if (chunks == 1)
+                if (chunks == 1 || full)
                     MB200_CUDA(cudaMemcpyAsync(dst, c_slot[s], (size_t)rows * n * 4, cudaMemcpyDeviceToHost, P.out));
                 else
                     MB200_CUDA(cudaMemcpy2DAsync(dst, (size_t)n * 4, c_slot[s], (size_t)nj * 4, (size_t)nj * 4,
