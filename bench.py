@@ -349,6 +349,41 @@ def fp64_peak(blas):
     return _FP64_PEAK["v"]
 
 
+_CALL_LOOP_C = r"""
+#include <stdint.h>
+#include <time.h>
+typedef int64_t (*fn6_t)(int64_t, int64_t, int64_t, int64_t, int64_t, int64_t);
+/* reps back-to-back calls of a six-argument intrinsic, as a compiled caller makes them;
+   returns the host seconds spent issuing them (nothing is waited for) */
+double call_loop(void *fn, int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, int64_t n, int64_t reps) {
+    struct timespec t0, t1;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    for (int64_t i = 0; i < reps; ++i) ((fn6_t)fn)(a, b, c, m, k, n);
+    clock_gettime(CLOCK_MONOTONIC, &t1);
+    return (double)(t1.tv_sec - t0.tv_sec) + 1e-9 * (double)(t1.tv_nsec - t0.tv_nsec);
+}
+"""
+
+
+def compiled_call_loop():
+    """A C loop around the entry point (built with gcc into a temporary directory), so that the
+    per-call figures of the launch-bound cases are a compiled caller's, without the foreign-call
+    overhead of the Python binding.  None when no compiler is at hand."""
+    import ctypes as C
+    import tempfile
+    try:
+        d = tempfile.mkdtemp(prefix="mind_b200_bench_")
+        src, lib = os.path.join(d, "call_loop.c"), os.path.join(d, "libcall_loop.so")
+        with open(src, "w") as f:
+            f.write(_CALL_LOOP_C)
+        subprocess.run(["gcc", "-O2", "-shared", "-fPIC", "-o", lib, src], check=True, capture_output=True)
+        fn = C.CDLL(lib).call_loop
+        fn.argtypes, fn.restype = [C.c_void_p] + [C.c_int64] * 7, C.c_double
+        return fn
+    except Exception:
+        return None
+
+
 def latency_workloads(blas, torch, stream):
     """The launch-latency regime: benchmark configuration 1 (int8 256^3) and the reference's routing
     shape (scores[11922] = catalog[11922 x 384] . query, benches/det_gemv_q16_mt.rs:56-58), device
@@ -411,6 +446,19 @@ def latency_workloads(blas, torch, stream):
     r3 = lambda v: round(v, 3) if isinstance(v, float) else v
     out["gemm_i8_256"] = {"us": r3(us), "us_graph": r3(gus), "host_us": r3(host_us["i8"]),
                           "top_s": r3(2.0 * n ** 3 / us / 1e6)}
+    loop = compiled_call_loop()
+    if loop is not None:  # the same calls from compiled code: one foreign call around the whole loop
+        reps = 2000
+        fn_addr = C.cast(raw, C.c_void_p)
+        loop(fn_addr, a.data_ptr(), b.data_ptr(), c.data_ptr(), n, n, n, 50)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        host_s = loop(fn_addr, a.data_ptr(), b.data_ptr(), c.data_ptr(), n, n, n, reps)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        out["gemm_i8_256"]["us_compiled_caller"] = r3(e0.elapsed_time(e1) * 1e3 / reps)
+        out["gemm_i8_256"]["host_us_compiled_caller"] = r3(host_s * 1e6 / reps)
 
     m, k, q = 11922, 384, 64
     seed = 0xDEADBEEF00000000 ^ ((m << 20) ^ k)
