@@ -57,8 +57,8 @@ WORKLOADS = {
 ELEM_BYTES = {KIND_Q16: 4, KIND_I8: 1, KIND_I16: 2}
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel, one launch at the
 # workload's full size, from the ncu captures summarised under profiles/ (bytes).
-NCU_TRAFFIC = {"gemm_i8": 5596628736 + 1057698048, "gemv_q16": 1073876000 + 3520000,
-               "gemm_i16": 83467520 + 49964800, "gemv_i16": 536918272 + 3374848}
+NCU_TRAFFIC = {"gemm_i8": 5699589376 + 1054785280, "gemv_q16": 1073876000 + 3520000,
+               "gemm_i16": 96119808 + 46307840, "gemv_i16": 536918272 + 3374848}
 
 
 def work_units(w, m):
