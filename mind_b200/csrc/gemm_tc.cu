@@ -61,32 +61,32 @@ template <int MODE, int PAIR>
 struct Cfg;
 template <>
 struct Cfg<0, 1> {
-    static constexpr int BLOCK_N = 256, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 2, STAGES = 4, TMEM_COLS = 512, NSUB = 1;
+    static constexpr int BLOCK_N = 256, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 2, STAGES = 4, TMEM_COLS = 512, NSUB = 1, EPI_PATCHES = 2;
 };
 template <>
 struct Cfg<1, 1> {  // int16: two accumulators of 2 x BLOCK_N columns (A high / A low times [B high | B low])
-    static constexpr int BLOCK_N = 128, NA = 2, NB = 2, NACC = 4, ACC_STAGES = 1, STAGES = 3, TMEM_COLS = 512, NSUB = 1;
+    static constexpr int BLOCK_N = 128, NA = 2, NB = 2, NACC = 4, ACC_STAGES = 1, STAGES = 3, TMEM_COLS = 512, NSUB = 1, EPI_PATCHES = 1;
 };
 template <>
 struct Cfg<0, 2> {
-    static constexpr int BLOCK_N = 256, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 2, STAGES = 6, TMEM_COLS = 512, NSUB = 1;
+    static constexpr int BLOCK_N = 256, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 2, STAGES = 6, TMEM_COLS = 512, NSUB = 1, EPI_PATCHES = 2;
 };
 
 template <>
 struct Cfg<2, 1> {  // linear part of the Q16.16 product: a (4 limbs) x bh (2 limbs), 4 accumulators
-    static constexpr int BLOCK_N = 128, NA = 4, NB = 2, NACC = 4, ACC_STAGES = 1, STAGES = 2, TMEM_COLS = 512, NSUB = 1;
+    static constexpr int BLOCK_N = 128, NA = 4, NB = 2, NACC = 4, ACC_STAGES = 1, STAGES = 2, TMEM_COLS = 512, NSUB = 1, EPI_PATCHES = 1;
 };
 template <>
 struct Cfg<4, 1> {  // the same with 64-column tiles: twice the CTAs for mid-sized products, two accumulator stages
-    static constexpr int BLOCK_N = 64, NA = 4, NB = 2, NACC = 4, ACC_STAGES = 2, STAGES = 2, TMEM_COLS = 512, NSUB = 1;
+    static constexpr int BLOCK_N = 64, NA = 4, NB = 2, NACC = 4, ACC_STAGES = 2, STAGES = 2, TMEM_COLS = 512, NSUB = 1, EPI_PATCHES = 2;
 };
 template <>
 struct Cfg<3, 1> {  // int8, narrow tiles
-    static constexpr int BLOCK_N = 64, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 4, STAGES = 3, TMEM_COLS = 256, NSUB = 1;
+    static constexpr int BLOCK_N = 64, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 4, STAGES = 3, TMEM_COLS = 256, NSUB = 1, EPI_PATCHES = 2;
 };
 template <>
 struct Cfg<5, 2> {  // int8, 256 x 512 tiles on a CTA pair: two MMAs of N = 256 share every A slab
-    static constexpr int BLOCK_N = 512, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 1, STAGES = 4, TMEM_COLS = 512, NSUB = 2;
+    static constexpr int BLOCK_N = 512, NA = 1, NB = 1, NACC = 1, ACC_STAGES = 1, STAGES = 3, TMEM_COLS = 512, NSUB = 2, EPI_PATCHES = 2;
 };
 
 // Epilogue warps of a mode: four, or eight where a tile has four accumulators to drain.
@@ -422,8 +422,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
         // ---------------------------------------------------------------- epilogue
         const int q = warp & 3;  // TMEM lane quadrant this warp may read
         const int c_first = ((warp - 2) / 4) * EPI_COLS;  // its share of the tile's columns
-        uint32_t* const patch = reinterpret_cast<uint32_t*>(smem_raw + (patches0 - raw)) + (warp - 2) * EPI_PATCH_WORDS;
-        const uint32_t patch_addr = patches0 + (uint32_t)(warp - 2) * (EPI_PATCH_WORDS * 4);
+        // each epilogue warp owns EPI_PATCHES patches of 4 KiB (two where shared memory allows: a
+        // block is written while the tensor store of the one before still reads its patch)
+        constexpr int EPI_PATCHES = cfg::EPI_PATCHES;
+        uint32_t* const patch = reinterpret_cast<uint32_t*>(smem_raw + (patches0 - raw)) + (warp - 2) * EPI_PATCHES * EPI_PATCH_WORDS;
+        const uint32_t patch_first = patches0 + (uint32_t)(warp - 2) * (EPI_PATCHES * EPI_PATCH_WORDS * 4);
+        uint32_t blocks_stored = 0;
         uint32_t tcount = 0;
         for (int item = tile_first; item < total_tiles; item += tile_step, ++tcount) {
             int tm, tn;
@@ -481,8 +485,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                     // groups), and ONE bulk tensor store writes it out: nine instructions per block
                     // instead of ninety-six, and rows / columns past the matrix edge are clipped by
                     // the hardware.  The patch is reused once the previous store has read it.
-                    if (lane == 0) bulk_wait_group_read<0>();
+                    if (lane == 0) bulk_wait_group_read<EPI_PATCHES - 1>();
                     __syncwarp();
+                    const uint32_t patch_addr = patch_first + (blocks_stored++ % EPI_PATCHES) * (EPI_PATCH_WORDS * 4);
                     const uint32_t prow = patch_addr + (uint32_t)lane * 128u;
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
@@ -654,7 +659,7 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
     constexpr int B_ROWS = cfg::BLOCK_N / PAIR;
     constexpr int BOX_N = B_ROWS < 128 ? B_ROWS : 128;  // width of an MN-major box = its swizzle width
     constexpr int STAGE_BYTES = cfg::NA * A_TILE_BYTES + cfg::NB * B_ROWS * BLOCK_K;
-    constexpr int SMEM = cfg::STAGES * STAGE_BYTES + 1024 + 1024 + epi_warps<MODE, PAIR>() * EPI_PATCH_WORDS * 4;
+    constexpr int SMEM = cfg::STAGES * STAGE_BYTES + 1024 + 1024 + epi_warps<MODE, PAIR>() * cfg::EPI_PATCHES * EPI_PATCH_WORDS * 4;
     static_assert(SMEM <= 232448, "shared memory budget");
     if (m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff)
         return fail(MIND_B200_ERR_TOO_LARGE, "GEMM dimension above 2^31-1");
