@@ -243,6 +243,7 @@ struct I8Job {
     int64_t m, k, n, band;
     int g;
     bool exchange;                 // K-slices of B passed between the devices (needs peer access)
+    bool a_page, b_page, c_page;   // pageable host operands: moved by the staging threads (staging.cu)
     int dev[MAX_MULTI];            // device ordinals, by worker
     int8_t* b_dev[MAX_MULTI];      // every device's own full copy of B
     cudaEvent_t b_ready[MAX_MULTI];  // worker i's slice has reached every device
@@ -294,6 +295,13 @@ int64_t i8_worker(I8Job& J, int w) {
 
     // ---- phase 1: uploads, all queued on this device's in-stream: this device's share of B
     // (passed on to every peer), then the sub-bands of A
+    // Host-side completion of copies that the staging threads make (pageable operands): the CUDA
+    // event of a group is recorded by the thread that queues its last chunk, and this thread
+    // waits on the host until that has happened before it makes a stream wait for the event.
+    StageStatus stage_status;
+    StageGroup b_group, out_groups[nslot];
+    std::vector<StageGroup> up_groups(J.a_page ? (size_t)nsub : 0);
+    const int device = J.dev[w];
     auto uploads = [&]() -> int64_t {
         MB200_CUDA(cudaEventRecord(P->start, ctx->stream));
         MB200_CUDA(cudaStreamWaitEvent(P->in, P->start, 0));
@@ -302,12 +310,23 @@ int64_t i8_worker(I8Job& J, int w) {
             const int64_t ks = (k + J.g - 1) / J.g, k0 = (int64_t)w * ks, k1 = k0 + ks < k ? k0 + ks : k;
             if (k1 > k0) {
                 const size_t off = (size_t)k0 * n, bytes = (size_t)(k1 - k0) * n;
-                MB200_CUDA(cudaMemcpyAsync(b_stage + off, J.b + off, bytes, cudaMemcpyHostToDevice, P->in));
+                if (J.b_page) {  // the pushes below must follow the whole slice in stream order
+                    stage_upload(device, reinterpret_cast<char*>(b_stage) + off, (size_t)n,
+                                 reinterpret_cast<const char*>(J.b) + off, (size_t)n, (size_t)n, (size_t)(k1 - k0), P->in,
+                                 &b_group, nullptr, &stage_status);
+                    b_group.wait();
+                } else {
+                    MB200_CUDA(cudaMemcpyAsync(b_stage + off, J.b + off, bytes, cudaMemcpyHostToDevice, P->in));
+                }
                 for (int h = 1; h < J.g; ++h) {  // start with the next device round: spreads the NVLink load
                     const int peer = (w + h) % J.g;
                     MB200_CUDA(cudaMemcpyPeerAsync(J.b_dev[peer] + off, J.dev[peer], b_stage + off, J.dev[w], bytes, P->in));
                 }
             }
+        } else if (J.b_page) {
+            stage_upload(device, reinterpret_cast<char*>(b_stage), (size_t)n, reinterpret_cast<const char*>(J.b), (size_t)n,
+                         (size_t)n, (size_t)k, P->in, &b_group, nullptr, &stage_status);
+            b_group.wait();
         } else {
             MB200_CUDA(cudaMemcpyAsync(b_stage, J.b, (size_t)k * n, cudaMemcpyHostToDevice, P->in));
         }
@@ -316,6 +335,14 @@ int64_t i8_worker(I8Job& J, int w) {
             const int64_t s0 = i * sub, srows = (rows - s0 < sub) ? rows - s0 : sub;
             int8_t* dst = a_stage + (size_t)s0 * kp;
             const int8_t* src = J.a + (size_t)(r0 + s0) * k;
+            if (J.a_page) {
+                cudaEvent_t ev = P->ready[i];
+                cudaStream_t in = P->in;
+                stage_upload(device, reinterpret_cast<char*>(dst), (size_t)kp, reinterpret_cast<const char*>(src), (size_t)k,
+                             (size_t)k, (size_t)srows, in, &up_groups[(size_t)i], [ev, in] { cudaEventRecord(ev, in); },
+                             &stage_status);
+                continue;
+            }
             if (kp == k)
                 MB200_CUDA(cudaMemcpyAsync(dst, src, (size_t)srows * k, cudaMemcpyHostToDevice, P->in));
             else  // pad to a 16-byte pitch on the way: the pad bytes are never read
@@ -340,8 +367,12 @@ int64_t i8_worker(I8Job& J, int w) {
         for (int64_t i = 0; i < nsub; ++i) {
             const int s = (int)(i % nslot);
             const int64_t s0 = i * sub, srows = (rows - s0 < sub) ? rows - s0 : sub;
+            if (J.a_page) up_groups[(size_t)i].wait();  // the event below has been recorded
             MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P->ready[i], 0));
-            if (i >= nslot) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P->out_done[s], 0));  // slot free
+            if (i >= nslot) {  // slot free
+                if (J.c_page) out_groups[s].wait();
+                MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P->out_done[s], 0));
+            }
             const int8_t* a_sub = a_stage + (size_t)s0 * kp;
             if (b_direct)
                 MB200_TRY(launch_gemm_i8_tc_bmn(ctx, a_sub, b_stage, c_slot[s], srows, n, k, kp, n));
@@ -349,12 +380,25 @@ int64_t i8_worker(I8Job& J, int w) {
                 MB200_TRY(launch_gemm_i8_tc(ctx, a_sub, bt, c_slot[s], srows, n, k, kp, kp));
             MB200_CUDA(cudaEventRecord(P->gemm_done[s], ctx->stream));
             MB200_CUDA(cudaStreamWaitEvent(P->out, P->gemm_done[s], 0));
-            MB200_CUDA(cudaMemcpyAsync(J.c + (size_t)(r0 + s0) * n, c_slot[s], (size_t)srows * n * 4,
-                                       cudaMemcpyDeviceToHost, P->out));
-            MB200_CUDA(cudaEventRecord(P->out_done[s], P->out));
+            if (J.c_page) {
+                cudaEvent_t ev = P->out_done[s];
+                cudaStream_t out = P->out;
+                stage_download(device, reinterpret_cast<char*>(J.c + (size_t)(r0 + s0) * n),
+                               reinterpret_cast<const char*>(c_slot[s]), (size_t)srows * n * 4, out, &out_groups[s],
+                               [ev, out] { cudaEventRecord(ev, out); }, &stage_status);
+            } else {
+                MB200_CUDA(cudaMemcpyAsync(J.c + (size_t)(r0 + s0) * n, c_slot[s], (size_t)srows * n * 4,
+                                           cudaMemcpyDeviceToHost, P->out));
+                MB200_CUDA(cudaEventRecord(P->out_done[s], P->out));
+            }
         }
-        for (int s = 0; s < nslot && s < nsub; ++s) MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P->out_done[s], 0));
+        for (int s = 0; s < nslot && s < nsub; ++s) {
+            if (J.c_page) out_groups[s].wait();
+            MB200_CUDA(cudaStreamWaitEvent(ctx->stream, P->out_done[s], 0));
+        }
+        if (J.c_page) stager_drain();  // the last chunks are in the caller's buffer
         MB200_CUDA(cudaStreamSynchronize(ctx->stream));
+        if (stage_status.failed.load()) return fail(MIND_B200_ERR_CUDA, "a staged copy of a pageable host operand failed");
         return check_err_word(ctx);
     };
     if (!J.failed.load()) {
@@ -363,6 +407,7 @@ int64_t i8_worker(I8Job& J, int w) {
     }
     // Whatever happened, nothing of this call may still be in flight on this device when the
     // arenas are handed to the next call, and no peer may still be copying from or into them.
+    if (J.a_page || J.b_page || J.c_page) stager_drain();
     if (P) {
         cudaStreamSynchronize(P->in);
         cudaStreamSynchronize(P->out);
@@ -428,6 +473,13 @@ int64_t multi_gemm_i8(const int8_t* a, const int8_t* b, int32_t* c, int64_t m, i
     J.g = g;
     J.band = (m + g - 1) / g;
     J.exchange = P.peer_ok;
+    // pageable operands go through the staging threads when a row fits one of their slots
+    const bool row_fits = align_up((size_t)k, 16) <= stager_slot_bytes() && (size_t)n * 4 <= stager_slot_bytes();
+    const bool may_stage = row_fits && (host_pointer_is_pageable(a) || host_pointer_is_pageable(b) || host_pointer_is_pageable(c)) &&
+                           stager_start();
+    J.a_page = may_stage && host_pointer_is_pageable(a);
+    J.b_page = may_stage && host_pointer_is_pageable(b);
+    J.c_page = may_stage && host_pointer_is_pageable(c);
     for (int i = 0; i < g; ++i) {
         J.dev[i] = P.devices[i];
         J.b_dev[i] = nullptr;
