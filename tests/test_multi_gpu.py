@@ -135,3 +135,22 @@ def test_device_operands_stay_on_their_device_and_foreign_ones_are_refused(multi
     assert e.value.code == mind_b200.ERR_INVALID and "lives on device 1" in str(e.value)
     with pytest.raises(mind_b200.MindB200Error):
         gpu.set_devices(gpu.device_count() + 1)
+
+
+def test_devices_come_from_the_environment(multi):
+    """MINDB200_DEVICES names the GPUs a host-operand call may use: a count or a list of ordinals
+    (read once, when the library first needs it)."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = ("import sys; sys.path.insert(0, %r); import numpy as np; import oracle as O; from mind_b200 import blas; "
+              "print('devices', blas.devices()); m, k, n = 2048, 512, 1024; g = O.Lcg(9); a, b = g.i8(m * k), g.i8(k * n); "
+              "c = np.empty(m * n, dtype=np.int32); blas.matmul_mm_i8_v(a, b, c, m, k, n); "
+              "assert np.array_equal(c[:4 * n], O.gemm_i8(a[:4 * k], b, 4, k, n)); "
+              "assert np.array_equal(c[-4 * n:], O.gemm_i8(a[-4 * k:], b, 4, k, n)); print('ok')") % root
+    for value, want in (("2", 2), ("1,0", 2), ("", 1), ("99", multi.device_count())):
+        env = dict(os.environ, MINDB200_DEVICES=value)
+        r = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, env=env, timeout=600)
+        assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
+        assert f"devices {want}" in r.stdout, (value, r.stdout)
