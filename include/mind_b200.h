@@ -193,7 +193,8 @@ int64_t mind_b200_shutdown(void);
 int64_t mind_b200_set_gemm_path(int64_t path);
 /* Measurement knob of the int8 GEMM's tile order: m-tiles walked together before moving on in
  * N (0 = default, 8) and the order variant (0 = default: odd groups walk N backwards; 1 = the
- * same; 2 = every group walks N forwards).  Every setting gives identical bytes. */
+ * same; 2 = every group walks N forwards; 3 = the default order with the epilogue storing rows
+ * itself instead of handing its blocks to TMA stores).  Every setting gives identical bytes. */
 int64_t mind_b200_set_tile_order(int64_t group_m, int64_t raster);
 /* Self-test of the bounded waits inside the GEMM kernels: launches a one-warp kernel that waits
  * (with the given limit, 1..1000 ms) on a barrier nothing will ever complete.  The expected

@@ -845,7 +845,7 @@ int64_t mind_b200_set_gemm_path(int64_t path) {
 int64_t mind_b200_set_tile_order(int64_t group_m, int64_t raster) {
     clear_error();
     if (group_m < 0 || group_m > 64 || raster < 0 || raster > 3) return fail(MIND_B200_ERR_INVALID, "bad tile order");
-    // (raster 3 = default order, with the 256 x 512 kernel's epilogue in its transposing form: a measurement knob)
+    // (raster 3 = default order, with the epilogue in its row-store form instead of TMA stores: a measurement knob)
     tuning().group_m = (int)group_m;
     tuning().raster = (int)raster;
     return 0;
