@@ -280,7 +280,7 @@ def run_reference(args, w):
 
 
 # ------------------------------------------------------------------- GPU arm
-def quick_workload(name, blas, torch, stream, dist=None, world=1, rank=0, steps=30):
+def quick_workload(name, blas, torch, stream, dist=None, world=1, rank=0, steps=30, l2="rotate"):
     """Device-resident timing of one of the other benchmark configurations, row-sharded over
     the ranks like the headline workload (each rank its band, max over ranks).  Compact: value,
     unit, kernel_only (the compute kernels without operand re-layout) and its roofline fraction."""
@@ -296,10 +296,17 @@ def quick_workload(name, blas, torch, stream, dist=None, world=1, rank=0, steps=
     blas.lcg_fill(a, rows * k, kind, w["seed"], r0 * k, w["shift"])
     blas.lcg_fill(b, k * n, kind, w["seed"], m * k, w["shift"])
     fn = getattr(blas, w["fn"])
-    call = (lambda: fn(a, b, c, rows, k)) if n == 1 else (lambda: fn(a, b, c, rows, k, n))
-    flush = None
-    if (rows * k + k * n) * ELEM_BYTES[kind] <= 2 * L2_BYTES:
-        flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device="cuda")
+    sets, flush, _ = operand_sets(torch, a, b, c, l2)
+    turn = [0]
+
+    def call():
+        pa, pb, pc = sets[turn[0] % len(sets)]
+        turn[0] += 1
+        if n == 1:
+            fn(pa, pb, pc, rows, k)
+        else:
+            fn(pa, pb, pc, rows, k, n)
+
     for _ in range(3):
         call()
     torch.cuda.synchronize()
@@ -335,6 +342,22 @@ def quick_workload(name, blas, torch, stream, dist=None, world=1, rank=0, steps=
     if peak and out["kernel_only"]:
         out["frac"] = round(out["kernel_only"] / peak, 3)
     return out
+
+
+def operand_sets(torch, a, b, c, mode):
+    """How a workload whose operands fit in L2 is kept from finding them there on the next step.
+    "rotate": identical copies of (A, B, C), used in turn, larger than L2 together with a margin
+    -- the step's inputs are cold, as with inputs larger than L2.  "flush": one set, and a buffer
+    twice the size of L2 is written between steps (which also leaves L2 full of dirty lines that
+    the step's first kernel then has to write back).  Returns (sets, flush buffer or None, note)."""
+    one = a.numel() * a.element_size() + b.numel() * b.element_size() + c.numel() * c.element_size()
+    if (a.numel() * a.element_size() + b.numel() * b.element_size()) > 2 * L2_BYTES:
+        return [(a, b, c)], None, "operands larger than L2"
+    count = max(3, -(-3 * L2_BYTES // one))
+    if mode == "flush" or count > 64:  # (a tiny workload would need hundreds of sets: flush instead)
+        return [(a, b, c)], torch.empty(2 * L2_BYTES, dtype=torch.uint8, device="cuda"), "L2 flushed between steps"
+    sets = [(a, b, c)] + [(a.clone(), b.clone(), torch.empty_like(c)) for _ in range(count - 1)]
+    return sets, None, f"{count} operand sets of {one >> 20} MiB used in turn (larger than L2 together)"
 
 
 _FP64_PEAK = {}
@@ -656,9 +679,13 @@ def run_mine(args, w):
         c_sha = output_hash(torch, dist, c, m, n, world, rank, r0, rows)
 
     in_bytes = (rows * k + k * n) * es
-    flush = None
-    if in_bytes <= 2 * L2_BYTES:  # operands could sit in L2 between steps: evict them
-        flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device="cuda")
+    # operands that could sit in L2 between steps: several sets used in turn (or a flush)
+    sets, flush, l2_note = operand_sets(torch, a, b, c, args.l2)
+    turn = [0]
+
+    def next_set():
+        turn[0] += 1
+        return sets[turn[0] % len(sets)]
 
     def barrier():
         if world > 1:
@@ -672,7 +699,7 @@ def run_mine(args, w):
     for _ in range(args.warmup):
         if flush is not None:
             flush.fill_(1)
-        step(a, b, c)
+        step(*next_set())
     barrier()
     sampler.mark_begin()
     launches0 = blas.kernel_launches()
@@ -682,7 +709,7 @@ def run_mine(args, w):
         if flush is not None:
             flush.fill_(1)
         e0.record(stream)
-        step(a, b, c)
+        step(*next_set())
         e1.record(stream)
     barrier()
     sampler.mark_end()
@@ -712,7 +739,7 @@ def run_mine(args, w):
         y0, y1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         y0.record(stream)
         for _ in range(reps):
-            step(a, b, c)
+            step(*next_set())
         y1.record(stream)
         barrier()
         s2.mark_end()
@@ -729,7 +756,7 @@ def run_mine(args, w):
                          "sm_mhz_p90": ck.get("sm_mhz_p90"), "clock_samples": ck.get("samples"),
                          "power_w_max": ck.get("power_w_max"), "reasons": ck.get("reasons"),
                          "mcycles_per_step": round(per * 1e-3 * ck["sm_mhz"], 3) if ck.get("sm_mhz") else None,
-                         "l2": "L2 not flushed between steps" if flush is not None else "operands larger than L2"}
+                         "l2": l2_note}
 
     # End to end: the same product through ONE call with HOST (pinned) operands, so every step
     # copies A and B to the device(s) and C back inside the timed region.  At N > 1 rank 0 makes
@@ -738,6 +765,7 @@ def run_mine(args, w):
     e2e = e2e_pageable = None
     e2e_steps = max(1, min(args.steps, 3))
     del flush
+    del sets[1:]
     if world > 1:
         dist.barrier(group=host_group)
     if rank == 0:
@@ -832,7 +860,7 @@ def run_mine(args, w):
     if args.workload == "gemm_i8" and not args.size and not args.no_others:
         del a, b, c
         torch.cuda.empty_cache()
-        others = {name: quick_workload(name, blas, torch, stream, dist, world, rank)
+        others = {name: quick_workload(name, blas, torch, stream, dist, world, rank, l2=args.l2)
                   for name in ("gemm_q16", "gemv_q16", "gemm_i16")}
         if world == 1:
             others.update(latency_workloads(blas, torch, stream))
@@ -875,7 +903,7 @@ def run_mine(args, w):
                 "dtype": w["dtype"], "data": "synthetic"}
         line["config"] = {"workload": f"{args.workload} {m}x{k}x{n}" if n > 1 else f"{args.workload} {m}x{k}",
                           "sharding": f"{world} row band(s) of {-(-m // world)} rows, B replicated, no collective",
-                          "l2": "operands larger than L2" if in_bytes > 2 * L2_BYTES else "L2 flushed between steps",
+                          "l2": l2_note,
                           "gemm_path": args.path, "seed": hex(w["seed"]), "gate": gate}
         line["roofline"] = roofline
         line["cpu_baseline"] = cpu_baseline(w) if world == 1 and not args.no_cpu else None
@@ -914,6 +942,8 @@ def main():
     ap.add_argument("--sustain", type=float, default=3.0, help="seconds of back-to-back calls after the timed region (0: skip)")
     ap.add_argument("--group-m", type=int, default=0, help="int8 tile order: m-tiles per group (0: default)")
     ap.add_argument("--raster", type=int, default=0, help="int8 tile order variant (0: default)")
+    ap.add_argument("--l2", default="rotate", choices=["rotate", "flush"],
+                    help="operands that fit in L2: use several operand sets in turn (default) or flush L2 between steps")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-check", action="store_true", help="skip the whole-output gate before timing")
     ap.add_argument("--no-others", action="store_true", help="skip the other configurations' ride-along numbers")
