@@ -187,7 +187,10 @@ int64_t mind_b200_shutdown(void);
  * (default: side by side up to 2^31 products, where the tensor-core half is latency-bound);
  * 10 / 11 = int8 GEMM: the narrow-tile kernel (128 x 64 tiles, for products with few tiles)
  * always / never (default: when the wide tiles would leave most SMs idle); 12 / 13 = int8 GEMM:
- * the kernel with 256 x 512 tiles on CTA pairs always / never (default: for long K and many tiles).
+ * the kernel with 256 x 512 tiles on CTA pairs always / never (default: for long K and many tiles);
+ * 14 = Q16.16 GEMM only: the hybrid in its earlier form, floor(a * (b & 0xffff) / 65536) on the
+ * FP64 pipe beside seven limb products (default: floor((a & 0xffff) * (b & 0xffff) / 65536) on the
+ * FP32 pipe beside eleven).
  * Every path gives identical bytes.  The setting is process-wide and meant for tests and
  * measurements; a call that is already running keeps the kernels it chose. */
 int64_t mind_b200_set_gemm_path(int64_t path);
@@ -212,6 +215,13 @@ int64_t mind_b200_profile_read(int64_t* launches_out, double* total_ms_out);
  * such FMA per product.  sm_mhz_out (may be NULL) receives the SM clock the loop ran at (cycle
  * counter over wall clock inside the kernel).  Synchronous; a few milliseconds. */
 int64_t mind_b200_fp64_fma_peak(double* fma_per_s_out, double* sm_mhz_out);
+/* The same for the FP32 pipe in its packed round-down form (fma.rm.f32x2, two FMAs per
+ * instruction, both counted): the ceiling of the Q16.16 GEMM's floor kernel in its default form,
+ * which spends one FP32 FMA per product on floor((a & 0xffff) * (b & 0xffff) / 65536). */
+int64_t mind_b200_fp32_fma_peak(double* fma_per_s_out, double* sm_mhz_out);
+/* Q16.16 GEMM hybrid, measurement knob: SMs given to the tensor-core half while the floor kernel
+ * runs beside it on the others; 0 = the halves in sequence, -1 = chosen by size (the default). */
+int64_t mind_b200_set_q16_split(int64_t side_sms);
 
 /* ---- seeded inputs and large-shape checking on the device ------------------------------------- */
 /* Fills dst (device or host pointer) with elements [offset, offset + n) of the reference's

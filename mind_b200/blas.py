@@ -182,6 +182,26 @@ def fp64_fma_peak(with_clock: bool = False):
     return (float(v.value), float(mhz.value)) if with_clock else float(v.value)
 
 
+def fp32_fma_peak(with_clock: bool = False):
+    """Measured FP32 FMA rate of the current device in the packed round-down form the Q16.16 floor
+    kernel uses, FMA per second (and, with_clock, the SM clock in MHz the loop ran at)."""
+    import ctypes as C
+    f = lib().mind_b200_fp32_fma_peak
+    f.argtypes, f.restype = [C.POINTER(C.c_double), C.POINTER(C.c_double)], C.c_int64
+    v, mhz = C.c_double(0.0), C.c_double(0.0)
+    check(f(C.byref(v), C.byref(mhz)))
+    return (float(v.value), float(mhz.value)) if with_clock else float(v.value)
+
+
+def set_q16_split(side_sms: int) -> None:
+    """Q16.16 hybrid, measurement knob: SMs of the tensor-core half beside the floor kernel
+    (0 = in sequence, -1 = by size)."""
+    import ctypes as C
+    f = lib().mind_b200_set_q16_split
+    f.argtypes, f.restype = [C.c_int64], C.c_int64
+    check(f(int(side_sms)))
+
+
 def profile_read() -> tuple[int, float]:
     """(kernels timed since the last read, their summed duration in ms)."""
     import ctypes as C

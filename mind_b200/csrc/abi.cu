@@ -575,6 +575,7 @@ int64_t gemm_q16_local(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, in
     DevLock lock(ctx->mu);
     const int g_gemm_path = tuning().gemm_path.load(), g_q16_mode = tuning().q16_mode.load(),
               g_q16_side_sms = tuning().q16_side_sms.load();
+    const bool floor_f32 = tuning().q16_floor.load() == 0;
     Call call(ctx);
     const int ia = call.add((void*)a, (size_t)m * k * 4, false);
     const int ib = call.add((void*)b, (size_t)k * n * 4, false);
@@ -592,18 +593,21 @@ int64_t gemm_q16_local(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, in
         const bool may_hybrid = g_gemm_path != 1 && k % 4 == 0 && n % 4 == 0 &&
                                 (g_q16_mode == 7 || (g_q16_mode == 0 && big));
         MB200_TRY(arena_reserve(ctx, ctx->scratch, (b_transposed ? align_up((size_t)k * n * 4, 1024) : 0) +
-                                                       (may_hybrid ? 4 * a_plane + 2 * b_plane : 0) + 16384));
+                                                       (may_hybrid ? 4 * a_plane + 4 * b_plane : 0) + 16384));
         if (b_transposed) {
             int32_t* bkn = static_cast<int32_t*>(arena_take(ctx->scratch, (size_t)k * n * 4));
             MB200_TRY(launch_transpose_i32(ctx, db, bkn, n, k));
             db = bkn;
         }
         // Path 1 keeps the all-integer kernel (the cross-check).  Otherwise, when the operands
-        // allow 16-byte loads: large products split into a linear part a * (b >> 16) on the
-        // tensor cores (byte planes of a and of b >> 16, seven limb products) plus the floor part
-        // floor(a * (b & 0xffff) / 65536) on the FP64 pipe, added onto it; smaller ones run the
-        // single FP64-pipe kernel (both halves on the CUDA cores), where three extra launches
-        // would cost more than they save.
+        // allow 16-byte loads: large products split into a linear part on the tensor cores (byte
+        // planes, limb products mod 2^32) plus the per-product floor on the CUDA cores, added onto
+        // it.  In the default form the linear part is a * (b >> 16) + (a >> 16) * (b & 0xffff)
+        // (eleven limb products) and what is left, floor((a & 0xffff) * (b & 0xffff) / 65536), fits
+        // the FP32 pipe; in the earlier form (q16_floor = 1) the linear part is a * (b >> 16) alone
+        // (seven) and floor(a * (b & 0xffff) / 65536) runs on the FP64 pipe at half the rate.
+        // Smaller products run the single FP64-pipe kernel (everything on the CUDA cores), where
+        // three extra launches would cost more than they save.
         const int32_t* da = call.dev<int32_t>(ia);
         int32_t* dc = call.dev<int32_t>(ic);
         const bool fp64_ok = g_gemm_path != 1 && gemm_q16_fp64_usable(da, db, k, n);
@@ -612,32 +616,38 @@ int64_t gemm_q16_local(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, in
             uint8_t* ap[4];
             uint8_t* bp[4] = {nullptr, nullptr, nullptr, nullptr};
             for (int i = 0; i < 4; ++i) ap[i] = static_cast<uint8_t*>(arena_take(ctx->scratch, a_plane));
-            for (int i = 0; i < 2; ++i) bp[i] = static_cast<uint8_t*>(arena_take(ctx->scratch, b_plane));
+            for (int i = 0; i < (floor_f32 ? 4 : 2); ++i) bp[i] = static_cast<uint8_t*>(arena_take(ctx->scratch, b_plane));
+            const int b_what = floor_f32 ? 2 : 1;
+            auto launch_floor = [&](int max_blocks) {
+                return floor_f32 ? launch_gemm_q16_floor_f32(ctx, da, db, dc, m, k, n, max_blocks)
+                                 : launch_gemm_q16_floor_add(ctx, da, db, dc, m, k, n, max_blocks);
+            };
             // Products up to 2^31 (1024^3 is 2^30): the tensor-core half is latency-bound (a few
-            // k-blocks per tile, fewer tiles than SMs) and the FP64 half takes five times as long, so
-            // the two run side by side: c is zeroed, the byte split and the tensor-core kernel go to
-            // a second stream on 16 SMs, the FP64 kernel keeps the rest, and both add onto c with
-            // red.global.add (sums mod 2^32 commute).  Measured at 1024^3: 113 us against 121 us in
-            // sequence (8 / 12 / 24 SMs: 170 / 133 / 127 us); from 1536^3 up the sequence is as fast
-            // or faster (the tensor-core half is ~6 % of the work there and would idle its SMs).  In
-            // sequence the tensor-core half runs 64-column tiles when it has fewer 128 x 128 tiles
-            // than SMs (135 -> 121 us at 1024^3, 787 -> 756 us at 2048^3).
+            // k-blocks per tile, fewer tiles than SMs), so the two halves run side by side: c is
+            // zeroed, the byte split and the tensor-core kernel go to a second stream on a few SMs,
+            // the floor kernel keeps the rest, and both add onto c with red.global.add (sums mod
+            // 2^32 commute).  Measured at 1024^3 with the FP32 floor kernel: 86 us with 32 SMs for
+            // the tensor-core half (8 / 16 / 24 / 48 SMs: 203 / 116 / 93 / 95 us) against 103 us in
+            // sequence; from 2048^3 up the sequence is as fast or faster (525 / 530 us at 2048^3).
+            // With the FP64 floor kernel, which takes twice as long: 16 SMs, 113 us against 121 us.
+            // In sequence the tensor-core half runs 64-column tiles when it has fewer 128 x 128 tiles
+            // than SMs.
             const double work = (double)m * (double)n * (double)k;
             // (not with a short K: there the outputs dominate, and side by side every output is an atomic)
-            const int side_sms = g_q16_side_sms >= 0 ? g_q16_side_sms : (work <= 2147483648.0 && k >= 512 ? 16 : 0);
+            const int side_sms = g_q16_side_sms >= 0 ? g_q16_side_sms : (work <= 2147483648.0 && k >= 512 ? (floor_f32 ? 32 : 16) : 0);
             if (side_sms > 0 && side_sms < ctx->sm_count) {
                 MB200_CUDA(cudaMemsetAsync(dc, 0, (size_t)m * n * 4, ctx->stream));
                 MB200_CUDA(cudaEventRecord(ctx->fork_ev, ctx->stream));
                 MB200_CUDA(cudaStreamWaitEvent(ctx->side, ctx->fork_ev, 0));
                 // the long kernel first, so that a lone call does not start it behind the host work
                 // of the three short launches
-                int64_t rc = launch_gemm_q16_floor_add(ctx, da, db, dc, m, k, n, ctx->sm_count - side_sms);
+                int64_t rc = launch_floor(ctx->sm_count - side_sms);
                 cudaStream_t main_stream = ctx->stream;
                 const bool profiling = ctx->profile;
                 ctx->stream = ctx->side;  // the launchers below use the context's stream
                 ctx->profile = false;     // kernel timing covers the FP64 kernel, which spans the call
                 if (!rc) rc = launch_split_i32_bytes(ctx, da, ap, 0, m, k, kp);
-                if (!rc) rc = launch_split_i32_bytes(ctx, db, bp, 1, k, n, np);
+                if (!rc) rc = launch_split_i32_bytes(ctx, db, bp, b_what, k, n, np);
                 if (!rc) rc = launch_gemm_q16_linear_tc(ctx, ap, bp, dc, m, n, k, kp, np, true, side_sms);
                 ctx->stream = main_stream;
                 ctx->profile = profiling;
@@ -648,9 +658,9 @@ int64_t gemm_q16_local(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, in
                 return call.end(true);
             }
             MB200_TRY(launch_split_i32_bytes(ctx, da, ap, 0, m, k, kp));
-            MB200_TRY(launch_split_i32_bytes(ctx, db, bp, 1, k, n, np));
+            MB200_TRY(launch_split_i32_bytes(ctx, db, bp, b_what, k, n, np));
             MB200_TRY(launch_gemm_q16_linear_tc(ctx, ap, bp, dc, m, n, k, kp, np, false, 0));
-            MB200_TRY(launch_gemm_q16_floor_add(ctx, da, db, dc, m, k, n, 0));
+            MB200_TRY(launch_floor(0));
             return call.end(true);
         }
         if (fp64_ok)
@@ -829,12 +839,13 @@ int64_t mind_b200_reserve(int64_t scratch_bytes, int64_t staging_bytes) {
 
 int64_t mind_b200_set_gemm_path(int64_t path) {
     clear_error();
-    if (path < 0 || path > 13)
-        return fail(MIND_B200_ERR_INVALID, "gemm path must be 0 (auto), 1 (CUDA cores), 2 / 3 (CTA pairs / single CTA), 4 / 5 (the same with B transposed first), 6 / 7 (Q16.16: FP64-pipe kernel alone / tensor-core hybrid), 8 / 9 (the hybrid with its halves in sequence / side by side) 10 / 11 (int8: the narrow-tile kernel always / never) or 12 / 13 (int8: the 256 x 512-tile pair kernel always / never)");
+    if (path < 0 || path > 14)
+        return fail(MIND_B200_ERR_INVALID, "gemm path must be 0 (auto), 1 (CUDA cores), 2 / 3 (CTA pairs / single CTA), 4 / 5 (the same with B transposed first), 6 / 7 (Q16.16: FP64-pipe kernel alone / tensor-core hybrid), 8 / 9 (the hybrid with its halves in sequence / side by side) 10 / 11 (int8: the narrow-tile kernel always / never) 12 / 13 (int8: the 256 x 512-tile pair kernel always / never) or 14 (Q16.16: the hybrid with its floor term on the FP64 pipe)");
     Tuning& t = tuning();
     t.force_transpose = (path == 4 || path == 5) ? 1 : 0;
-    t.q16_mode = path == 6 ? 6 : (path >= 7 && path <= 9) ? 7 : 0;
-    t.q16_side_sms = path == 8 ? 0 : path == 9 ? 16 : -1;
+    t.q16_mode = path == 6 ? 6 : ((path >= 7 && path <= 9) || path == 14) ? 7 : 0;
+    t.q16_floor = path == 14 ? 1 : 0;
+    t.q16_side_sms = path == 8 ? 0 : path == 9 ? 32 : -1;
     t.small_tile = path == 10 ? 1 : (path == 0 ? -1 : 0);
     t.wide_pair = path == 12 ? 1 : (path == 0 ? -1 : 0);
     t.gemm_path = path == 1 ? 1 : 0;
@@ -903,6 +914,22 @@ int64_t mind_b200_profile_read(int64_t* launches_out, double* total_ms_out) {
     if (total_ms_out) *total_ms_out = total;
     ctx->prof_count = 0;
     return 0;
+}
+
+int64_t mind_b200_set_q16_split(int64_t side_sms) {
+    clear_error();
+    if (side_sms < -1 || side_sms > 1024) return fail(MIND_B200_ERR_INVALID, "bad SM count");
+    tuning().q16_side_sms = (int)side_sms;
+    return 0;
+}
+
+int64_t mind_b200_fp32_fma_peak(double* fma_per_s_out, double* sm_mhz_out) {
+    clear_error();
+    if (!fma_per_s_out) return fail(MIND_B200_ERR_INVALID, "null output");
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return MIND_B200_ERR_NO_DEVICE;
+    DevLock lock(ctx->mu);
+    return measure_fp32_fma_peak(ctx, fma_per_s_out, sm_mhz_out);
 }
 
 int64_t mind_b200_fp64_fma_peak(double* fma_per_s_out, double* sm_mhz_out) {

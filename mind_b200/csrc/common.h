@@ -33,6 +33,7 @@ struct Tuning {
     std::atomic<int> gemm_path{0};        // 0 = tensor cores, 1 = CUDA-core cross-check kernels
     std::atomic<int> force_transpose{0};  // tensor cores: always re-lay B out K-contiguous
     std::atomic<int> q16_mode{0};         // Q16.16 GEMM: 0 = by size, 6 = FP64-pipe kernel alone, 7 = hybrid
+    std::atomic<int> q16_floor{0};        // hybrid: the per-product floor on 0 = the FP32 pipe (low halves), 1 = the FP64 pipe
     std::atomic<int> q16_side_sms{-1};    // hybrid: SMs of the tensor-core half beside the FP64 half (-1 = by size)
     std::atomic<int> pair_mode{0};        // CTAs per int8 tile: 1, 2, or 0 = pick per call
     std::atomic<int> small_tile{-1};      // int8 GEMM narrow-tile kernel: -1 = by shape, 0 = never, 1 = always
@@ -206,9 +207,13 @@ bool tc_pair_forced();
 // of element >> 16), and the tensor-core product of those planes (see gemm_tc.cu).
 int64_t launch_split_i32_bytes(DeviceCtx* ctx, const int32_t* src, uint8_t* const planes[4], int what,
                                int64_t rows, int64_t cols, int64_t pitch);
-int64_t launch_gemm_q16_linear_tc(DeviceCtx* ctx, const uint8_t* const a_limb[4], const uint8_t* const bh_limb[2],
+int64_t launch_gemm_q16_linear_tc(DeviceCtx* ctx, const uint8_t* const a_limb[4], const uint8_t* const b_limb[4],
                                   int32_t* p_out, int64_t m, int64_t n, int64_t k, int64_t kp_a,
                                   int64_t pitch_b, bool accumulate, int max_ctas);
+// The per-product floor term of the low halves on the FP32 pipe, added onto c (gemm_q16_f32.cu).
+int64_t launch_gemm_q16_floor_f32(DeviceCtx* ctx, const int32_t* a, const int32_t* b, int32_t* c, int64_t m,
+                                  int64_t k, int64_t n, int max_blocks);
+int64_t measure_fp32_fma_peak(DeviceCtx* ctx, double* fma_per_s, double* sm_mhz);
 // Floor part of the Q16.16 product on the FP64 pipe, added onto the linear part already in c.
 int64_t launch_gemm_q16_floor_add(DeviceCtx* ctx, const int32_t* a, const int32_t* b, int32_t* c, int64_t m,
                                   int64_t k, int64_t n, int max_blocks);

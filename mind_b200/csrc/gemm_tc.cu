@@ -107,6 +107,7 @@ struct TcParams {
     const int32_t* row_sums;  // int16 mode: sum of every row of A
     int accumulate;           // add onto C with red.global.add (C shared with a kernel running beside this one)
     int k_splits;             // > 1: every tile's K range is cut into this many work items (accumulate is set, C zeroed)
+    int q16_low;              // Q16.16 linear mode: a second pass over K adds (a >> 16) * (b & 0xffff)
     int tma_store;            // the epilogue hands its 32 x 32 blocks to TMA stores (C 16-byte aligned, N % 4 == 0, no accumulate)
     int* err;
 };
@@ -150,6 +151,7 @@ __global__ void __launch_bounds__(tc_threads<MODE, PAIR>(), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
                const __grid_constant__ CUtensorMap tm_a2, const __grid_constant__ CUtensorMap tm_a3,
                const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
+               const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_b3,
                const __grid_constant__ CUtensorMap tm_c, const TcParams p) {
     constexpr bool Q16LIN = MODE == 2 || MODE == 4;  // linear part of the Q16.16 product (wide / narrow tiles)
     static_assert(!Q16LIN || (PAIR == 1 && BMN), "the Q16.16 linear-part mode is single-CTA, B in place");
@@ -224,6 +226,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
             prefetch_tensormap(&tm_a3);
         }
         if (cfg::NB == 2) prefetch_tensormap(&tm_b1);
+        if (Q16LIN && p.q16_low) {
+            prefetch_tensormap(&tm_b2);
+            prefetch_tensormap(&tm_b3);
+        }
     }
     if (warp == 1) {
         tmem_alloc<PAIR>(tmem_slot, TMEM_COLS);
@@ -262,6 +268,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                 const int row_b = tn * BLOCK_N + (int)cta * B_ROWS;
                 const int kb0 = (item % p.k_splits) * kb_per_split;
                 const int kb1 = min(k_blocks, kb0 + kb_per_split);
+                // Q16.16 with the low-half term: a second pass over the same K range, in which a
+                // stage holds only the two high planes of a and the two planes of b & 0xffff
+                const int passes = (Q16LIN && p.q16_low) ? 2 : 1;
+                for (int pass = 0; ok && pass < passes; ++pass)
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
                     if (!wait_bounded(empty0 + 8 * s, ph ^ 1u, abort_s, p.err, 1)) {
@@ -270,7 +280,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                     }
                     const uint32_t dst = tiles0 + s * STAGE_BYTES;
                     const int kx = kb * BLOCK_K;
-                    if (PAIR == 1) {
+                    if (Q16LIN && pass == 1) {
+                        const uint32_t bar = full0 + 8 * s;
+                        mbar_arrive_expect_tx(bar, 2 * A_TILE_BYTES + 2 * B_TILE_BYTES);
+                        tma_load_2d(dst + 2 * A_TILE_BYTES, &tm_a2, bar, kx, row_a, pol_a);
+                        tma_load_2d(dst + 3 * A_TILE_BYTES, &tm_a3, bar, kx, row_a, pol_a);
+                        const uint32_t db = dst + cfg::NA * A_TILE_BYTES;
+#pragma unroll
+                        for (int j = 0; j < B_ROWS / BOX_N; ++j) {
+                            tma_load_2d(db + j * B_BOX_BYTES, &tm_b2, bar, row_b + BOX_N * j, kx, pol_b);
+                            tma_load_2d(db + B_TILE_BYTES + j * B_BOX_BYTES, &tm_b3, bar, row_b + BOX_N * j, kx, pol_b);
+                        }
+                    } else if (PAIR == 1) {
                         const uint32_t bar = full0 + 8 * s;
                         mbar_arrive_expect_tx(bar, STAGE_BYTES);
                         tma_load_2d(dst, &tm_a0, bar, kx, row_a, pol_a);
@@ -349,6 +370,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                 const uint32_t d0 = tmem_base + as * ACC_COLS;
                 const int kb0 = (item % p.k_splits) * kb_per_split;
                 const int kb1 = min(k_blocks, kb0 + kb_per_split);
+                const int passes = (Q16LIN && p.q16_low) ? 2 : 1;
+                for (int pass = 0; ok && pass < passes; ++pass)
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
                     if (!wait_bounded(full0 + 8 * s, ph, abort_s, p.err, 3)) {
@@ -363,7 +386,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                                          : BOX_N == 128 ? smem_desc_mn_sw128(sb, B_BOX_BYTES) : smem_desc_mn_sw64(sb);
 #pragma unroll
                     for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks) {
-                        const uint32_t acc = (kb != kb0 || ks != 0) ? 1u : 0u;
+                        const uint32_t acc = (kb != kb0 || ks != 0 || pass != 0) ? 1u : 0u;
                         const uint64_t koff = (uint64_t)((ks * UMMA_K) >> 4);
                         const uint64_t kb_off = (uint64_t)ks * B_KSTEP;
                         if (MODE == 5) {
@@ -385,6 +408,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant_
                             const uint64_t b0d = db0 + kb_off;
                             const uint64_t b1d = (BOX_N == 128 ? smem_desc_mn_sw128(sb + B_TILE_BYTES, B_BOX_BYTES)
                                                                : smem_desc_mn_sw64(sb + B_TILE_BYTES)) + kb_off;
+                            if (pass == 1) {
+                                // ah * bl, ah = a3*256 + a2 (a3 signed), bl = bl1*256 + bl0 (both unsigned):
+                                // the stage's B planes are bl0 and bl1 in this pass
+                                mma_i8<PAIR>(d0, a2d, b0d, ID_UU, 1u);                   // a2.bl0      -> s0
+                                mma_i8<PAIR>(d0 + BLOCK_N, a3d, b0d, ID_SU, 1u);         // a3.bl0      -> s1
+                                mma_i8<PAIR>(d0 + BLOCK_N, a2d, b1d, ID_UU, 1u);         // a2.bl1      -> s1
+                                mma_i8<PAIR>(d0 + 2 * BLOCK_N, a3d, b1d, ID_SU, 1u);     // a3.bl1      -> s2
+                                continue;
+                            }
                             mma_i8<PAIR>(d0, a0d, b0d, ID_UU, acc);                  // a0.bh0      -> s0
                             mma_i8<PAIR>(d0 + BLOCK_N, a0d, b1d, ID_US, acc);        // a0.bh1      -> s1
                             mma_i8<PAIR>(d0 + BLOCK_N, a1d, b0d, ID_UU, 1u);         // a1.bh0      -> s1
@@ -654,7 +686,7 @@ template <int MODE, int PAIR, bool BMN>
 int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0, const void* b1,
                   int32_t* c, int64_t m, int64_t n, int64_t k, int64_t kp_a, int64_t kp_b,
                   const void* a2 = nullptr, const void* a3 = nullptr, const int32_t* row_sums = nullptr,
-                  bool accumulate = false, int max_ctas = 0) {
+                  bool accumulate = false, int max_ctas = 0, const void* b2 = nullptr, const void* b3 = nullptr) {
     using cfg = Cfg<MODE, PAIR>;
     constexpr int B_ROWS = cfg::BLOCK_N / PAIR;
     constexpr int BOX_N = B_ROWS < 128 ? B_ROWS : 128;  // width of an MN-major box = its swizzle width
@@ -683,7 +715,13 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
         else
             MB200_TRY(make_tmap(&tb1, b1, k, n, kp_b, B_ROWS));
     }
+    CUtensorMap tb2 = tb0, tb3 = tb0;
+    if (b2 && b3) {  // Q16.16: the planes of b & 0xffff, for the second pass
+        MB200_TRY(make_tmap(&tb2, b2, n, k, kp_b, BLOCK_K, BOX_N));
+        MB200_TRY(make_tmap(&tb3, b3, n, k, kp_b, BLOCK_K, BOX_N));
+    }
     TcParams p;
+    p.q16_low = (b2 && b3) ? 1 : 0;
     p.c = c;
     p.m = (int)m;
     p.n = (int)n;
@@ -783,7 +821,7 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
         }
     }
     prof_begin(ctx);
-    MB200_CUDA(cudaLaunchKernelEx(&lc, kern, ta0, ta1, ta2, ta3, tb0, tb1, tc, p));
+    MB200_CUDA(cudaLaunchKernelEx(&lc, kern, ta0, ta1, ta2, ta3, tb0, tb1, tb2, tb3, tc, p));
     prof_end(ctx);
     count_launch();
     return check_launch("gemm_tc_kernel");
@@ -845,20 +883,22 @@ int64_t launch_gemm_i8_tc_bmn(DeviceCtx* ctx, const int8_t* a, const int8_t* b, 
 
 bool tc_pair_forced() { return tuning().pair_mode.load() == 2; }
 
-// Linear part of the Q16.16 GEMM on tensor cores: P[i,j] = sum_k a[i,k] * bh[k,j] mod 2^32,
-// from the four byte planes of a (a_limb[0] lowest, a_limb[3] signed) and the two byte planes
-// of bh = b >> 16 (bh_limb[1] signed), B planes in B's own orientation ([K][pitch_b]).
+// Linear part of the Q16.16 GEMM on tensor cores, mod 2^32, from byte planes: a_limb[0..3] the
+// bytes of a (a_limb[3] signed), b_limb[0..1] the bytes of bh = b >> 16 (b_limb[1] signed) and,
+// when given, b_limb[2..3] the bytes of bl = b & 0xffff; B planes in B's own orientation
+// ([K][pitch_b]).  Without bl planes P = sum_k a * bh (seven limb products); with them
+// P = sum_k a * bh + (a >> 16) * bl (four more, in a second pass over K).
 // accumulate: add onto p_out (red.global.add) instead of storing; max_ctas > 0 caps the persistent
 // grid, for running beside another kernel that holds the other SMs.
-int64_t launch_gemm_q16_linear_tc(DeviceCtx* ctx, const uint8_t* const a_limb[4], const uint8_t* const bh_limb[2],
+int64_t launch_gemm_q16_linear_tc(DeviceCtx* ctx, const uint8_t* const a_limb[4], const uint8_t* const b_limb[4],
                                   int32_t* p_out, int64_t m, int64_t n, int64_t k, int64_t kp_a,
                                   int64_t pitch_b, bool accumulate, int max_ctas) {
     // fewer 128 x 128 tiles than SMs: 64-column tiles put twice as many CTAs on a latency-bound product
     if (max_ctas <= 0 && ((m + 127) / 128) * ((n + 127) / 128) < ctx->sm_count)
-        return launch_tc<4, 1, true>(ctx, a_limb[0], a_limb[1], bh_limb[0], bh_limb[1], p_out, m, n, k, kp_a,
-                                     pitch_b, a_limb[2], a_limb[3], nullptr, accumulate, max_ctas);
-    return launch_tc<2, 1, true>(ctx, a_limb[0], a_limb[1], bh_limb[0], bh_limb[1], p_out, m, n, k, kp_a,
-                                 pitch_b, a_limb[2], a_limb[3], nullptr, accumulate, max_ctas);
+        return launch_tc<4, 1, true>(ctx, a_limb[0], a_limb[1], b_limb[0], b_limb[1], p_out, m, n, k, kp_a,
+                                     pitch_b, a_limb[2], a_limb[3], nullptr, accumulate, max_ctas, b_limb[2], b_limb[3]);
+    return launch_tc<2, 1, true>(ctx, a_limb[0], a_limb[1], b_limb[0], b_limb[1], p_out, m, n, k, kp_a,
+                                 pitch_b, a_limb[2], a_limb[3], nullptr, accumulate, max_ctas, b_limb[2], b_limb[3]);
 }
 
 int64_t launch_gemm_i16_tc_bmn(DeviceCtx* ctx, const int8_t* a_hi, const uint8_t* a_lo,

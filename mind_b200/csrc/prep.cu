@@ -271,7 +271,8 @@ __global__ void __launch_bounds__(256) split_i16_fused_kernel(const SplitJob j0,
 
 // int32 matrix [rows][cols] -> byte planes [rows][pitch] (cols % 4 == 0, 16-byte aligned source).
 // WHAT = 0: the four bytes of each element (plane 3 holds the signed top byte);
-// WHAT = 1: the two bytes of (element >> 16), i.e. planes 0 / 1 = bytes 2 / 3 of the element.
+// WHAT = 1: the two bytes of (element >> 16), i.e. planes 0 / 1 = bytes 2 / 3 of the element;
+// WHAT = 2: those two, then planes 2 / 3 = bytes 0 / 1 (the high half first, then the low half).
 template <int WHAT>
 __global__ void split_i32_bytes_kernel(const int4* __restrict__ src, uint8_t* __restrict__ p0,
                                        uint8_t* __restrict__ p1, uint8_t* __restrict__ p2,
@@ -296,6 +297,10 @@ __global__ void split_i32_bytes_kernel(const int4* __restrict__ src, uint8_t* __
         } else {
             *reinterpret_cast<uint32_t*>(p0 + o) = b2;
             *reinterpret_cast<uint32_t*>(p1 + o) = b3;
+            if (WHAT == 2) {
+                *reinterpret_cast<uint32_t*>(p2 + o) = b0;
+                *reinterpret_cast<uint32_t*>(p3 + o) = b1;
+            }
         }
     }
 }
@@ -311,6 +316,9 @@ int64_t launch_split_i32_bytes(DeviceCtx* ctx, const int32_t* src, uint8_t* cons
     const int4* s4 = reinterpret_cast<const int4*>(src);
     if (what == 0)
         split_i32_bytes_kernel<0><<<(unsigned)blocks, 256, 0, ctx->stream>>>(s4, planes[0], planes[1], planes[2],
+                                                                             planes[3], rows, cols / 4, pitch);
+    else if (what == 2)
+        split_i32_bytes_kernel<2><<<(unsigned)blocks, 256, 0, ctx->stream>>>(s4, planes[0], planes[1], planes[2],
                                                                              planes[3], rows, cols / 4, pitch);
     else
         split_i32_bytes_kernel<1><<<(unsigned)blocks, 256, 0, ctx->stream>>>(s4, planes[0], planes[1], nullptr,

@@ -102,9 +102,96 @@ __global__ void fp64_fma_peak_kernel(double* __restrict__ sink, int iters, doubl
     }
 }
 
+// The same for the FP32 pipe in the form the Q16.16 floor kernel uses it: packed fma.rm.f32x2, an
+// 8 x 4 tile of register pairs (64 chains per thread).  Counts FMAs, two per instruction.
+__global__ void fp32_fma_peak_kernel(float* __restrict__ sink, int iters, float x, float y,
+                                     unsigned long long* __restrict__ clocks) {
+    unsigned long long c0 = 0, t0 = 0;
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        c0 = clock64();
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    }
+    unsigned long long acc[8][4], a[8], b[4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const unsigned int av = __float_as_uint(x + (float)i);
+        a[i] = ((unsigned long long)av << 32) | av;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const unsigned int s = __float_as_uint(8388608.0f + (float)((threadIdx.x + 4 * i + j) & 255));
+            acc[i][j] = ((unsigned long long)s << 32) | s;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const unsigned int lo = __float_as_uint(y + 0.25f * (float)j), hi = __float_as_uint(y + 0.125f * (float)j);
+        b[j] = ((unsigned long long)hi << 32) | lo;
+    }
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                asm volatile("fma.rm.f32x2 %0, %1, %2, %0;" : "+l"(acc[i][j]) : "l"(a[i]), "l"(b[j]));
+    }
+    unsigned long long t = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) t ^= acc[i][j];
+    if (t == 0x123456789abcdefull) sink[0] = 1.0f;  // never true: keeps the chains alive
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        clocks[0] = clock64() - c0;
+        clocks[1] = t1 - t0;
+    }
+}
+
+// One of the two peak kernels, timed: FMA / s over the whole device and the SM clock it ran at.
+template <typename Launch>
+int64_t time_peak_kernel(DeviceCtx* ctx, const char* name, double fma_per_thread, Launch launch, double* fma_per_s,
+                         double* sm_mhz) {
+    const int threads = 256, blocks = ctx->sm_count;
+    unsigned long long* clocks = nullptr;
+    MB200_CUDA(cudaMalloc(&clocks, 2 * sizeof(unsigned long long) + sizeof(double)));
+    cudaEvent_t e0, e1;
+    MB200_CUDA(cudaEventCreate(&e0));
+    MB200_CUDA(cudaEventCreate(&e1));
+    float ms = 0.f;
+    for (int rep = 0; rep < 2; ++rep) {
+        MB200_CUDA(cudaEventRecord(e0, ctx->stream));
+        launch(blocks, threads, clocks);
+        MB200_CUDA(cudaEventRecord(e1, ctx->stream));
+        count_launch();
+        MB200_TRY(check_launch(name));
+        MB200_CUDA(cudaEventSynchronize(e1));
+        MB200_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    unsigned long long h[2] = {0, 0};
+    MB200_CUDA(cudaMemcpy(h, clocks, sizeof h, cudaMemcpyDeviceToHost));
+    cudaFree(clocks);
+    *fma_per_s = ms > 0.f ? (double)blocks * threads * fma_per_thread / (ms * 1e-3) : 0.0;
+    if (sm_mhz) *sm_mhz = h[1] ? (double)h[0] * 1e3 / (double)h[1] : 0.0;
+    return 0;
+}
+
 }  // namespace
 
-// FMA / s of the kernel above on the current device (CUDA events around one launch, after a
+int64_t measure_fp32_fma_peak(DeviceCtx* ctx, double* fma_per_s, double* sm_mhz) {
+    const int iters = 1 << 13;
+    return time_peak_kernel(
+        ctx, "fp32_fma_peak_kernel", (double)iters * 64.0,
+        [&](int blocks, int threads, unsigned long long* clocks) {
+            fp32_fma_peak_kernel<<<blocks, threads, 0, ctx->stream>>>(reinterpret_cast<float*>(clocks + 2), iters, 3.0f,
+                                                                     0.25f, clocks);
+        },
+        fma_per_s, sm_mhz);
+}
+
+// FMA / s of fp64_fma_peak_kernel on the current device (CUDA events around one launch, after a
 // warm-up launch).  Synchronous.
 int64_t measure_fp64_fma_peak(DeviceCtx* ctx, double* fma_per_s, double* sm_mhz) {
     const int iters = 1 << 13, threads = 256;

@@ -153,9 +153,13 @@ def test_gemm_i16_shapes(gpu, path):
         assert np.all(c[m * n :] == 0x5A5A5A5A)
 
 
-# 0: by size; 1: all-integer kernel; 6: FP64-pipe kernel alone; 7: tensor-core linear part + FP64 floor
-# part (8: one after the other, 9: side by side on two streams, both adding onto C)
-@pytest.mark.parametrize("path", [0, 1, 6, 7, 8, 9])
+# 0: by size; 1: all-integer kernel; 6: FP64-pipe kernel alone; 7: tensor-core linear part + the floor
+# term on the FP32 pipe (8: one after the other, 9: side by side on two streams, both adding onto C);
+# 14: the hybrid with the floor term on the FP64 pipe
+Q16_PATHS = [0, 1, 6, 7, 8, 9, 14]
+
+
+@pytest.mark.parametrize("path", Q16_PATHS)
 def test_gemm_q16_shapes(gpu, path):
     gpu.set_gemm_path(path)
     # the last shape has a long K on a single output tile: many blocks add into the same outputs
@@ -220,7 +224,7 @@ def test_q16_floor_chain_range_and_long_k(gpu):
     both ends of the range across one slice boundary: a = INT_MIN / INT_MAX with b & 0xffff =
     0xffff for K = 2^20 + 48, several blocks sharing one output tile."""
     m, n, k = 8, 4, (1 << 20) + 48
-    gpu.set_gemm_path(7)
+    gpu.set_gemm_path(14)
     try:
         for aval in (-2**31, 2**31 - 1):
             a = np.full(m * k, aval, dtype=np.int64).astype(np.int32)
@@ -230,6 +234,27 @@ def test_q16_floor_chain_range_and_long_k(gpu):
             c = np.empty(m * n, dtype=np.int32)
             gpu.matmul_mm_q16_v(a, b, c, m, k, n)
             assert np.array_equal(c, O.gemm_q16(a, b, m, k, n)), aval
+    finally:
+        gpu.set_gemm_path(0)
+
+
+@pytest.mark.parametrize("path", [7, 8, 9])
+def test_q16_f32_chain_holds_128_full_terms(gpu, path):
+    """The default hybrid adds floor((a & 0xffff) * (b & 0xffff) / 65536) to binary32 chains that
+    start at 2^23 and are emptied every 128 products; a chain is exact only while it stays below
+    2^24.  Every product at the largest possible term (both low halves 0xffff, term 65534), every
+    sign combination of the high halves, K across several emptyings and not a multiple of 128."""
+    m, n, k = 136, 132, 128 * 5 + 20
+    gpu.set_gemm_path(path)
+    try:
+        for aval, bval in ((-1, -1), (0xFFFF, 0xFFFF), (0x7FFFFFFF, -1), (-1, 0x7FFFFFFF), (-0x7FFF0001, 0x7FFFFFFF)):
+            a = np.full(m * k, aval, dtype=np.int64).astype(np.int32)
+            b = np.full(k * n, bval, dtype=np.int64).astype(np.int32)
+            a[:: 257] = 0x1234FFFE                           # not all equal
+            b[:: 263] = -0x10000 + 0xFFFE
+            c = np.empty(m * n, dtype=np.int32)
+            gpu.matmul_mm_q16_v(a, b, c, m, k, n)
+            assert np.array_equal(c, O.gemm_q16(a, b, m, k, n)), (aval, bval)
     finally:
         gpu.set_gemm_path(0)
 
