@@ -17,7 +17,7 @@ OBJ = os.path.join(PKG, "build")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB = os.path.join(LIB_DIR, "libmind_b200.so")
 
-SOURCES = ["context.cu", "prep.cu", "util.cu", "gemm_simt.cu", "gemm_q16.cu", "gemm_q16_f32.cu", "gemv.cu", "gemm_tc.cu",
+SOURCES = ["context.cu", "prep.cu", "util.cu", "gemm_simt.cu", "gemm_q16.cu", "gemm_q16_f32.cu", "gemm_q16_fused.cu", "gemv.cu", "gemm_tc.cu",
            "abi.cu", "multi.cu", "staging.cu", "runtime.cu", "no_alloc.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -576,6 +576,7 @@ int64_t gemm_q16_local(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, in
     const int g_gemm_path = tuning().gemm_path.load(), g_q16_mode = tuning().q16_mode.load(),
               g_q16_side_sms = tuning().q16_side_sms.load();
     const bool floor_f32 = tuning().q16_floor.load() == 0;
+    const bool want_fused = floor_f32 && tuning().q16_fused.load() == 1 && g_q16_side_sms < 0;
     Call call(ctx);
     const int ia = call.add((void*)a, (size_t)m * k * 4, false);
     const int ib = call.add((void*)b, (size_t)k * n * 4, false);
@@ -589,11 +590,13 @@ int64_t gemm_q16_local(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, in
         // the byte planes of the tensor-core hybrid
         const int64_t kp = (int64_t)align_up((size_t)k, 16), np = (int64_t)align_up((size_t)n, 16);
         const size_t a_plane = align_up((size_t)m * kp, 1024), b_plane = align_up((size_t)k * np, 1024);
+        const int64_t mp = (int64_t)align_up((size_t)m, 4);
+        const size_t a_low_bytes = align_up((size_t)k * mp * 4, 1024), b_low_bytes = align_up((size_t)k * np * 4, 1024);
         const bool big = (double)m * (double)n * (double)k >= 536870912.0;  // measured cross-over: 768^3 .. 1024^3
         const bool may_hybrid = g_gemm_path != 1 && k % 4 == 0 && n % 4 == 0 &&
                                 (g_q16_mode == 7 || (g_q16_mode == 0 && big));
         MB200_TRY(arena_reserve(ctx, ctx->scratch, (b_transposed ? align_up((size_t)k * n * 4, 1024) : 0) +
-                                                       (may_hybrid ? 4 * a_plane + 4 * b_plane : 0) + 16384));
+                                                       (may_hybrid ? 4 * a_plane + 4 * b_plane + (want_fused ? a_low_bytes + b_low_bytes : 0) : 0) + 16384));
         if (b_transposed) {
             int32_t* bkn = static_cast<int32_t*>(arena_take(ctx->scratch, (size_t)k * n * 4));
             MB200_TRY(launch_transpose_i32(ctx, db, bkn, n, k));
@@ -617,6 +620,16 @@ int64_t gemm_q16_local(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, in
             uint8_t* bp[4] = {nullptr, nullptr, nullptr, nullptr};
             for (int i = 0; i < 4; ++i) ap[i] = static_cast<uint8_t*>(arena_take(ctx->scratch, a_plane));
             for (int i = 0; i < (floor_f32 ? 4 : 2); ++i) bp[i] = static_cast<uint8_t*>(arena_take(ctx->scratch, b_plane));
+            // One kernel for both halves (gemm_q16_fused.cu) where it can run: the limb products
+            // hide behind the FMAs of the floor term on the same SM, and C is written once.
+            if (want_fused && gemm_q16_fused_usable(ctx)) {
+                float* a_low_t = static_cast<float*>(arena_take(ctx->scratch, a_low_bytes));
+                float* b_low = static_cast<float*>(arena_take(ctx->scratch, b_low_bytes));
+                MB200_TRY(launch_split_q16_a(ctx, da, ap, a_low_t, m, k, kp, mp));
+                MB200_TRY(launch_split_i32_bytes(ctx, db, bp, 3, k, n, np, b_low, np));
+                MB200_TRY(launch_gemm_q16_fused(ctx, ap, bp, a_low_t, b_low, dc, m, n, k, kp, np, mp, np));
+                return call.end(true);
+            }
             const int b_what = floor_f32 ? 2 : 1;
             auto launch_floor = [&](int max_blocks) {
                 return floor_f32 ? launch_gemm_q16_floor_f32(ctx, da, db, dc, m, k, n, max_blocks)
@@ -845,6 +858,7 @@ int64_t mind_b200_set_gemm_path(int64_t path) {
     t.force_transpose = (path == 4 || path == 5) ? 1 : 0;
     t.q16_mode = path == 6 ? 6 : ((path >= 7 && path <= 9) || path == 14) ? 7 : 0;
     t.q16_floor = path == 14 ? 1 : 0;
+    t.q16_fused = (path == 8 || path == 9 || path == 14) ? 0 : 1;
     t.q16_side_sms = path == 8 ? 0 : path == 9 ? 32 : -1;
     t.small_tile = path == 10 ? 1 : (path == 0 ? -1 : 0);
     t.wide_pair = path == 12 ? 1 : (path == 0 ? -1 : 0);

@@ -33,6 +33,7 @@ struct Tuning {
     std::atomic<int> gemm_path{0};        // 0 = tensor cores, 1 = CUDA-core cross-check kernels
     std::atomic<int> force_transpose{0};  // tensor cores: always re-lay B out K-contiguous
     std::atomic<int> q16_mode{0};         // Q16.16 GEMM: 0 = by size, 6 = FP64-pipe kernel alone, 7 = hybrid
+    std::atomic<int> q16_fused{1};        // hybrid: 1 = one fused kernel where it can run, 0 = the two-kernel forms
     std::atomic<int> q16_floor{0};        // hybrid: the per-product floor on 0 = the FP32 pipe (low halves), 1 = the FP64 pipe
     std::atomic<int> q16_side_sms{-1};    // hybrid: SMs of the tensor-core half beside the FP64 half (-1 = by size)
     std::atomic<int> pair_mode{0};        // CTAs per int8 tile: 1, 2, or 0 = pick per call
@@ -183,6 +184,10 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn encode_tiled_fn();
+// Tensor map over a row-major 8-bit matrix [rows][k] (row pitch in bytes): boxes of box_bytes (128
+// or 64, = the swizzle width) along k by box_rows rows.  Cached per thread (gemm_tc.cu).
+int64_t make_tmap_u8(CUtensorMap* tm, const void* base, int64_t k, int64_t rows, int64_t pitch, int box_rows,
+                     int box_bytes);
 
 // ---- kernels' host launchers (device pointers only, asynchronous on ctx->stream) ----
 // int8 GEMM on tensor cores: C[M,N] (i32) = A[M,K] . Bt[N,K]^T, both operands
@@ -206,7 +211,8 @@ bool tc_pair_forced();
 // Q16.16 hybrid: byte planes of an int32 matrix (what = 0: all four bytes; 1: the two bytes
 // of element >> 16), and the tensor-core product of those planes (see gemm_tc.cu).
 int64_t launch_split_i32_bytes(DeviceCtx* ctx, const int32_t* src, uint8_t* const planes[4], int what,
-                               int64_t rows, int64_t cols, int64_t pitch);
+                               int64_t rows, int64_t cols, int64_t pitch, float* low_scaled = nullptr,
+                               int64_t low_pitch = 0);
 int64_t launch_gemm_q16_linear_tc(DeviceCtx* ctx, const uint8_t* const a_limb[4], const uint8_t* const b_limb[4],
                                   int32_t* p_out, int64_t m, int64_t n, int64_t k, int64_t kp_a,
                                   int64_t pitch_b, bool accumulate, int max_ctas);
@@ -214,6 +220,26 @@ int64_t launch_gemm_q16_linear_tc(DeviceCtx* ctx, const uint8_t* const a_limb[4]
 int64_t launch_gemm_q16_floor_f32(DeviceCtx* ctx, const int32_t* a, const int32_t* b, int32_t* c, int64_t m,
                                   int64_t k, int64_t n, int max_blocks);
 int64_t measure_fp32_fma_peak(DeviceCtx* ctx, double* fma_per_s, double* sm_mhz);
+// The fused form (gemm_q16_fused.cu): limb products and floor term in one kernel.  a_low_t /
+// b_low are the binary32 planes launch_split_q16_a / launch_split_i32_bytes(what = 3) write.
+bool gemm_q16_fused_usable(DeviceCtx* ctx);
+int64_t launch_gemm_q16_fused(DeviceCtx* ctx, const uint8_t* const a_limb[4], const uint8_t* const b_limb[4],
+                              const float* a_low_t, const float* b_low, int32_t* c, int64_t m, int64_t n, int64_t k,
+                              int64_t kp_a, int64_t pitch_b, int64_t mp, int64_t np);
+// a[m][k] (k % 4 == 0, 16-byte aligned) -> its four byte planes [m][kp] and (a & 0xffff) as
+// binary32, transposed: a_low_t[k][mp] (mp % 4 == 0, mp >= m; columns m..mp-1 are written as zeros).
+int64_t launch_split_q16_a(DeviceCtx* ctx, const int32_t* a, uint8_t* const planes[4], float* a_low_t, int64_t m,
+                           int64_t k, int64_t kp, int64_t mp);
+
+// Low halves of Q16.16 operands as binary32, exactly, without the integer-to-float unit: the
+// 16-bit value is or-ed into the mantissa of 2^23 and 2^23 taken off again.
+constexpr uint32_t Q16_TWO23_BITS = 0x4B000000u;  // binary32 2^23: the low 23 bits are an integer field
+__device__ __forceinline__ float q16_low_half_f32(int32_t v) {  // (v & 0xffff)
+    return __uint_as_float(Q16_TWO23_BITS | ((uint32_t)v & 0xffffu)) - 8388608.0f;
+}
+__device__ __forceinline__ float q16_low_half_scaled_f32(int32_t v) {  // (v & 0xffff) * 2^-16: (2^23 + bl) * 2^-16 - 2^7
+    return __fmaf_rn(__uint_as_float(Q16_TWO23_BITS | ((uint32_t)v & 0xffffu)), 1.52587890625e-05f, -128.0f);
+}
 // Floor part of the Q16.16 product on the FP64 pipe, added onto the linear part already in c.
 int64_t launch_gemm_q16_floor_add(DeviceCtx* ctx, const int32_t* a, const int32_t* b, int32_t* c, int64_t m,
                                   int64_t k, int64_t n, int max_blocks);

@@ -42,17 +42,8 @@ __device__ __forceinline__ uint64_t fma2_rm(uint64_t a, uint64_t b, uint64_t c) 
     return d;
 }
 
-constexpr uint32_t TWO23_BITS = 0x4B000000u;  // binary32 2^23: the low 23 bits are an integer field
+constexpr uint32_t TWO23_BITS = Q16_TWO23_BITS;
 constexpr uint64_t CHAIN_START = ((uint64_t)TWO23_BITS << 32) | TWO23_BITS;
-
-// (v & 0xffff) as binary32, exactly
-__device__ __forceinline__ float low_half_f32(int32_t v) {
-    return __uint_as_float(TWO23_BITS | ((uint32_t)v & 0xffffu)) - 8388608.0f;
-}
-// (v & 0xffff) * 2^-16 as binary32, exactly: (2^23 + bl) * 2^-16 - 2^7, one rounding, nothing to round
-__device__ __forceinline__ float low_half_scaled_f32(int32_t v) {
-    return __fmaf_rn(__uint_as_float(TWO23_BITS | ((uint32_t)v & 0xffffu)), 1.52587890625e-05f, -128.0f);
-}
 
 struct F32Smem {
     float ad[2][FBK][FBM + 4];  // al
@@ -97,8 +88,8 @@ gemm_q16_f32_kernel(const int32_t* __restrict__ a, const int32_t* __restrict__ b
 #pragma unroll
         for (int i = 0; i < A_VEC; ++i) {
             const int r = (tid >> 2) + 64 * i, kq = (tid & 3) * 4;
-            const float x = low_half_f32(ra[i].x), y = low_half_f32(ra[i].y), z = low_half_f32(ra[i].z),
-                        w = low_half_f32(ra[i].w);
+            const float x = q16_low_half_f32(ra[i].x), y = q16_low_half_f32(ra[i].y), z = q16_low_half_f32(ra[i].z),
+                        w = q16_low_half_f32(ra[i].w);
             sm.ad[buf][kq][r] = x;
             sm.ad[buf][kq + 1][r] = y;
             sm.ad[buf][kq + 2][r] = z;
@@ -109,8 +100,8 @@ gemm_q16_f32_kernel(const int32_t* __restrict__ a, const int32_t* __restrict__ b
             const int e = tid + FTHREADS * i;
             const int kq = e / (FBN / 4), cc = (e % (FBN / 4)) * 4;
             *reinterpret_cast<float4*>(&sm.bf[buf][kq][cc]) =
-                make_float4(low_half_scaled_f32(rb[i].x), low_half_scaled_f32(rb[i].y), low_half_scaled_f32(rb[i].z),
-                            low_half_scaled_f32(rb[i].w));
+                make_float4(q16_low_half_scaled_f32(rb[i].x), q16_low_half_scaled_f32(rb[i].y), q16_low_half_scaled_f32(rb[i].z),
+                            q16_low_half_scaled_f32(rb[i].w));
         }
     };
 

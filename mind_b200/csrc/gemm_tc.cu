@@ -54,7 +54,6 @@ constexpr int BLOCK_K = 128;            // bytes (= 8-bit elements) of K per sta
 constexpr int UMMA_K = 32;              // K of one tcgen05.mma kind::i8
 constexpr int TC_THREADS = 192;  // TMA warp + MMA warp + four epilogue warps (see epi_warps)
 constexpr int A_TILE_BYTES = BLOCK_M * BLOCK_K;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 constexpr int EPI_PATCH_WORDS = 32 * 32;  // per epilogue warp: a 32 x 32 block of outputs (4 KiB, 1024-byte aligned)
 
 template <int MODE, int PAIR>
@@ -111,25 +110,6 @@ struct TcParams {
     int tma_store;            // the epilogue hands its 32 x 32 blocks to TMA stores (C 16-byte aligned, N % 4 == 0, no accumulate)
     int* err;
 };
-
-__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_s,
-                                             int* err_g, int code,
-                                             unsigned long long limit_ns = WAIT_LIMIT_NS) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = globaltimer_ns();
-    uint32_t spins = 0;
-    while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((++spins & 63u) == 0u) {
-            if (*abort_s) return false;
-            if (globaltimer_ns() - t0 > limit_ns) {
-                *abort_s = 1;
-                atomicCAS(err_g, 0, code);
-                return false;
-            }
-        }
-    }
-}
 
 __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int group_m, int raster,
                                             int& tm, int& tn) {
@@ -828,6 +808,11 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
 }
 
 }  // namespace
+
+int64_t make_tmap_u8(CUtensorMap* tm, const void* base, int64_t k, int64_t rows, int64_t pitch, int box_rows,
+                     int box_bytes) {
+    return make_tmap(tm, base, k, rows, pitch, box_rows, box_bytes);
+}
 
 int64_t launch_wait_selftest(DeviceCtx* ctx, int64_t limit_ms) {
     wait_selftest_kernel<<<1, 32, 0, ctx->stream>>>(ctx->err_word, (unsigned long long)limit_ms * 1000000ull);

@@ -272,11 +272,13 @@ __global__ void __launch_bounds__(256) split_i16_fused_kernel(const SplitJob j0,
 // int32 matrix [rows][cols] -> byte planes [rows][pitch] (cols % 4 == 0, 16-byte aligned source).
 // WHAT = 0: the four bytes of each element (plane 3 holds the signed top byte);
 // WHAT = 1: the two bytes of (element >> 16), i.e. planes 0 / 1 = bytes 2 / 3 of the element;
-// WHAT = 2: those two, then planes 2 / 3 = bytes 0 / 1 (the high half first, then the low half).
+// WHAT = 2: those two, then planes 2 / 3 = bytes 0 / 1 (the high half first, then the low half);
+// WHAT = 3: as 2, and (element & 0xffff) * 2^-16 as binary32 into low_scaled[rows][low_pitch].
 template <int WHAT>
 __global__ void split_i32_bytes_kernel(const int4* __restrict__ src, uint8_t* __restrict__ p0,
                                        uint8_t* __restrict__ p1, uint8_t* __restrict__ p2,
-                                       uint8_t* __restrict__ p3, int64_t rows, int64_t cols4, int64_t pitch) {
+                                       uint8_t* __restrict__ p3, int64_t rows, int64_t cols4, int64_t pitch,
+                                       float* __restrict__ low_scaled, int64_t low_pitch) {
     const int64_t total = rows * cols4;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
@@ -297,18 +299,71 @@ __global__ void split_i32_bytes_kernel(const int4* __restrict__ src, uint8_t* __
         } else {
             *reinterpret_cast<uint32_t*>(p0 + o) = b2;
             *reinterpret_cast<uint32_t*>(p1 + o) = b3;
-            if (WHAT == 2) {
+            if (WHAT >= 2) {
                 *reinterpret_cast<uint32_t*>(p2 + o) = b0;
                 *reinterpret_cast<uint32_t*>(p3 + o) = b1;
             }
+            if (WHAT == 3)
+                *reinterpret_cast<float4*>(low_scaled + r * low_pitch + c) =
+                    make_float4(q16_low_half_scaled_f32(v.x), q16_low_half_scaled_f32(v.y),
+                                q16_low_half_scaled_f32(v.z), q16_low_half_scaled_f32(v.w));
         }
+    }
+}
+
+// a[m][k] -> four byte planes [m][kp] and (a & 0xffff) as binary32, transposed to [k][mp]: tiles of
+// 64 rows by 64 of K, the transposition through shared memory so that both sides move whole lines.
+__global__ void __launch_bounds__(256)
+split_q16_a_kernel(const int32_t* __restrict__ a, uint8_t* __restrict__ p0, uint8_t* __restrict__ p1,
+                   uint8_t* __restrict__ p2, uint8_t* __restrict__ p3, float* __restrict__ a_low_t, int m, int k,
+                   int64_t kp, int64_t mp) {
+    __shared__ float ft[64][65];
+    const int r0 = blockIdx.y * 64, k0 = blockIdx.x * 64, tid = threadIdx.x;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = (tid >> 4) + 16 * i, kq = (tid & 15) * 4;
+        int4 v = make_int4(0, 0, 0, 0);
+        const bool inside = r0 + r < m && k0 + kq < k;
+        if (inside) v = *reinterpret_cast<const int4*>(a + (size_t)(r0 + r) * k + k0 + kq);
+        ft[kq][r] = q16_low_half_f32(v.x);
+        ft[kq + 1][r] = q16_low_half_f32(v.y);
+        ft[kq + 2][r] = q16_low_half_f32(v.z);
+        ft[kq + 3][r] = q16_low_half_f32(v.w);
+        if (inside) {
+            const uint32_t lo01 = __byte_perm(v.x, v.y, 0x5140), lo23 = __byte_perm(v.z, v.w, 0x5140);
+            const uint32_t hi01 = __byte_perm(v.x, v.y, 0x7362), hi23 = __byte_perm(v.z, v.w, 0x7362);
+            const int64_t o = (int64_t)(r0 + r) * kp + k0 + kq;
+            *reinterpret_cast<uint32_t*>(p0 + o) = __byte_perm(lo01, lo23, 0x5410);
+            *reinterpret_cast<uint32_t*>(p1 + o) = __byte_perm(lo01, lo23, 0x7632);
+            *reinterpret_cast<uint32_t*>(p2 + o) = __byte_perm(hi01, hi23, 0x5410);
+            *reinterpret_cast<uint32_t*>(p3 + o) = __byte_perm(hi01, hi23, 0x7632);
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int kk = (tid >> 4) + 16 * i, rq = (tid & 15) * 4;
+        if (k0 + kk < k && r0 + rq < mp)  // rows past m were read as zeros
+            *reinterpret_cast<float4*>(a_low_t + (size_t)(k0 + kk) * mp + r0 + rq) =
+                make_float4(ft[kk][rq], ft[kk][rq + 1], ft[kk][rq + 2], ft[kk][rq + 3]);
     }
 }
 
 }  // namespace
 
+int64_t launch_split_q16_a(DeviceCtx* ctx, const int32_t* a, uint8_t* const planes[4], float* a_low_t, int64_t m,
+                           int64_t k, int64_t kp, int64_t mp) {
+    if (m <= 0 || k <= 0) return 0;
+    dim3 grid((unsigned)((k + 63) / 64), (unsigned)((m + 63) / 64));
+    if (grid.y > 65535) return fail(MIND_B200_ERR_TOO_LARGE, "too many rows for the Q16.16 operand split");
+    split_q16_a_kernel<<<grid, 256, 0, ctx->stream>>>(a, planes[0], planes[1], planes[2], planes[3], a_low_t, (int)m,
+                                                      (int)k, kp, mp);
+    count_launch();
+    return check_launch("split_q16_a_kernel");
+}
+
 int64_t launch_split_i32_bytes(DeviceCtx* ctx, const int32_t* src, uint8_t* const planes[4], int what,
-                               int64_t rows, int64_t cols, int64_t pitch) {
+                               int64_t rows, int64_t cols, int64_t pitch, float* low_scaled, int64_t low_pitch) {
     const int64_t total = rows * (cols / 4);
     if (total <= 0) return 0;
     int64_t blocks = (total + 255) / 256;
@@ -316,13 +371,17 @@ int64_t launch_split_i32_bytes(DeviceCtx* ctx, const int32_t* src, uint8_t* cons
     const int4* s4 = reinterpret_cast<const int4*>(src);
     if (what == 0)
         split_i32_bytes_kernel<0><<<(unsigned)blocks, 256, 0, ctx->stream>>>(s4, planes[0], planes[1], planes[2],
-                                                                             planes[3], rows, cols / 4, pitch);
+                                                                             planes[3], rows, cols / 4, pitch, nullptr, 0);
     else if (what == 2)
         split_i32_bytes_kernel<2><<<(unsigned)blocks, 256, 0, ctx->stream>>>(s4, planes[0], planes[1], planes[2],
-                                                                             planes[3], rows, cols / 4, pitch);
+                                                                             planes[3], rows, cols / 4, pitch, nullptr, 0);
+    else if (what == 3)
+        split_i32_bytes_kernel<3><<<(unsigned)blocks, 256, 0, ctx->stream>>>(s4, planes[0], planes[1], planes[2],
+                                                                             planes[3], rows, cols / 4, pitch, low_scaled,
+                                                                             low_pitch);
     else
         split_i32_bytes_kernel<1><<<(unsigned)blocks, 256, 0, ctx->stream>>>(s4, planes[0], planes[1], nullptr,
-                                                                             nullptr, rows, cols / 4, pitch);
+                                                                             nullptr, rows, cols / 4, pitch, nullptr, 0);
     count_launch();
     return check_launch("split_i32_bytes_kernel");
 }

@@ -61,6 +61,79 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Wait on an mbarrier phase, bounded in time.  When the limit runs out the waiter raises the
+// CTA's abort flag and records `code` in the device error word (first failure wins); every other
+// waiter of the CTA sees the flag within 64 polls and gives up too.  Returns false on giving up.
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_s,
+                                             int* err_g, int code,
+                                             unsigned long long limit_ns = WAIT_LIMIT_NS) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 63u) == 0u) {
+            if (*abort_s) return false;
+            if (globaltimer_ns() - t0 > limit_ns) {
+                *abort_s = 1;
+                atomicCAS(err_g, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+// The same wait for a thread that goes on to READ, with ordinary loads, the shared memory the
+// barrier guards.  Returns `one` (any non-zero value the compiler cannot know: a kernel parameter)
+// on success and 0 on giving up; the caller folds (result - one) into the address of those loads,
+// which makes them data-dependent on the outcome of the wait.  The acquire of try_wait orders
+// them already; the dependency keeps that order out of the instruction scheduler's hands (on the
+// release side of the same pipeline an order left to it was seen to fail: gemm_q16_fused.cu).
+__device__ __forceinline__ uint32_t mbar_try_wait_dep(uint32_t bar, uint32_t parity, uint32_t one) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, %3, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"(bar), "r"(parity), "r"(one)
+        : "memory");
+    return r;
+}
+__device__ __forceinline__ uint32_t wait_bounded_dep(uint32_t bar, uint32_t parity, volatile int* abort_s, int* err_g,
+                                                     int code, uint32_t one,
+                                                     unsigned long long limit_ns = WAIT_LIMIT_NS) {
+    uint32_t r = mbar_try_wait_dep(bar, parity, one);
+    if (r) return r;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (true) {
+        r = mbar_try_wait_dep(bar, parity, one);
+        if (r) return r;
+        if ((++spins & 63u) == 0u) {
+            if (*abort_s) return 0u;
+            if (globaltimer_ns() - t0 > limit_ns) {
+                *abort_s = 1;
+                atomicCAS(err_g, 0, code);
+                return 0u;
+            }
+        }
+    }
+}
+
+// Registers per thread of the calling warpgroup (four consecutive warps, all of which must
+// execute this together): give some back to the CTA's pool, or take more from it (waits until
+// the pool has them).  N is a multiple of 8.
+template <int N>
+__device__ __forceinline__ void regs_release() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void regs_take() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // ----------------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");

@@ -350,7 +350,7 @@ def test_stability_reruns(gpu):
     a = lcg_dev(gpu, n * n, 0, seed)
     b = lcg_dev(gpu, n * n, 0, seed, offset=n * n)
     want = torch.from_numpy(O.gemm_q16(a.cpu().numpy(), b.cpu().numpy(), n, n, n)).cuda()
-    for path in (0, 8, 9, 1):  # single FP64-pipe kernel (this size), hybrid in sequence / side by side, all-integer
+    for path in (0, 7, 8, 9, 1):  # single FP64-pipe kernel (this size), fused hybrid, two-kernel hybrid in sequence / side by side, all-integer
         gpu.set_gemm_path(path)
         for _ in range(256 if path != 1 else 32):
             c = torch.empty(n * n, dtype=torch.int32, device="cuda")
@@ -383,6 +383,29 @@ def test_stability_reruns(gpu):
         assert torch.equal(c, want)
         gpu.matmul_mm_i16(a16, b16, c, m, k, n)
         assert torch.equal(c, want16)
+
+
+def test_q16_fused_kernel_under_producer_lag(gpu):
+    """The fused Q16.16 kernel's FP32 stages are a TMA ring that the compute warps release with an
+    mbarrier arrive.  Operands larger than L2 per call make the producer lag now and then, which
+    is when a release that could overtake the last reads of a stage showed (one tile in thirty at
+    2048^3 before the release was tied to the use of those reads).  Full-range operands, several
+    shapes (ragged ones too), every run against the all-integer kernel's bytes."""
+    for (m, k, n, reps) in ((2048, 2048, 2048, 12), (2048, 1024, 2048, 12), (1000, 2052, 1500, 8), (3000, 516, 3004, 8)):
+        seed = 0xDEADBEEF00000000 ^ (m * 131 + k * 17 + n)
+        a = lcg_dev(gpu, m * k, 0, seed, shift=0)
+        b = lcg_dev(gpu, k * n, 0, seed, offset=m * k, shift=0)
+        want = torch.empty(m * n, dtype=torch.int32, device="cuda")
+        gpu.set_gemm_path(1)
+        gpu.matmul_mm_q16_v(a, b, want, m, k, n)
+        for path in (8, 7):
+            gpu.set_gemm_path(path)
+            for _ in range(reps if path == 7 else 1):
+                c = torch.zeros(m * n, dtype=torch.int32, device="cuda")
+                gpu.matmul_mm_q16_v(a, b, c, m, k, n)
+                gpu.synchronize()
+                assert torch.equal(c, want), (path, m, k, n)
+    gpu.set_gemm_path(0)
 
 
 def test_cuda_graph_capture_and_replay(gpu):
