@@ -895,7 +895,7 @@ def run_mine(args, w):
         roofline = {"bound": w["bound"], "achieved": achieved, "peak": peak, "unit": w["unit"],
                     "frac": (achieved / peak) if achieved and peak else None,
                     "traffic": NCU_TRAFFIC.get(args.workload) if not args.size and world == 1 else None,
-                    "kernel": "gemm_tc_kernel" if w["bound"] == "tensor" else ("rows_group_kernel" if w["bound"] == "hbm" else "gemm_tc_kernel<2> + gemm_q16_f32_kernel"),
+                    "kernel": "gemm_tc_kernel" if w["bound"] == "tensor" else ("rows_group_kernel" if w["bound"] == "hbm" else "gemm_q16_fused_kernel"),
                     "kernel_ms": main_ms / args.steps if n_main else None, "peak_source": peak_note}
         if w["bound"] == "fp32-pipe" and achieved:
             # the ceiling of the earlier form of this kernel (one fma.rm.f64 per product), for comparison

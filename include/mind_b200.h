@@ -182,15 +182,16 @@ int64_t mind_b200_shutdown(void);
  * transposed into scratch first (otherwise B is read in place whenever its pitch and base are
  * 16-byte aligned); 1 = the independent CUDA-core kernels kept as an on-device cross-check
  * (for Q16.16: the all-integer kernel); 6 / 7 = Q16.16 GEMM only: the FP64-pipe kernel alone /
- * the tensor-core hybrid at every size (default: hybrid from 2^29 products up, i.e. about 800^3);
- * 8 / 9 = the hybrid with its two halves one after the other / side by side on two streams
- * (default: side by side up to 2^31 products, where the tensor-core half is latency-bound);
+ * the tensor-core hybrid at every size (default: hybrid from 2^29 products up, i.e. about 800^3).
+ * The hybrid is ONE kernel that forms the limb products on the tensor cores and the per-product
+ * floor term on the FP32 pipe of the same SM; 8 / 9 = the hybrid as two kernels instead, one
+ * after the other / side by side on two streams, both adding onto C;
  * 10 / 11 = int8 GEMM: the narrow-tile kernel (128 x 64 tiles, for products with few tiles)
  * always / never (default: when the wide tiles would leave most SMs idle); 12 / 13 = int8 GEMM:
  * the kernel with 256 x 512 tiles on CTA pairs always / never (default: for long K and many tiles);
- * 14 = Q16.16 GEMM only: the hybrid in its earlier form, floor(a * (b & 0xffff) / 65536) on the
- * FP64 pipe beside seven limb products (default: floor((a & 0xffff) * (b & 0xffff) / 65536) on the
- * FP32 pipe beside eleven).
+ * 14 = Q16.16 GEMM only: the two-kernel hybrid in its earlier form, floor(a * (b & 0xffff) / 65536)
+ * on the FP64 pipe beside seven limb products (default: floor((a & 0xffff) * (b & 0xffff) / 65536)
+ * on the FP32 pipe beside eleven).
  * Every path gives identical bytes.  The setting is process-wide and meant for tests and
  * measurements; a call that is already running keeps the kernels it chose. */
 int64_t mind_b200_set_gemm_path(int64_t path);

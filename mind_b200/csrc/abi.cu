@@ -625,8 +625,8 @@ int64_t gemm_q16_local(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, in
             if (want_fused && gemm_q16_fused_usable(ctx)) {
                 float* a_low_t = static_cast<float*>(arena_take(ctx->scratch, a_low_bytes));
                 float* b_low = static_cast<float*>(arena_take(ctx->scratch, b_low_bytes));
-                MB200_TRY(launch_split_q16_a(ctx, da, ap, a_low_t, m, k, kp, mp));
-                MB200_TRY(launch_split_i32_bytes(ctx, db, bp, 3, k, n, np, b_low, np));
+                MB200_TRY(launch_split_q16_ab(ctx, da, db, ap, bp, a_low_t, b_low, dc,
+                                              gemm_q16_fused_shares_tiles(ctx, m, n, k), m, k, n, kp, np, mp));
                 MB200_TRY(launch_gemm_q16_fused(ctx, ap, bp, a_low_t, b_low, dc, m, n, k, kp, np, mp, np));
                 return call.end(true);
             }

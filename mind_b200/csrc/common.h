@@ -211,8 +211,7 @@ bool tc_pair_forced();
 // Q16.16 hybrid: byte planes of an int32 matrix (what = 0: all four bytes; 1: the two bytes
 // of element >> 16), and the tensor-core product of those planes (see gemm_tc.cu).
 int64_t launch_split_i32_bytes(DeviceCtx* ctx, const int32_t* src, uint8_t* const planes[4], int what,
-                               int64_t rows, int64_t cols, int64_t pitch, float* low_scaled = nullptr,
-                               int64_t low_pitch = 0);
+                               int64_t rows, int64_t cols, int64_t pitch);
 int64_t launch_gemm_q16_linear_tc(DeviceCtx* ctx, const uint8_t* const a_limb[4], const uint8_t* const b_limb[4],
                                   int32_t* p_out, int64_t m, int64_t n, int64_t k, int64_t kp_a,
                                   int64_t pitch_b, bool accumulate, int max_ctas);
@@ -221,15 +220,21 @@ int64_t launch_gemm_q16_floor_f32(DeviceCtx* ctx, const int32_t* a, const int32_
                                   int64_t k, int64_t n, int max_blocks);
 int64_t measure_fp32_fma_peak(DeviceCtx* ctx, double* fma_per_s, double* sm_mhz);
 // The fused form (gemm_q16_fused.cu): limb products and floor term in one kernel.  a_low_t /
-// b_low are the binary32 planes launch_split_q16_a / launch_split_i32_bytes(what = 3) write.
+// b_low are the binary32 planes launch_split_q16_ab writes; c must be zero where tiles are shared.
 bool gemm_q16_fused_usable(DeviceCtx* ctx);
 int64_t launch_gemm_q16_fused(DeviceCtx* ctx, const uint8_t* const a_limb[4], const uint8_t* const b_limb[4],
                               const float* a_low_t, const float* b_low, int32_t* c, int64_t m, int64_t n, int64_t k,
                               int64_t kp_a, int64_t pitch_b, int64_t mp, int64_t np);
-// a[m][k] (k % 4 == 0, 16-byte aligned) -> its four byte planes [m][kp] and (a & 0xffff) as
-// binary32, transposed: a_low_t[k][mp] (mp % 4 == 0, mp >= m; columns m..mp-1 are written as zeros).
-int64_t launch_split_q16_a(DeviceCtx* ctx, const int32_t* a, uint8_t* const planes[4], float* a_low_t, int64_t m,
-                           int64_t k, int64_t kp, int64_t mp);
+// One launch that prepares everything the fused kernel reads (prep.cu: split_q16_ab_kernel):
+// a[m][k] -> its four byte planes [m][kp] and (a & 0xffff) as binary32, transposed: a_low_t[k][mp]
+// (mp % 4 == 0, mp >= m); b[k][n] -> the byte planes of b >> 16 (bp[0..1]) and of b & 0xffff
+// (bp[2..3]), [k][np], and (b & 0xffff) * 2^-16 as binary32, b_low[k][np]; zero_c: c[m][n] = 0.
+// k % 4 == 0, n % 4 == 0, 16-byte aligned a, b (and c when zeroed).
+int64_t launch_split_q16_ab(DeviceCtx* ctx, const int32_t* a, const int32_t* b, uint8_t* const ap[4],
+                            uint8_t* const bp[4], float* a_low_t, float* b_low, int32_t* c, bool zero_c, int64_t m,
+                            int64_t k, int64_t n, int64_t kp, int64_t np, int64_t mp);
+// Whether the fused kernel will add onto c for this shape (some tile is shared between CTAs), so c must start at zero.
+bool gemm_q16_fused_shares_tiles(DeviceCtx* ctx, int64_t m, int64_t n, int64_t k);
 
 // Low halves of Q16.16 operands as binary32, exactly, without the integer-to-float unit: the
 // 16-bit value is or-ed into the mantissa of 2^23 and 2^23 taken off again.

@@ -137,6 +137,9 @@ gemm_q16_fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(misc);
+    // from here on global memory is read and written: the kernel before this one (the operand
+    // split, which also zeroes C where tiles are shared) must be done
+    griddep_wait();
 
     // 384 threads start with 168 registers each; the third warpgroup keeps 56 and the two
     // compute warpgroups take 224 (256 * 224 + 128 * 56 = 384 * 168: the launcher checks that the
@@ -459,6 +462,16 @@ bool gemm_q16_fused_usable(DeviceCtx* ctx) {
     return usable;
 }
 
+// A tile shared by several blocks is added to with red.global.add: C must start from zero then
+// (the operand split does that).  Same partition rule as the kernel's.
+bool gemm_q16_fused_shares_tiles(DeviceCtx* ctx, int64_t m, int64_t n, int64_t k) {
+    const int64_t tiles = ((m + UT - 1) / UT) * ((n + UT - 1) / UT), k_units = (k + UNIT_K - 1) / UNIT_K;
+    const int64_t units = tiles * k_units, grid = units < ctx->sm_count ? units : ctx->sm_count;
+    for (int64_t b = 1; b < grid; ++b)
+        if ((units * b / grid) % k_units != 0) return true;
+    return false;
+}
+
 // c = the whole Q16.16 product.  a_limb[0..3]: byte planes of a ([m][kp_a], a_limb[3] signed);
 // b_limb[0..1]: bytes of b >> 16, b_limb[2..3]: bytes of b & 0xffff ([k][pitch_b]); a_low_t:
 // (a & 0xffff) as binary32, transposed, [k][mp]; b_low: (b & 0xffff) * 2^-16 as binary32, [k][np].
@@ -486,13 +499,22 @@ int64_t launch_gemm_q16_fused(DeviceCtx* ctx, const uint8_t* const a_limb[4], co
     p.err = ctx->err_word;
     p.one = 1u;
     const unsigned grid = (unsigned)(p.units < ctx->sm_count ? p.units : ctx->sm_count);
-    // a tile shared by several blocks is added to: C starts from zero then
-    bool shared_tiles = false;
-    for (unsigned b = 1; b < grid && !shared_tiles; ++b) shared_tiles = (p.units * b / grid) % p.k_units != 0;
-    if (shared_tiles) MB200_CUDA(cudaMemsetAsync(c, 0, (size_t)m * (size_t)n * 4, ctx->stream));
+    // Launched so that it may start while the kernel before it (the operand split) still runs: its
+    // set-up (barriers, TMEM, tensor-map prefetch, the register hand-over) touches no global memory,
+    // and every role waits for that kernel before its first global access.
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(grid, 1, 1);
+    lc.blockDim = dim3(FUSED_THREADS, 1, 1);
+    lc.dynamicSmemBytes = FUSED_SMEM;
+    lc.stream = ctx->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at;
+    lc.numAttrs = 1;
     prof_begin(ctx);
-    gemm_q16_fused_kernel<<<grid, FUSED_THREADS, FUSED_SMEM, ctx->stream>>>(ta[0], ta[1], ta[2], ta[3], tb[0], tb[1], tb[2],
-                                                                          tb[3], taf, tbf, p);
+    MB200_CUDA(cudaLaunchKernelEx(&lc, gemm_q16_fused_kernel, ta[0], ta[1], ta[2], ta[3], tb[0], tb[1], tb[2], tb[3], taf,
+                                  tbf, p));
     prof_end(ctx);
     count_launch();
     return check_launch("gemm_q16_fused_kernel");

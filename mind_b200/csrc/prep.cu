@@ -272,13 +272,11 @@ __global__ void __launch_bounds__(256) split_i16_fused_kernel(const SplitJob j0,
 // int32 matrix [rows][cols] -> byte planes [rows][pitch] (cols % 4 == 0, 16-byte aligned source).
 // WHAT = 0: the four bytes of each element (plane 3 holds the signed top byte);
 // WHAT = 1: the two bytes of (element >> 16), i.e. planes 0 / 1 = bytes 2 / 3 of the element;
-// WHAT = 2: those two, then planes 2 / 3 = bytes 0 / 1 (the high half first, then the low half);
-// WHAT = 3: as 2, and (element & 0xffff) * 2^-16 as binary32 into low_scaled[rows][low_pitch].
+// WHAT = 2: those two, then planes 2 / 3 = bytes 0 / 1 (the high half first, then the low half).
 template <int WHAT>
 __global__ void split_i32_bytes_kernel(const int4* __restrict__ src, uint8_t* __restrict__ p0,
                                        uint8_t* __restrict__ p1, uint8_t* __restrict__ p2,
-                                       uint8_t* __restrict__ p3, int64_t rows, int64_t cols4, int64_t pitch,
-                                       float* __restrict__ low_scaled, int64_t low_pitch) {
+                                       uint8_t* __restrict__ p3, int64_t rows, int64_t cols4, int64_t pitch) {
     const int64_t total = rows * cols4;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
@@ -299,26 +297,23 @@ __global__ void split_i32_bytes_kernel(const int4* __restrict__ src, uint8_t* __
         } else {
             *reinterpret_cast<uint32_t*>(p0 + o) = b2;
             *reinterpret_cast<uint32_t*>(p1 + o) = b3;
-            if (WHAT >= 2) {
+            if (WHAT == 2) {
                 *reinterpret_cast<uint32_t*>(p2 + o) = b0;
                 *reinterpret_cast<uint32_t*>(p3 + o) = b1;
             }
-            if (WHAT == 3)
-                *reinterpret_cast<float4*>(low_scaled + r * low_pitch + c) =
-                    make_float4(q16_low_half_scaled_f32(v.x), q16_low_half_scaled_f32(v.y),
-                                q16_low_half_scaled_f32(v.z), q16_low_half_scaled_f32(v.w));
         }
     }
 }
 
-// a[m][k] -> four byte planes [m][kp] and (a & 0xffff) as binary32, transposed to [k][mp]: tiles of
-// 64 rows by 64 of K, the transposition through shared memory so that both sides move whole lines.
-__global__ void __launch_bounds__(256)
-split_q16_a_kernel(const int32_t* __restrict__ a, uint8_t* __restrict__ p0, uint8_t* __restrict__ p1,
-                   uint8_t* __restrict__ p2, uint8_t* __restrict__ p3, float* __restrict__ a_low_t, int m, int k,
-                   int64_t kp, int64_t mp) {
-    __shared__ float ft[64][65];
-    const int r0 = blockIdx.y * 64, k0 = blockIdx.x * 64, tid = threadIdx.x;
+// a[m][k] -> four byte planes [m][kp] and (a & 0xffff) as binary32, transposed to [k][mp]: one tile
+// of 64 rows by 64 of K per call (256 threads), the transposition through shared memory so that
+// both sides move whole lines.
+__device__ __forceinline__ void split_q16_a_tile(float (&ft)[64][65], int tile_k, int tile_r,
+                                                 const int32_t* __restrict__ a, uint8_t* __restrict__ p0,
+                                                 uint8_t* __restrict__ p1, uint8_t* __restrict__ p2,
+                                                 uint8_t* __restrict__ p3, float* __restrict__ a_low_t, int m, int k,
+                                                 int64_t kp, int64_t mp) {
+    const int r0 = tile_r * 64, k0 = tile_k * 64, tid = threadIdx.x;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int r = (tid >> 4) + 16 * i, kq = (tid & 15) * 4;
@@ -349,21 +344,93 @@ split_q16_a_kernel(const int32_t* __restrict__ a, uint8_t* __restrict__ p0, uint
     }
 }
 
+// Everything the fused Q16.16 kernel reads, in one launch: blocks [0, a_blocks) split A (above),
+// blocks [a_blocks, a_blocks + b_blocks) split B into its four byte planes and (b & 0xffff) * 2^-16
+// as binary32, the remaining blocks (if any) zero C for a product whose tiles are shared between
+// CTAs.  The kernel after this one may start while it runs (its set-up touches no global
+// memory; it waits for this grid before it reads or writes anything).
+struct SplitQ16Job {
+    const int32_t *a, *b;
+    uint8_t *ap[4], *bp[4];
+    float *a_low_t, *b_low;
+    int32_t* c_zero;  // nullptr: C is not touched
+    int m, k, n;
+    int64_t kp, np, mp;
+    int a_tiles_k, a_blocks, b_blocks;
+};
+
+__global__ void __launch_bounds__(256) split_q16_ab_kernel(const SplitQ16Job job) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    __shared__ float ft[64][65];
+    const int blk = blockIdx.x;
+    if (blk < job.a_blocks) {
+        split_q16_a_tile(ft, blk % job.a_tiles_k, blk / job.a_tiles_k, job.a, job.ap[0], job.ap[1], job.ap[2],
+                         job.ap[3], job.a_low_t, job.m, job.k, job.kp, job.mp);
+    } else if (blk < job.a_blocks + job.b_blocks) {
+        const int64_t cols4 = job.n / 4, total = (int64_t)job.k * cols4;
+        const int4* src = reinterpret_cast<const int4*>(job.b);
+        for (int64_t i = (int64_t)(blk - job.a_blocks) * 256 + threadIdx.x; i < total; i += (int64_t)job.b_blocks * 256) {
+            const int64_t r = i / cols4, c = (i - r * cols4) * 4;
+            const int4 v = src[i];
+            const uint32_t lo01 = __byte_perm(v.x, v.y, 0x5140), lo23 = __byte_perm(v.z, v.w, 0x5140);
+            const uint32_t hi01 = __byte_perm(v.x, v.y, 0x7362), hi23 = __byte_perm(v.z, v.w, 0x7362);
+            const int64_t o = r * job.np + c;
+            *reinterpret_cast<uint32_t*>(job.bp[0] + o) = __byte_perm(hi01, hi23, 0x5410);  // bytes of b >> 16
+            *reinterpret_cast<uint32_t*>(job.bp[1] + o) = __byte_perm(hi01, hi23, 0x7632);
+            *reinterpret_cast<uint32_t*>(job.bp[2] + o) = __byte_perm(lo01, lo23, 0x5410);  // bytes of b & 0xffff
+            *reinterpret_cast<uint32_t*>(job.bp[3] + o) = __byte_perm(lo01, lo23, 0x7632);
+            *reinterpret_cast<float4*>(job.b_low + o) =
+                make_float4(q16_low_half_scaled_f32(v.x), q16_low_half_scaled_f32(v.y), q16_low_half_scaled_f32(v.z),
+                            q16_low_half_scaled_f32(v.w));
+        }
+    } else {
+        const int z_blocks = gridDim.x - job.a_blocks - job.b_blocks;
+        const int64_t total = (int64_t)job.m * job.n / 4;  // n % 4 == 0 and C 16-byte aligned (the fused kernel's own rule)
+        int4* dst = reinterpret_cast<int4*>(job.c_zero);
+        for (int64_t i = (int64_t)(blk - job.a_blocks - job.b_blocks) * 256 + threadIdx.x; i < total;
+             i += (int64_t)z_blocks * 256)
+            dst[i] = make_int4(0, 0, 0, 0);
+    }
+}
+
 }  // namespace
 
-int64_t launch_split_q16_a(DeviceCtx* ctx, const int32_t* a, uint8_t* const planes[4], float* a_low_t, int64_t m,
-                           int64_t k, int64_t kp, int64_t mp) {
-    if (m <= 0 || k <= 0) return 0;
-    dim3 grid((unsigned)((k + 63) / 64), (unsigned)((m + 63) / 64));
-    if (grid.y > 65535) return fail(MIND_B200_ERR_TOO_LARGE, "too many rows for the Q16.16 operand split");
-    split_q16_a_kernel<<<grid, 256, 0, ctx->stream>>>(a, planes[0], planes[1], planes[2], planes[3], a_low_t, (int)m,
-                                                      (int)k, kp, mp);
+// See split_q16_ab_kernel.  b_low has B's plane pitch np (in elements); zero_c: also clear c[m][n].
+int64_t launch_split_q16_ab(DeviceCtx* ctx, const int32_t* a, const int32_t* b, uint8_t* const ap[4],
+                            uint8_t* const bp[4], float* a_low_t, float* b_low, int32_t* c, bool zero_c, int64_t m,
+                            int64_t k, int64_t n, int64_t kp, int64_t np, int64_t mp) {
+    if (m <= 0 || k <= 0 || n <= 0) return 0;
+    SplitQ16Job job;
+    job.a = a;
+    job.b = b;
+    for (int i = 0; i < 4; ++i) {
+        job.ap[i] = ap[i];
+        job.bp[i] = bp[i];
+    }
+    job.a_low_t = a_low_t;
+    job.b_low = b_low;
+    job.c_zero = zero_c ? c : nullptr;
+    job.m = (int)m;
+    job.k = (int)k;
+    job.n = (int)n;
+    job.kp = kp;
+    job.np = np;
+    job.mp = mp;
+    const int64_t a_blocks = ((k + 63) / 64) * ((m + 63) / 64);
+    int64_t b_blocks = (k * (n / 4) + 1023) / 1024, z_blocks = zero_c ? (m * n / 4 + 2047) / 2048 : 0;
+    if (b_blocks > ctx->sm_count * 16) b_blocks = ctx->sm_count * 16;
+    if (z_blocks > ctx->sm_count * 8) z_blocks = ctx->sm_count * 8;
+    if (a_blocks + b_blocks + z_blocks > 0x7fffffff) return fail(MIND_B200_ERR_TOO_LARGE, "operand split grid too large");
+    job.a_tiles_k = (int)((k + 63) / 64);
+    job.a_blocks = (int)a_blocks;
+    job.b_blocks = (int)b_blocks;
+    split_q16_ab_kernel<<<(unsigned)(a_blocks + b_blocks + z_blocks), 256, 0, ctx->stream>>>(job);
     count_launch();
-    return check_launch("split_q16_a_kernel");
+    return check_launch("split_q16_ab_kernel");
 }
 
 int64_t launch_split_i32_bytes(DeviceCtx* ctx, const int32_t* src, uint8_t* const planes[4], int what,
-                               int64_t rows, int64_t cols, int64_t pitch, float* low_scaled, int64_t low_pitch) {
+                               int64_t rows, int64_t cols, int64_t pitch) {
     const int64_t total = rows * (cols / 4);
     if (total <= 0) return 0;
     int64_t blocks = (total + 255) / 256;
@@ -371,17 +438,13 @@ int64_t launch_split_i32_bytes(DeviceCtx* ctx, const int32_t* src, uint8_t* cons
     const int4* s4 = reinterpret_cast<const int4*>(src);
     if (what == 0)
         split_i32_bytes_kernel<0><<<(unsigned)blocks, 256, 0, ctx->stream>>>(s4, planes[0], planes[1], planes[2],
-                                                                             planes[3], rows, cols / 4, pitch, nullptr, 0);
+                                                                             planes[3], rows, cols / 4, pitch);
     else if (what == 2)
         split_i32_bytes_kernel<2><<<(unsigned)blocks, 256, 0, ctx->stream>>>(s4, planes[0], planes[1], planes[2],
-                                                                             planes[3], rows, cols / 4, pitch, nullptr, 0);
-    else if (what == 3)
-        split_i32_bytes_kernel<3><<<(unsigned)blocks, 256, 0, ctx->stream>>>(s4, planes[0], planes[1], planes[2],
-                                                                             planes[3], rows, cols / 4, pitch, low_scaled,
-                                                                             low_pitch);
+                                                                             planes[3], rows, cols / 4, pitch);
     else
         split_i32_bytes_kernel<1><<<(unsigned)blocks, 256, 0, ctx->stream>>>(s4, planes[0], planes[1], nullptr,
-                                                                             nullptr, rows, cols / 4, pitch, nullptr, 0);
+                                                                             nullptr, rows, cols / 4, pitch);
     count_launch();
     return check_launch("split_i32_bytes_kernel");
 }
