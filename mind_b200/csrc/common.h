@@ -188,6 +188,9 @@ EncodeTiledFn encode_tiled_fn();
 // or 64, = the swizzle width) along k by box_rows rows.  Cached per thread (gemm_tc.cu).
 int64_t make_tmap_u8(CUtensorMap* tm, const void* base, int64_t k, int64_t rows, int64_t pitch, int box_rows,
                      int box_bytes);
+// Tensor map over the int32 output c[m][n] (16-byte aligned, n % 4 == 0): boxes of 32 x 32 elements in
+// the 128-byte swizzle, for tensor stores / reductions from shared memory.
+int64_t make_tmap_c32(CUtensorMap* tm, int32_t* c, int64_t n, int64_t m);
 
 // ---- kernels' host launchers (device pointers only, asynchronous on ctx->stream) ----
 // int8 GEMM on tensor cores: C[M,N] (i32) = A[M,K] . Bt[N,K]^T, both operands

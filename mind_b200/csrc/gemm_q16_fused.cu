@@ -15,7 +15,8 @@
 //   warps 0..7  compute: the 8 x 8 register tile of gemm_q16_f32.cu per thread, operands from
 //               shared-memory stages filled by TMA from pre-converted binary32 planes
 //               (al transposed to [K][M], bl * 2^-16 as [K][N]); at the end of a run they drain
-//               the four TMEM accumulators into a shared tile, add their own sums and store.
+//               the four TMEM accumulators into a shared tile, add their own sums in place, and
+//               the tile leaves as sixteen tensor stores (or tensor reductions, see below).
 //   warp 8      lane 0 feeds the FP32 stages (TMA, three stages of 16 of K).
 //   warp 9      lane 0 feeds and drives the tensor cores: one shared-memory stage of six byte
 //               planes (a0..a3, two of b); per 128 of K a first pass with the planes of b >> 16
@@ -24,8 +25,10 @@
 //   warps 10, 11  idle (a warpgroup is four warps).
 //
 // Work is dealt out stream-K fashion in units of 32 of K of one tile, block b takes units
-// [b U / G, (b + 1) U / G); a run that covers its tile's whole K stores its outputs, the others
-// add with red.global.add onto a zeroed C (sums mod 2^32 commute).
+// [b U / G, (b + 1) U / G); a run that covers its tile's whole K stores its tile, the others add
+// theirs onto a zeroed C with cp.reduce.async.bulk.tensor (.add, performed in L2; sums mod 2^32
+// commute).  Per-element red.global.add from the register tiles cost a third of the kernel's
+// time at 1024^3 (two runs per CTA, 16 384 scattered 4-byte reductions each).
 //
 // Every wait is an mbarrier wait bounded in time; when one runs out the CTA's roles leave their
 // loops, the error word is set and the kernel ends normally.
@@ -47,8 +50,9 @@ constexpr int PLANE_BYTES = UT * TCB_K;      // one byte plane of a stage
 constexpr int TC_STAGE_BYTES = 6 * PLANE_BYTES;
 constexpr int F_HALF_BYTES = FSTEP * UT * 4;  // A or B part of an FP32 stage
 constexpr int F_STAGE_BYTES = 2 * F_HALF_BYTES;
-constexpr int T_PITCH = UT + 4;              // words; rows 16-byte aligned, lanes 4 banks apart
-constexpr int T_BYTES = UT * T_PITCH * 4;
+constexpr int T_BOX = 32;                    // the output tile is kept as 4 x 4 boxes of 32 x 32 words,
+constexpr int T_BOX_BYTES = T_BOX * T_BOX * 4;  // each 32 rows of 128 bytes in the 128-byte swizzle (what a tensor store reads)
+constexpr int T_BYTES = (UT / T_BOX) * (UT / T_BOX) * T_BOX_BYTES;
 constexpr int FUSED_THREADS = 384;
 constexpr int COMPUTE_WARPS = 8;
 constexpr int FUSED_SMEM = 1024 + TC_STAGE_BYTES + FSTAGES * F_STAGE_BYTES + T_BYTES + 256;
@@ -93,7 +97,7 @@ gemm_q16_fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_co
                       const __grid_constant__ CUtensorMap tm_bh0, const __grid_constant__ CUtensorMap tm_bh1,
                       const __grid_constant__ CUtensorMap tm_bl0, const __grid_constant__ CUtensorMap tm_bl1,
                       const __grid_constant__ CUtensorMap tm_af, const __grid_constant__ CUtensorMap tm_bf,
-                      const FusedParams p) {
+                      const __grid_constant__ CUtensorMap tm_c, const FusedParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t tc0 = (raw + 1023u) & ~1023u;            // six byte planes, 1024-byte aligned (swizzled)
@@ -103,11 +107,10 @@ gemm_q16_fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_co
     const uint32_t tc_full = bars, tc_empty = bars + 8;
     const uint32_t f_full0 = bars + 16, f_empty0 = f_full0 + 8 * FSTAGES;
     const uint32_t tmem_full = f_empty0 + 8 * FSTAGES, tmem_empty = tmem_full + 8;
-    const uint32_t t_ready = tmem_empty + 8, t_free = t_ready + 8;
-    const uint32_t tmem_slot = t_free + 8;
+    const uint32_t t_ready = tmem_empty + 8, t_free = t_ready + 8, t_done = t_free + 8;
+    const uint32_t tmem_slot = t_done + 8;
     int* const misc = reinterpret_cast<int*>(smem_raw + (tmem_slot - raw));
     volatile int* const abort_s = misc + 1;
-    const uint32_t* const t_tile = reinterpret_cast<const uint32_t*>(smem_raw + (t0 - raw));
     const float* const f_tile = reinterpret_cast<const float*>(smem_raw + (f0 - raw));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -123,11 +126,12 @@ gemm_q16_fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_co
         mbar_init(tmem_empty, COMPUTE_WARPS);
         mbar_init(t_ready, COMPUTE_WARPS);
         mbar_init(t_free, COMPUTE_WARPS);
+        mbar_init(t_done, COMPUTE_WARPS);
         misc[1] = 0;
         fence_mbar_init();
         prefetch_tensormap(&tm_a0); prefetch_tensormap(&tm_a1); prefetch_tensormap(&tm_a2); prefetch_tensormap(&tm_a3);
         prefetch_tensormap(&tm_bh0); prefetch_tensormap(&tm_bh1); prefetch_tensormap(&tm_bl0); prefetch_tensormap(&tm_bl1);
-        prefetch_tensormap(&tm_af); prefetch_tensormap(&tm_bf);
+        prefetch_tensormap(&tm_af); prefetch_tensormap(&tm_bf); prefetch_tensormap(&tm_c);
     }
     if (warp == 9) {
         tmem_alloc<1>(tmem_slot, 512);
@@ -349,16 +353,24 @@ gemm_q16_fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_co
             if (!ok) break;
             empty_chains();
 
-            // The accumulators of this run: wait for the last MMA, drain this warp's 32 rows x 64
-            // columns of the four of them into the shared tile as s0 + (s1 << 8) + (s2 << 16) +
-            // (s3 << 24) (lane = row), free TMEM for the next run, and when all eight warps have
-            // written, every thread picks up its own 8 x 8 outputs from the tile.
+            // The accumulators of this run.  The output tile lives in shared memory as 4 x 4 boxes of
+            // 32 x 32 words, each in the layout a tensor store reads (32 rows of 128 bytes, 16-byte
+            // chunk j of row l at position j ^ (l & 7)).  (1) Lane 0 makes sure its tensor stores of
+            // the previous run have read the tile, and all eight warps meet (t_free).  (2) After the
+            // last MMA each warp drains its 32 rows x 64 columns of the four accumulators into the
+            // tile as s0 + (s1 << 8) + (s2 << 16) + (s3 << 24) (lane = row) and frees TMEM for the
+            // next run.  (3) When all have written, every thread adds its own 8 x 8 floor sums in
+            // place.  (4) When all have done that, lane 0 of warp w sends boxes 2 w and 2 w + 1: a
+            // tensor store if this run covers the tile's whole K, a tensor reduction (add) otherwise.
+            if (lane == 0) {
+                bulk_wait_group_read<0>();
+                mbar_arrive(t_free);
+            }
             if (!wait_bounded(tmem_full, rc & 1u, abort_s, p.err, 16)) break;
             tc_fence_after();
-            if (!wait_bounded(t_free, (rc & 1u) ^ 1u, abort_s, p.err, 17)) break;  // the tile's last readers
+            if (!wait_bounded(t_free, rc & 1u, abort_s, p.err, 17)) break;
             {
                 const uint32_t tsrc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 64);
-                const uint32_t trow = t0 + (uint32_t)((q * 32 + lane) * T_PITCH + half * 64) * 4u;
 #pragma unroll
                 for (int c0 = 0; c0 < 64; c0 += 16) {
                     uint32_t s0[16], s1[16], s2[16], s3[16];
@@ -367,13 +379,15 @@ gemm_q16_fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_co
                     tmem_ld16(tsrc + 2 * UT + c0, s2);
                     tmem_ld16(tsrc + 3 * UT + c0, s3);
                     tmem_ld_wait();
+                    // box (q, 2 half + c0 / 32), chunks (c0 % 32) / 4 .. + 3 of row `lane`
+                    const uint32_t brow = t0 + (uint32_t)((q * 4 + 2 * half + c0 / 32) * T_BOX_BYTES + lane * 128);
 #pragma unroll
                     for (int j = 0; j < 16; j += 4) {
                         uint32_t v[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e)
                             v[e] = s0[j + e] + (s1[j + e] << 8) + (s2[j + e] << 16) + (s3[j + e] << 24);
-                        st_shared_v4(trow + (uint32_t)(c0 + j) * 4u, v[0], v[1], v[2], v[3]);
+                        st_shared_v4(brow + (uint32_t)((((c0 % 32) + j) / 4) ^ (lane & 7)) * 16u, v[0], v[1], v[2], v[3]);
                     }
                 }
             }
@@ -386,36 +400,50 @@ gemm_q16_fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_co
             }
             const uint32_t written = wait_bounded_dep(t_ready, rc & 1u, abort_s, p.err, 18, p.one);
             if (!written) break;
-            const uint32_t* const t_rd = t_tile + (written - p.one);  // reads below depend on the wait
+            const uint32_t t_rd = t0 + (written - p.one);  // the accesses below depend on the wait
 
-            const bool owns = r.ku0 == 0 && r.ku1 == p.k_units;
             const uint32_t bias = emptied * TWO23_BITS;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const int rl = (i / 4) * 64 + ty * 4 + (i % 4), rg = row0 + rl;
+                const int rl = (i / 4) * 64 + ty * 4 + (i % 4);
 #pragma unroll
                 for (int g = 0; g < 2; ++g) {
-                    const int cl = g * 64 + tx * 4, cg = col0 + cl;
-                    const uint4 lin = *reinterpret_cast<const uint4*>(t_rd + rl * T_PITCH + cl);
-                    const uint32_t o0 = sum[i][4 * g] - bias + lin.x, o1 = sum[i][4 * g + 1] - bias + lin.y,
-                                   o2 = sum[i][4 * g + 2] - bias + lin.z, o3 = sum[i][4 * g + 3] - bias + lin.w;
-                    if (rg >= p.m || cg >= p.n) continue;  // (n % 4 == 0: a group of four is inside or outside)
-                    unsigned int* dst = reinterpret_cast<unsigned int*>(p.c) + (size_t)rg * p.n + cg;
-                    if (owns) {
-                        *reinterpret_cast<uint4*>(dst) = make_uint4(o0, o1, o2, o3);
-                    } else {
-                        atomicAdd(dst, o0); atomicAdd(dst + 1, o1); atomicAdd(dst + 2, o2); atomicAdd(dst + 3, o3);
-                    }
+                    const int cl = g * 64 + tx * 4;
+                    const uint32_t at = t_rd + (uint32_t)(((rl / T_BOX) * 4 + cl / T_BOX) * T_BOX_BYTES + (rl % T_BOX) * 128 +
+                                                          ((((cl % T_BOX) / 4) ^ (rl & 7)) << 4));
+                    const uint4 lin = ld_shared_v4(at);
+                    st_shared_v4(at, sum[i][4 * g] - bias + lin.x, sum[i][4 * g + 1] - bias + lin.y,
+                                 sum[i][4 * g + 2] - bias + lin.z, sum[i][4 * g + 3] - bias + lin.w);
                 }
             }
-            __threadfence_block();  // the reads of the tile above are done before it is handed back
+            fence_proxy_async_smem();  // these writes are read by the tensor stores below (another proxy)
             __syncwarp();
-            if (lane == 0) mbar_arrive(t_free);
+            if (lane == 0) {
+                mbar_arrive(t_done);
+                if (!wait_bounded(t_done, rc & 1u, abort_s, p.err, 19)) {
+                    ok = false;
+                } else {
+                    const bool owns = r.ku0 == 0 && r.ku1 == p.k_units;
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int box = 2 * warp + e, y = row0 + (box / 4) * T_BOX, x = col0 + (box % 4) * T_BOX;
+                        if (y >= p.m || x >= p.n) continue;  // (a box partly outside is clipped by the hardware)
+                        if (owns)
+                            tma_store_2d(&tm_c, t0 + (uint32_t)box * T_BOX_BYTES, x, y);
+                        else
+                            tma_reduce_add_2d(&tm_c, t0 + (uint32_t)box * T_BOX_BYTES, x, y);
+                    }
+                    bulk_commit_group();
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
             ++rc;
         }
     }
 
     // ------------------------------------------------------------------ teardown
+    if (warp < COMPUTE_WARPS && lane == 0) bulk_wait_group<0>();  // this warp's tensor stores have landed
     __syncwarp();
     if (*abort_s) __nanosleep(200000);  // let copies / MMAs still in flight land before freeing
     tc_fence_before();
@@ -486,6 +514,8 @@ int64_t launch_gemm_q16_fused(DeviceCtx* ctx, const uint8_t* const a_limb[4], co
     for (int i = 0; i < 4; ++i) MB200_TRY(make_tmap_u8(&tb[i], b_limb[i], n, k, pitch_b, TCB_K, 128));
     MB200_TRY(make_tmap_f32(&taf, a_low_t, m, k, mp * 4));
     MB200_TRY(make_tmap_f32(&tbf, b_low, n, k, np * 4));
+    CUtensorMap tc;
+    MB200_TRY(make_tmap_c32(&tc, c, n, m));
     const int64_t m_tiles = (m + UT - 1) / UT, n_tiles = (n + UT - 1) / UT;
     if (m_tiles * n_tiles > 0x7fffffff) return fail(MIND_B200_ERR_TOO_LARGE, "too many output tiles");
     FusedParams p;
@@ -514,7 +544,7 @@ int64_t launch_gemm_q16_fused(DeviceCtx* ctx, const uint8_t* const a_limb[4], co
     lc.numAttrs = 1;
     prof_begin(ctx);
     MB200_CUDA(cudaLaunchKernelEx(&lc, gemm_q16_fused_kernel, ta[0], ta[1], ta[2], ta[3], tb[0], tb[1], tb[2], tb[3], taf,
-                                  tbf, p));
+                                  tbf, tc, p));
     prof_end(ctx);
     count_launch();
     return check_launch("gemm_q16_fused_kernel");

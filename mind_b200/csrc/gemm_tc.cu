@@ -809,6 +809,8 @@ int64_t launch_tc(DeviceCtx* ctx, const void* a0, const void* a1, const void* b0
 
 }  // namespace
 
+int64_t make_tmap_c32(CUtensorMap* tm, int32_t* c, int64_t n, int64_t m) { return make_tmap_c(tm, c, n, m); }
+
 int64_t make_tmap_u8(CUtensorMap* tm, const void* base, int64_t k, int64_t rows, int64_t pitch, int box_rows,
                      int box_bytes) {
     return make_tmap(tm, base, k, rows, pitch, box_rows, box_bytes);

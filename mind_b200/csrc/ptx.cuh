@@ -178,6 +178,14 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int
                  "r"(src), "r"(x), "r"(y)
                  : "memory");
 }
+// The same, adding the tile onto what global memory holds (element type from the tensor map;
+// the additions are performed in L2, atomically per element).
+__device__ __forceinline__ void tma_reduce_add_2d(const void* tmap, uint32_t src, int32_t x, int32_t y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Until at most N of this thread's bulk groups still have to READ their shared-memory source.
 template <int N>
@@ -192,6 +200,11 @@ __device__ __forceinline__ void bulk_wait_group() {
 // Makes this thread's earlier shared-memory writes visible to the TMA engine (async proxy).
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
 }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
