@@ -182,7 +182,7 @@ int64_t mind_b200_shutdown(void);
  * transposed into scratch first (otherwise B is read in place whenever its pitch and base are
  * 16-byte aligned); 1 = the independent CUDA-core kernels kept as an on-device cross-check
  * (for Q16.16: the all-integer kernel); 6 / 7 = Q16.16 GEMM only: the FP64-pipe kernel alone /
- * the tensor-core hybrid at every size (default: hybrid from 2^29 products up, i.e. about 800^3).
+ * the tensor-core hybrid at every size (default: hybrid from 2^25 products up, i.e. about 320^3).
  * The hybrid is ONE kernel that forms the limb products on the tensor cores and the per-product
  * floor term on the FP32 pipe of the same SM; 8 / 9 = the hybrid as two kernels instead, one
  * after the other / side by side on two streams, both adding onto C;

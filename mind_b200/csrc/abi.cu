@@ -592,7 +592,9 @@ int64_t gemm_q16_local(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, in
         const size_t a_plane = align_up((size_t)m * kp, 1024), b_plane = align_up((size_t)k * np, 1024);
         const int64_t mp = (int64_t)align_up((size_t)m, 4);
         const size_t a_low_bytes = align_up((size_t)k * mp * 4, 1024), b_low_bytes = align_up((size_t)k * np * 4, 1024);
-        const bool big = (double)m * (double)n * (double)k >= 536870912.0;  // measured cross-over: 768^3 .. 1024^3
+        // measured cross-over of the single FP64-pipe kernel and the fused kernel (warm, back to back):
+        // level at 256^3 (13 us both), 19.5 / 14.0 us at 384^3, 29.8 / 18.5 at 512^3, 74.8 / 32.8 at 768^3
+        const bool big = (double)m * (double)n * (double)k >= 33554432.0;
         const bool may_hybrid = g_gemm_path != 1 && k % 4 == 0 && n % 4 == 0 &&
                                 (g_q16_mode == 7 || (g_q16_mode == 0 && big));
         MB200_TRY(arena_reserve(ctx, ctx->scratch, (b_transposed ? align_up((size_t)k * n * 4, 1024) : 0) +
