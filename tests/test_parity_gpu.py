@@ -255,6 +255,16 @@ def test_q16_f32_chain_holds_128_full_terms(gpu, path):
             c = np.empty(m * n, dtype=np.int32)
             gpu.matmul_mm_q16_v(a, b, c, m, k, n)
             assert np.array_equal(c, O.gemm_q16(a, b, m, k, n)), (aval, bval)
+        # a very long K on a single small tile: every CTA of the fused kernel adds its share of the
+        # same outputs (tensor reductions), and the chains are emptied 8000 times per output
+        m, n, k = 8, 4, (1 << 20) + 48
+        a = np.full(m * k, -1, dtype=np.int32)
+        a[:: 7] = 0x7FFFFFFF
+        b = np.full(k * n, 0xFFFF, dtype=np.int32)
+        b[:: 5] = -1
+        c = np.empty(m * n, dtype=np.int32)
+        gpu.matmul_mm_q16_v(a, b, c, m, k, n)
+        assert np.array_equal(c, O.gemm_q16(a, b, m, k, n))
     finally:
         gpu.set_gemm_path(0)
 
