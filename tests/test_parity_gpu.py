@@ -198,6 +198,31 @@ def test_random_shapes_all_kernels(gpu):
         assert np.array_equal(y, O.gemv_q16(a, b[:k], m, k)), ("gemv", m, k)
 
 
+def test_random_shapes_fused_q16(gpu):
+    """Seeded random shapes through the fused Q16.16 kernel (forced at every size): K and N multiples
+    of 4 as the tensor-core forms need, M anything, tiles ragged on every side, one to several
+    hundred stream-K units per CTA, full-range operands, against the CPU oracle."""
+    rng = np.random.default_rng(20260202)
+    gpu.set_gemm_path(7)
+    try:
+        for t in range(14):
+            m = int(rng.integers(1, 700))
+            k = int(rng.integers(1, 200)) * 4
+            n = int(rng.integers(1, 180)) * 4
+            if t == 0:
+                m, k, n = 129, 36, 132          # a unit and a bit, two tiles and a bit
+            if t == 1:
+                m, k, n = 1, 4, 4
+            g = O.Lcg(int(rng.integers(1, 2**62)))
+            a, b = g.q16(m * k, 0), g.q16(k * n, 0)
+            c = np.full(m * n + 8, 0x5A5A5A5A, dtype=np.int32)
+            gpu.matmul_mm_q16_v(a, b, c, m, k, n)
+            assert np.array_equal(c[: m * n], O.gemm_q16(a, b, m, k, n)), (m, k, n)
+            assert np.all(c[m * n :] == 0x5A5A5A5A)
+    finally:
+        gpu.set_gemm_path(0)
+
+
 def test_q16_extreme_values(gpu):
     """INT_MIN / INT_MAX / -1 / 0x7FFF8000...: the hi/lo split must be exact everywhere."""
     specials = np.array([-2**31, 2**31 - 1, -1, 0, 1, 0x7FFF8000, 0x7FFF7FFF, -0x8000, 0x8000,
