@@ -68,8 +68,7 @@ __device__ __forceinline__ uint64_t fma2_rm(uint64_t a, uint64_t b, uint64_t c) 
 }
 
 struct FusedParams {
-    int32_t* c;
-    int m, n, k;
+    int m, n;           // extents of C (the tensor maps carry the rest)
     int n_tiles;
     int k_units;        // ceil(k / 32)
     long long units;    // tiles * k_units
@@ -519,10 +518,8 @@ int64_t launch_gemm_q16_fused(DeviceCtx* ctx, const uint8_t* const a_limb[4], co
     const int64_t m_tiles = (m + UT - 1) / UT, n_tiles = (n + UT - 1) / UT;
     if (m_tiles * n_tiles > 0x7fffffff) return fail(MIND_B200_ERR_TOO_LARGE, "too many output tiles");
     FusedParams p;
-    p.c = c;
     p.m = (int)m;
     p.n = (int)n;
-    p.k = (int)k;
     p.n_tiles = (int)n_tiles;
     p.k_units = (int)((k + UNIT_K - 1) / UNIT_K);
     p.units = m_tiles * n_tiles * p.k_units;
