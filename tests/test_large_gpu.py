@@ -424,6 +424,8 @@ def test_cuda_graph_capture_and_replay(gpu):
     cases = [("i8", 0, lambda c: gpu.matmul_mm_i8_v(a8, b8, c, n, n, n)),
              ("i16", 0, lambda c: gpu.matmul_mm_i16(a16, b16, c, n, n, n)),
              ("q16 one kernel", 6, lambda c: gpu.matmul_mm_q16_v(aq, bq, c, n, n, n)),
+             ("q16 fused kernel (launched programmatically behind its operand split)", 7,
+              lambda c: gpu.matmul_mm_q16_v(aq, bq, c, n, n, n)),
              ("q16 hybrid in sequence", 8, lambda c: gpu.matmul_mm_q16_v(aq, bq, c, n, n, n)),
              ("q16 hybrid side by side", 9, lambda c: gpu.matmul_mm_q16_v(aq, bq, c, n, n, n)),
              ("gemv", 0, lambda c: gpu.gemv_q16_mt(aq, bq, c, n, n))]
