@@ -17,7 +17,9 @@
 //               (al transposed to [K][M], bl * 2^-16 as [K][N]); at the end of a run they drain
 //               the four TMEM accumulators into a shared tile, add their own sums in place, and
 //               the tile leaves as sixteen tensor stores (or tensor reductions, see below).
-//   warp 8      lane 0 feeds the FP32 stages (TMA, three stages of 16 of K).
+//   warp 8      lane 0 feeds the FP32 stages (TMA; two stages of 32 of K: fewer, longer stages
+//               beat three of 16 by 4 % - a stage boundary is a vote, an arrive, a wait and a
+//               first shared-memory load that nothing hides).
 //   warp 9      lane 0 feeds and drives the tensor cores: one shared-memory stage of six byte
 //               planes (a0..a3, two of b); per 128 of K a first pass with the planes of b >> 16
 //               (seven MMAs per 32 of K) and a second with those of b & 0xffff (four, on a2 / a3).
@@ -43,8 +45,8 @@ namespace {
 constexpr int UT = 128;                      // output tile (rows and columns)
 constexpr int UNIT_K = 32;                   // stream-K granule = one MMA's K
 constexpr int TCB_K = 128;                   // K per tensor-core stage
-constexpr int FSTEP = 16;                    // K per FP32 stage
-constexpr int FSTAGES = 3;
+constexpr int FSTEP = 32;                    // K per FP32 stage
+constexpr int FSTAGES = 2;
 constexpr int FLUSH_FSTEPS = 128 / FSTEP;    // a chain holds 128 products
 constexpr int PLANE_BYTES = UT * TCB_K;      // one byte plane of a stage
 constexpr int TC_STAGE_BYTES = 6 * PLANE_BYTES;
@@ -331,14 +333,14 @@ gemm_q16_fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_co
                         for (int jp = 0; jp < 4; ++jp) chain[i][jp] = fma2_rm(a2[i], b2[jp], chain[i][jp]);
                 }
                 // Release the stage only once every lane's last fragments have been USED.  With a plain
-                // __syncwarp() before lane 0's arrive, the last A fragment of a stage (K step 15) was
-                // now and then read AFTER the producer had refilled the stage (it came back as the
-                // element 48 further on in K, three stages later), always in the warp that shares a
-                // scheduler with a producer warp, i.e. the one whose arrival is last and triggers the
-                // refill: one tile in thirty at 2048^3.  The vote below reads one chain per operand
-                // register of the last K step, and the arrive is predicated on its result, so neither a
-                // load of this stage nor an FMA waiting for one can follow the release in any
-                // instruction order.
+                // __syncwarp() before lane 0's arrive, the last A fragment of a stage (its last K step)
+                // was now and then read AFTER the producer had refilled the stage (with three stages of 16
+                // it came back as the element 48 further on in K: what the next fill puts there), always
+                // in the warp that shares a scheduler with a producer warp, i.e. the one whose arrival is
+                // last and triggers the refill: one tile in thirty at 2048^3.  The vote below reads one
+                // chain per operand register of the last K step, and the arrive is predicated on its
+                // result, so neither a load of this stage nor an FMA waiting for one can follow the
+                // release in any instruction order.
                 uint64_t used = chain[0][1] ^ chain[0][2] ^ chain[0][3];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) used ^= chain[i][0];
