@@ -595,10 +595,13 @@ int64_t gemm_q16_local(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, in
         // measured cross-over of the single FP64-pipe kernel and the fused kernel (warm, back to back):
         // level at 256^3 (13 us both), 19.5 / 14.0 us at 384^3, 29.8 / 18.5 at 512^3, 74.8 / 32.8 at 768^3
         const bool big = (double)m * (double)n * (double)k >= 33554432.0;
-        const bool may_hybrid = g_gemm_path != 1 && k % 4 == 0 && n % 4 == 0 &&
-                                (g_q16_mode == 7 || (g_q16_mode == 0 && big));
+        const bool hybrid_size = g_gemm_path != 1 && (g_q16_mode == 7 || (g_q16_mode == 0 && big));
+        // the two-kernel forms read the operands with 16-byte loads; the fused form takes any shape and base
+        const bool may_hybrid = hybrid_size && k % 4 == 0 && n % 4 == 0;
+        const bool may_fuse = hybrid_size && want_fused;
         MB200_TRY(arena_reserve(ctx, ctx->scratch, (b_transposed ? align_up((size_t)k * n * 4, 1024) : 0) +
-                                                       (may_hybrid ? 4 * a_plane + 4 * b_plane + (want_fused ? a_low_bytes + b_low_bytes : 0) : 0) + 16384));
+                                                       ((may_hybrid || may_fuse) ? 4 * a_plane + 4 * b_plane : 0) +
+                                                       (may_fuse ? a_low_bytes + b_low_bytes : 0) + 16384));
         if (b_transposed) {
             int32_t* bkn = static_cast<int32_t*>(arena_take(ctx->scratch, (size_t)k * n * 4));
             MB200_TRY(launch_transpose_i32(ctx, db, bkn, n, k));
@@ -616,15 +619,17 @@ int64_t gemm_q16_local(int64_t a, int64_t b, int64_t c, int64_t m, int64_t k, in
         const int32_t* da = call.dev<int32_t>(ia);
         int32_t* dc = call.dev<int32_t>(ic);
         const bool fp64_ok = g_gemm_path != 1 && gemm_q16_fp64_usable(da, db, k, n);
-        const bool hybrid = fp64_ok && may_hybrid && reinterpret_cast<uintptr_t>(dc) % 16 == 0;
+        const bool fuse = may_fuse && gemm_q16_fused_usable(ctx);
+        const bool hybrid = fuse || (fp64_ok && may_hybrid && reinterpret_cast<uintptr_t>(dc) % 16 == 0);
         if (hybrid) {
             uint8_t* ap[4];
             uint8_t* bp[4] = {nullptr, nullptr, nullptr, nullptr};
             for (int i = 0; i < 4; ++i) ap[i] = static_cast<uint8_t*>(arena_take(ctx->scratch, a_plane));
             for (int i = 0; i < (floor_f32 ? 4 : 2); ++i) bp[i] = static_cast<uint8_t*>(arena_take(ctx->scratch, b_plane));
             // One kernel for both halves (gemm_q16_fused.cu) where it can run: the limb products
-            // hide behind the FMAs of the floor term on the same SM, and C is written once.
-            if (want_fused && gemm_q16_fused_usable(ctx)) {
+            // hide behind the FMAs of the floor term on the same SM, and C is written once.  Its
+            // operand split pads every plane, so ragged shapes and odd bases take this path too.
+            if (fuse) {
                 float* a_low_t = static_cast<float*>(arena_take(ctx->scratch, a_low_bytes));
                 float* b_low = static_cast<float*>(arena_take(ctx->scratch, b_low_bytes));
                 MB200_TRY(launch_split_q16_ab(ctx, da, db, ap, bp, a_low_t, b_low, dc,

@@ -70,6 +70,8 @@ __device__ __forceinline__ uint64_t fma2_rm(uint64_t a, uint64_t b, uint64_t c) 
 }
 
 struct FusedParams {
+    int32_t* c;         // used only when the tile cannot leave through the tensor map (tma_c == 0)
+    int tma_c;          // C is 16-byte aligned with N % 4 == 0: tensor stores / reductions
     int m, n;           // extents of C (the tensor maps carry the rest)
     int n_tiles;
     int k_units;        // ceil(k / 32)
@@ -418,12 +420,13 @@ gemm_q16_fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_co
                 }
             }
             fence_proxy_async_smem();  // these writes are read by the tensor stores below (another proxy)
+            __threadfence_block();
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(t_done);
                 if (!wait_bounded(t_done, rc & 1u, abort_s, p.err, 19)) {
                     ok = false;
-                } else {
+                } else if (p.tma_c) {
                     const bool owns = r.ku0 == 0 && r.ku1 == p.k_units;
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
@@ -439,6 +442,27 @@ gemm_q16_fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_co
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
+            if (!p.tma_c) {
+                // C with an odd pitch or base: the warp writes its two boxes itself, lane = column
+                // (a row of a box is 128 contiguous bytes of C), stores or red.global.add
+                const bool owns = r.ku0 == 0 && r.ku1 == p.k_units;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int box = 2 * warp + e, y = row0 + (box / 4) * T_BOX, x = col0 + (box % 4) * T_BOX + lane;
+                    if (y >= p.m || x >= p.n) continue;
+                    const uint32_t src = t0 + (uint32_t)box * T_BOX_BYTES + (uint32_t)(lane & 3) * 4u;
+                    unsigned int* dst = reinterpret_cast<unsigned int*>(p.c) + (size_t)y * p.n + x;
+                    for (int rr = 0; rr < T_BOX && y + rr < p.m; ++rr, dst += p.n) {
+                        uint32_t v;
+                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(src + (uint32_t)(rr * 128 + (((lane >> 2) ^ (rr & 7)) << 4))) : "memory");
+                        if (owns)
+                            *dst = v;
+                        else
+                            atomicAdd(dst, v);
+                    }
+                }
+                __threadfence_block();  // the tile has been read before it is handed back (t_free, next run)
+            }
             ++rc;
         }
     }
@@ -504,7 +528,7 @@ bool gemm_q16_fused_shares_tiles(DeviceCtx* ctx, int64_t m, int64_t n, int64_t k
 // c = the whole Q16.16 product.  a_limb[0..3]: byte planes of a ([m][kp_a], a_limb[3] signed);
 // b_limb[0..1]: bytes of b >> 16, b_limb[2..3]: bytes of b & 0xffff ([k][pitch_b]); a_low_t:
 // (a & 0xffff) as binary32, transposed, [k][mp]; b_low: (b & 0xffff) * 2^-16 as binary32, [k][np].
-// Needs n % 4 == 0 and c 16-byte aligned.
+// Any m, n, k and any 4-byte aligned c (the planes carry their own padded pitches).
 int64_t launch_gemm_q16_fused(DeviceCtx* ctx, const uint8_t* const a_limb[4], const uint8_t* const b_limb[4],
                               const float* a_low_t, const float* b_low, int32_t* c, int64_t m, int64_t n, int64_t k,
                               int64_t kp_a, int64_t pitch_b, int64_t mp, int64_t np) {
@@ -515,11 +539,15 @@ int64_t launch_gemm_q16_fused(DeviceCtx* ctx, const uint8_t* const a_limb[4], co
     for (int i = 0; i < 4; ++i) MB200_TRY(make_tmap_u8(&tb[i], b_limb[i], n, k, pitch_b, TCB_K, 128));
     MB200_TRY(make_tmap_f32(&taf, a_low_t, m, k, mp * 4));
     MB200_TRY(make_tmap_f32(&tbf, b_low, n, k, np * 4));
-    CUtensorMap tc;
-    MB200_TRY(make_tmap_c32(&tc, c, n, m));
+    // C through a tensor map where the hardware can address it (16-byte base and pitch)
+    const bool tma_c = n % 4 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0;
+    CUtensorMap tc = taf;
+    if (tma_c) MB200_TRY(make_tmap_c32(&tc, c, n, m));
     const int64_t m_tiles = (m + UT - 1) / UT, n_tiles = (n + UT - 1) / UT;
     if (m_tiles * n_tiles > 0x7fffffff) return fail(MIND_B200_ERR_TOO_LARGE, "too many output tiles");
     FusedParams p;
+    p.c = c;
+    p.tma_c = tma_c ? 1 : 0;
     p.m = (int)m;
     p.n = (int)n;
     p.n_tiles = (int)n_tiles;

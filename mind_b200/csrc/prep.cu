@@ -312,14 +312,25 @@ __device__ __forceinline__ void split_q16_a_tile(float (&ft)[64][65], int tile_k
                                                  const int32_t* __restrict__ a, uint8_t* __restrict__ p0,
                                                  uint8_t* __restrict__ p1, uint8_t* __restrict__ p2,
                                                  uint8_t* __restrict__ p3, float* __restrict__ a_low_t, int m, int k,
-                                                 int64_t kp, int64_t mp) {
+                                                 int64_t kp, int64_t mp, bool vec) {
     const int r0 = tile_r * 64, k0 = tile_k * 64, tid = threadIdx.x;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int r = (tid >> 4) + 16 * i, kq = (tid & 15) * 4;
         int4 v = make_int4(0, 0, 0, 0);
         const bool inside = r0 + r < m && k0 + kq < k;
-        if (inside) v = *reinterpret_cast<const int4*>(a + (size_t)(r0 + r) * k + k0 + kq);
+        if (inside) {
+            const int32_t* src = a + (size_t)(r0 + r) * k + k0 + kq;
+            if (vec) {  // K % 4 == 0 and a 16-byte aligned base
+                v = *reinterpret_cast<const int4*>(src);
+            } else {    // element by element; past the row's end the group is filled with zeros
+                const int left = k - (k0 + kq);
+                v.x = src[0];
+                if (left > 1) v.y = src[1];
+                if (left > 2) v.z = src[2];
+                if (left > 3) v.w = src[3];
+            }
+        }
         ft[kq][r] = q16_low_half_f32(v.x);
         ft[kq + 1][r] = q16_low_half_f32(v.y);
         ft[kq + 2][r] = q16_low_half_f32(v.z);
@@ -354,6 +365,7 @@ struct SplitQ16Job {
     uint8_t *ap[4], *bp[4];
     float *a_low_t, *b_low;
     int32_t* c_zero;  // nullptr: C is not touched
+    int vec_a, vec_b, vec_c;  // 16-byte accesses allowed on that operand (aligned base, row length a multiple of 4)
     int m, k, n;
     int64_t kp, np, mp;
     int a_tiles_k, a_blocks, b_blocks;
@@ -365,13 +377,22 @@ __global__ void __launch_bounds__(256) split_q16_ab_kernel(const SplitQ16Job job
     const int blk = blockIdx.x;
     if (blk < job.a_blocks) {
         split_q16_a_tile(ft, blk % job.a_tiles_k, blk / job.a_tiles_k, job.a, job.ap[0], job.ap[1], job.ap[2],
-                         job.ap[3], job.a_low_t, job.m, job.k, job.kp, job.mp);
+                         job.ap[3], job.a_low_t, job.m, job.k, job.kp, job.mp, job.vec_a != 0);
     } else if (blk < job.a_blocks + job.b_blocks) {
-        const int64_t cols4 = job.n / 4, total = (int64_t)job.k * cols4;
-        const int4* src = reinterpret_cast<const int4*>(job.b);
+        const int64_t cols4 = (job.n + 3) / 4, total = (int64_t)job.k * cols4;
         for (int64_t i = (int64_t)(blk - job.a_blocks) * 256 + threadIdx.x; i < total; i += (int64_t)job.b_blocks * 256) {
             const int64_t r = i / cols4, c = (i - r * cols4) * 4;
-            const int4 v = src[i];
+            const int32_t* src = job.b + r * job.n + c;
+            int4 v = make_int4(0, 0, 0, 0);
+            if (job.vec_b) {
+                v = *reinterpret_cast<const int4*>(src);
+            } else {
+                const int64_t left = job.n - c;
+                v.x = src[0];
+                if (left > 1) v.y = src[1];
+                if (left > 2) v.z = src[2];
+                if (left > 3) v.w = src[3];
+            }
             const uint32_t lo01 = __byte_perm(v.x, v.y, 0x5140), lo23 = __byte_perm(v.z, v.w, 0x5140);
             const uint32_t hi01 = __byte_perm(v.x, v.y, 0x7362), hi23 = __byte_perm(v.z, v.w, 0x7362);
             const int64_t o = r * job.np + c;
@@ -385,11 +406,13 @@ __global__ void __launch_bounds__(256) split_q16_ab_kernel(const SplitQ16Job job
         }
     } else {
         const int z_blocks = gridDim.x - job.a_blocks - job.b_blocks;
-        const int64_t total = (int64_t)job.m * job.n / 4;  // n % 4 == 0 and C 16-byte aligned (the fused kernel's own rule)
-        int4* dst = reinterpret_cast<int4*>(job.c_zero);
-        for (int64_t i = (int64_t)(blk - job.a_blocks - job.b_blocks) * 256 + threadIdx.x; i < total;
-             i += (int64_t)z_blocks * 256)
-            dst[i] = make_int4(0, 0, 0, 0);
+        const int64_t first = (int64_t)(blk - job.a_blocks - job.b_blocks) * 256 + threadIdx.x, step = (int64_t)z_blocks * 256;
+        if (job.vec_c) {
+            int4* dst = reinterpret_cast<int4*>(job.c_zero);
+            for (int64_t i = first; i < (int64_t)job.m * job.n / 4; i += step) dst[i] = make_int4(0, 0, 0, 0);
+        } else {
+            for (int64_t i = first; i < (int64_t)job.m * job.n; i += step) job.c_zero[i] = 0;
+        }
     }
 }
 
@@ -410,6 +433,9 @@ int64_t launch_split_q16_ab(DeviceCtx* ctx, const int32_t* a, const int32_t* b, 
     job.a_low_t = a_low_t;
     job.b_low = b_low;
     job.c_zero = zero_c ? c : nullptr;
+    job.vec_a = (k % 4 == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0) ? 1 : 0;
+    job.vec_b = (n % 4 == 0 && reinterpret_cast<uintptr_t>(b) % 16 == 0) ? 1 : 0;
+    job.vec_c = ((m * n) % 4 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0) ? 1 : 0;
     job.m = (int)m;
     job.k = (int)k;
     job.n = (int)n;
@@ -417,7 +443,7 @@ int64_t launch_split_q16_ab(DeviceCtx* ctx, const int32_t* a, const int32_t* b, 
     job.np = np;
     job.mp = mp;
     const int64_t a_blocks = ((k + 63) / 64) * ((m + 63) / 64);
-    int64_t b_blocks = (k * (n / 4) + 1023) / 1024, z_blocks = zero_c ? (m * n / 4 + 2047) / 2048 : 0;
+    int64_t b_blocks = (k * ((n + 3) / 4) + 1023) / 1024, z_blocks = zero_c ? (m * n / 4 + 2047) / 2048 + 1 : 0;
     if (b_blocks > ctx->sm_count * 16) b_blocks = ctx->sm_count * 16;
     if (z_blocks > ctx->sm_count * 8) z_blocks = ctx->sm_count * 8;
     if (a_blocks + b_blocks + z_blocks > 0x7fffffff) return fail(MIND_B200_ERR_TOO_LARGE, "operand split grid too large");

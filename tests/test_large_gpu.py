@@ -408,6 +408,29 @@ def test_q16_fused_kernel_under_producer_lag(gpu):
     gpu.set_gemm_path(0)
 
 
+def test_q16_fused_ragged_and_unaligned_device_operands(gpu):
+    """Device operands one element past a 16-byte boundary, K and N not multiples of 4: the fused
+    kernel's operand split reads them element by element, and a C that a tensor map cannot
+    address is written by the warps themselves (stores for whole-K runs, red.global.add otherwise)."""
+    for (m, k, n, off) in ((777, 1030, 515, 1), (640, 512, 384, 1), (300, 2049, 130, 0), (129, 4099, 131, 3)):
+        seed = 0xDEADBEEF00000000 ^ (m * 131 + k * 17 + n)
+        abuf = lcg_dev(gpu, m * k + off, 0, seed, shift=0)
+        bbuf = lcg_dev(gpu, k * n + off, 0, seed, offset=m * k + off, shift=0)
+        a, b = abuf[off:], bbuf[off:]
+        cbuf = torch.full((m * n + off + 8,), 0x5A5A5A5A, dtype=torch.int32, device="cuda")
+        c = cbuf[off:]
+        want = torch.empty(m * n, dtype=torch.int32, device="cuda")
+        gpu.set_gemm_path(1)
+        gpu.matmul_mm_q16_v(a, b, want, m, k, n)
+        gpu.set_gemm_path(7)
+        for _ in range(3):
+            gpu.matmul_mm_q16_v(a, b, c, m, k, n)
+            gpu.synchronize()
+            assert torch.equal(c[: m * n], want), (m, k, n, off)
+            assert bool((c[m * n :] == 0x5A5A5A5A).all()) and bool((cbuf[:off] == 0x5A5A5A5A).all())
+    gpu.set_gemm_path(0)
+
+
 def test_cuda_graph_capture_and_replay(gpu):
     """Device-pointer calls are plain stream work: after one warm-up call (scratch sized, kernel
     attributes set) they can be captured into a CUDA graph and replayed, the two-stream Q16.16

@@ -199,26 +199,33 @@ def test_random_shapes_all_kernels(gpu):
 
 
 def test_random_shapes_fused_q16(gpu):
-    """Seeded random shapes through the fused Q16.16 kernel (forced at every size): K and N multiples
-    of 4 as the tensor-core forms need, M anything, tiles ragged on every side, one to several
-    hundred stream-K units per CTA, full-range operands, against the CPU oracle."""
+    """Seeded random shapes through the fused Q16.16 kernel (forced at every size): half of them
+    with K and N multiples of 4 (16-byte loads, tensor stores), half fully ragged (element-wise
+    operand split, the warp's own stores), some with every operand one element off a 16-byte
+    boundary; tiles ragged on every side, one to several hundred stream-K units per CTA,
+    full-range operands, against the CPU oracle."""
     rng = np.random.default_rng(20260202)
     gpu.set_gemm_path(7)
     try:
-        for t in range(14):
+        for t in range(20):
             m = int(rng.integers(1, 700))
             k = int(rng.integers(1, 200)) * 4
             n = int(rng.integers(1, 180)) * 4
+            if t % 2 == 1:
+                k, n = int(rng.integers(1, 800)), int(rng.integers(1, 700))
             if t == 0:
                 m, k, n = 129, 36, 132          # a unit and a bit, two tiles and a bit
             if t == 1:
-                m, k, n = 1, 4, 4
+                m, k, n = 1, 1, 1
             g = O.Lcg(int(rng.integers(1, 2**62)))
-            a, b = g.q16(m * k, 0), g.q16(k * n, 0)
-            c = np.full(m * n + 8, 0x5A5A5A5A, dtype=np.int32)
+            off = 1 if t % 4 >= 2 else 0        # operands one element past a 16-byte boundary
+            abuf, bbuf = g.q16(m * k + off, 0), g.q16(k * n + off, 0)
+            a, b = abuf[off:], bbuf[off:]
+            cbuf = np.full(m * n + 8 + off, 0x5A5A5A5A, dtype=np.int32)
+            c = cbuf[off:]
             gpu.matmul_mm_q16_v(a, b, c, m, k, n)
-            assert np.array_equal(c[: m * n], O.gemm_q16(a, b, m, k, n)), (m, k, n)
-            assert np.all(c[m * n :] == 0x5A5A5A5A)
+            assert np.array_equal(c[: m * n], O.gemm_q16(np.ascontiguousarray(a), np.ascontiguousarray(b), m, k, n)), (m, k, n, off)
+            assert np.all(c[m * n :] == 0x5A5A5A5A) and (off == 0 or cbuf[0] == 0x5A5A5A5A)
     finally:
         gpu.set_gemm_path(0)
 
