@@ -280,12 +280,14 @@ def run_reference(args, w):
 
 
 # ------------------------------------------------------------------- GPU arm
-def quick_workload(name, blas, torch, stream, dist=None, world=1, rank=0, steps=30, l2="rotate"):
+def quick_workload(name, blas, torch, stream, dist=None, world=1, rank=0, steps=30, l2="rotate", size=0):
     """Device-resident timing of one of the other benchmark configurations, row-sharded over
     the ranks like the headline workload (each rank its band, max over ranks).  Compact: value,
     unit, kernel_only (the compute kernels without operand re-layout) and its roofline fraction."""
     from mind_b200.shard import row_band
     w = WORKLOADS[name]
+    if size:  # the same workload at another (square) size
+        w = dict(w, m=size, k=size, n=size)
     m, k, n, kind = w["m"], w["k"], w["n"], w["kind"]
     r0, r1 = row_band(m, world, rank)
     rows = max(r1 - r0, 1)
@@ -871,6 +873,9 @@ def run_mine(args, w):
         torch.cuda.empty_cache()
         others = {name: quick_workload(name, blas, torch, stream, dist, world, rank, l2=args.l2)
                   for name in ("gemm_q16", "gemv_q16", "gemm_i16")}
+        # (cfg 2 is 1024^3, where set-up and two tile epilogues are a third of the kernel: the same at 4096^3)
+        others["gemm_q16_4096"] = quick_workload("gemm_q16", blas, torch, stream, dist, world, rank, steps=10,
+                                                 l2=args.l2, size=4096)
         if world == 1:
             others.update(latency_workloads(blas, torch, stream))
 
