@@ -329,14 +329,16 @@ gemm_q16_fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_co
                         a2[4 * g + 2] = ((uint64_t)v.z << 32) | v.z; a2[4 * g + 3] = ((uint64_t)v.w << 32) | v.w;
                         b2[2 * g] = ((uint64_t)w.y << 32) | w.x; b2[2 * g + 1] = ((uint64_t)w.w << 32) | w.z;
                     }
-                    // B pair outermost, rows walked forwards and backwards in turn: every FMA shares an
-                    // operand register with the one before it (2.53 ms at 4096^3 against 2.58 ms with rows
-                    // outermost and 2.55 ms without the serpentine)
+                    // B pair outermost (in the order 0, 2, 1, 3: consecutive pairs come from different
+                    // loads), rows walked forwards and backwards in turn, so that every FMA shares an
+                    // operand register with the one before it.  Kernel at 4096^3: 2.51 ms; rows outermost
+                    // 2.58 ms, pairs in order 2.52 ms, without the serpentine 2.55 ms.
 #pragma unroll
-                    for (int jp = 0; jp < 4; ++jp)
+                    for (int jj = 0; jj < 4; ++jj)
 #pragma unroll
                         for (int ii = 0; ii < 8; ++ii) {
-                            const int i = (jp & 1) ? 7 - ii : ii;
+                            const int jp = ((jj & 1) << 1) | (jj >> 1);
+                            const int i = (jj & 1) ? 7 - ii : ii;
                             chain[i][jp] = fma2_rm(a2[i], b2[jp], chain[i][jp]);
                         }
                 }
