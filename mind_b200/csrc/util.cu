@@ -127,12 +127,19 @@ __global__ void fp32_fma_peak_kernel(float* __restrict__ sink, int iters, float 
         const unsigned int lo = __float_as_uint(y + 0.25f * (float)j), hi = __float_as_uint(y + 0.125f * (float)j);
         b[j] = ((unsigned long long)hi << 32) | lo;
     }
+    // 2 x 2 blocks of the tile walked in a ring (every FMA shares an operand register with the one
+    // before it): the fastest of the orders tried for a register-only loop (32.0 TFMA/s; rows
+    // outermost 30.4, columns outermost 31.5, serpentine 31.7, a scalar fma.rm.f32 8 x 8 tile 28.0)
     for (int it = 0; it < iters; ++it) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+        for (int i = 0; i < 8; i += 2)
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int j = 0; j < 4; j += 2) {
                 asm volatile("fma.rm.f32x2 %0, %1, %2, %0;" : "+l"(acc[i][j]) : "l"(a[i]), "l"(b[j]));
+                asm volatile("fma.rm.f32x2 %0, %1, %2, %0;" : "+l"(acc[i][j + 1]) : "l"(a[i]), "l"(b[j + 1]));
+                asm volatile("fma.rm.f32x2 %0, %1, %2, %0;" : "+l"(acc[i + 1][j + 1]) : "l"(a[i + 1]), "l"(b[j + 1]));
+                asm volatile("fma.rm.f32x2 %0, %1, %2, %0;" : "+l"(acc[i + 1][j]) : "l"(a[i + 1]), "l"(b[j]));
+            }
     }
     unsigned long long t = 0;
 #pragma unroll
