@@ -11,7 +11,10 @@
 // last (recording the CUDA event that the kernels wait for), and the submitting thread can wait
 // on the host until that has happened.
 //
-// The slots are pinned once (first pageable call) and freed at shutdown.
+// The slots are pinned once (first pageable call) and freed at shutdown.  Upload slots are
+// write-combined (the host only writes them; measured 41.5 - 42.9 ms against 44.5 - 46.4 ms for the
+// 16384^3 int8 call with pageable operands, same host, alternating runs); download slots are not
+// (the host reads them).
 #include <condition_variable>
 #include <deque>
 #include <stdlib.h>
@@ -75,7 +78,9 @@ public:
         std::unique_lock<std::mutex> lk(mu_);
         idle_.wait(lk, [&] { return open_ == 0; });
     }
-    bool start() {
+    // write_combined: for slots the CPU only WRITES (uploads): streaming stores on the host side,
+    // no cache snoops on the DMA side.  Never for slots the CPU reads.
+    bool start(bool write_combined = false) {
         std::lock_guard<std::mutex> lk(mu_);
         if (started_) return ok_;
         started_ = true;
@@ -84,7 +89,8 @@ public:
         for (int t = 0; t < n_threads_ && ok_; ++t)
             for (int s = 0; s < SLOTS_PER_THREAD; ++s) {
                 Slot& sl = slots_[t][s];
-                if (cudaHostAlloc(&sl.ptr, SLOT_BYTES, cudaHostAllocPortable) != cudaSuccess) {
+                if (cudaHostAlloc(&sl.ptr, SLOT_BYTES,
+                                  cudaHostAllocPortable | (write_combined ? cudaHostAllocWriteCombined : 0)) != cudaSuccess) {
                     cudaGetLastError();
                     ok_ = false;
                     break;
@@ -188,7 +194,7 @@ void StageGroup::wait() {
     cv.wait(lk, [&] { return done; });
 }
 
-bool stager_start() { return up_team().start() && down_team().start(); }
+bool stager_start() { return up_team().start(true) && down_team().start(false); }
 
 size_t stager_slot_bytes() { return SLOT_BYTES; }
 
