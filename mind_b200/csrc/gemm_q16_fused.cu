@@ -35,6 +35,8 @@
 //
 // Every wait is an mbarrier wait bounded in time; when one runs out the CTA's roles leave their
 // loops, the error word is set and the kernel ends normally.
+#include <type_traits>
+
 #include "common.h"
 #include "ptx.cuh"
 
@@ -95,6 +97,10 @@ __device__ __forceinline__ Run next_run(long long& u, long long u_end, int k_uni
     return r;
 }
 
+// EDGE: the product has tiles whose second half (rows or columns 64..127) is all padding, and many
+// of them (a narrow N or M): those tiles skip the padding's loads and FMAs.  A build of its own,
+// because the extra paths cost the whole-tile loop 4 % through a different instruction schedule.
+template <bool EDGE>
 __global__ void __launch_bounds__(FUSED_THREADS, 1)
 gemm_q16_fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
                       const __grid_constant__ CUtensorMap tm_a2, const __grid_constant__ CUtensorMap tm_a3,
@@ -298,6 +304,7 @@ gemm_q16_fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_co
             };
 
             const int fsteps = (r.ku1 - r.ku0) * (UNIT_K / FSTEP);
+            const bool half_m = EDGE && row0 + 64 >= p.m, half_n = EDGE && col0 + 64 >= p.n;  // the second half is all padding
             int since = 0;
             for (int fs = 0; fs < fsteps; ++fs, ++it) {
                 const uint32_t s = it % FSTAGES, ph = (it / FSTAGES) & 1u;
@@ -309,39 +316,91 @@ gemm_q16_fused_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_co
                 // (landed - one = 0: the stage's address depends on the outcome of the wait)
                 const float* const fa_s = f_tile + s * (F_STAGE_BYTES / 4) + (landed - p.one);
                 const float* const fb_s = fa_s + F_HALF_BYTES / 4;
-                // fragments of step kk + 1 are fetched while those of step kk are multiplied
-                uint4 fa[2][2], fb[2][2];
-                auto fetch = [&](int kk, int slot) {
+                // One stage of FSTEP K steps.  Fragments of step kk + 1 are fetched while those of step kk
+                // are multiplied.  MG / NG: how many of the register tile's two row / column groups
+                // (rows +0..63 / +64..127 of the tile, likewise columns) lie inside C: a tile on the
+                // edge of a narrow product (64 batched queries against a catalogue: N = 64) skips the
+                // loads and the FMAs of the half that is padding.
+                auto stage_fmas = [&](auto mg_tag, auto ng_tag) {
+                    constexpr int MG = decltype(mg_tag)::value, NG = decltype(ng_tag)::value;
+                    uint4 fa[2][2], fb[2][2];
+                    auto fetch = [&](int kk, int slot) {
 #pragma unroll
-                    for (int g = 0; g < 2; ++g) {
-                        fa[slot][g] = *reinterpret_cast<const uint4*>(fa_s + kk * UT + g * 64 + ty * 4);
-                        fb[slot][g] = *reinterpret_cast<const uint4*>(fb_s + kk * UT + g * 64 + tx * 4);
+                        for (int g = 0; g < 2; ++g) {
+                            if (g < MG) fa[slot][g] = *reinterpret_cast<const uint4*>(fa_s + kk * UT + g * 64 + ty * 4);
+                            if (g < NG) fb[slot][g] = *reinterpret_cast<const uint4*>(fb_s + kk * UT + g * 64 + tx * 4);
+                        }
+                    };
+                    fetch(0, 0);
+#pragma unroll
+                    for (int kk = 0; kk < FSTEP; ++kk) {
+                        if (kk + 1 < FSTEP) fetch(kk + 1, (kk + 1) & 1);
+                        uint64_t a2[8], b2[4];
+#pragma unroll
+                        for (int g = 0; g < 2; ++g) {
+                            if (g < MG) {
+                                const uint4 v = fa[kk & 1][g];
+                                a2[4 * g] = ((uint64_t)v.x << 32) | v.x; a2[4 * g + 1] = ((uint64_t)v.y << 32) | v.y;
+                                a2[4 * g + 2] = ((uint64_t)v.z << 32) | v.z; a2[4 * g + 3] = ((uint64_t)v.w << 32) | v.w;
+                            }
+                            if (g < NG) {
+                                const uint4 w = fb[kk & 1][g];
+                                b2[2 * g] = ((uint64_t)w.y << 32) | w.x; b2[2 * g + 1] = ((uint64_t)w.w << 32) | w.z;
+                            }
+                        }
+                        // B pair outermost (in the order 0, 2, 1, 3: consecutive pairs come from different
+                        // loads), rows walked forwards and backwards in turn, so that every FMA shares an
+                        // operand register with the one before it.  Kernel at 4096^3: 2.51 ms; rows outermost
+                        // 2.58 ms, pairs in order 2.52 ms, without the serpentine 2.55 ms.
+#pragma unroll
+                        for (int jj = 0; jj < 4; ++jj)
+#pragma unroll
+                            for (int ii = 0; ii < 8; ++ii) {
+                                const int jp = ((jj & 1) << 1) | (jj >> 1);
+                                const int i = (jj & 1) ? 7 - ii : ii;
+                                if (jp < 2 * NG && i < 4 * MG) chain[i][jp] = fma2_rm(a2[i], b2[jp], chain[i][jp]);
+                            }
                     }
                 };
-                fetch(0, 0);
+                using one_t = std::integral_constant<int, 1>;
+                using two_t = std::integral_constant<int, 2>;
+                if (!EDGE || (!half_m && !half_n)) {
+                    // (the whole tile, written out on its own)
+                    uint4 fa[2][2], fb[2][2];
+                    auto fetch = [&](int kk, int slot) {
 #pragma unroll
-                for (int kk = 0; kk < FSTEP; ++kk) {
-                    if (kk + 1 < FSTEP) fetch(kk + 1, (kk + 1) & 1);
-                    uint64_t a2[8], b2[4];
-#pragma unroll
-                    for (int g = 0; g < 2; ++g) {
-                        const uint4 v = fa[kk & 1][g], w = fb[kk & 1][g];
-                        a2[4 * g] = ((uint64_t)v.x << 32) | v.x; a2[4 * g + 1] = ((uint64_t)v.y << 32) | v.y;
-                        a2[4 * g + 2] = ((uint64_t)v.z << 32) | v.z; a2[4 * g + 3] = ((uint64_t)v.w << 32) | v.w;
-                        b2[2 * g] = ((uint64_t)w.y << 32) | w.x; b2[2 * g + 1] = ((uint64_t)w.w << 32) | w.z;
-                    }
-                    // B pair outermost (in the order 0, 2, 1, 3: consecutive pairs come from different
-                    // loads), rows walked forwards and backwards in turn, so that every FMA shares an
-                    // operand register with the one before it.  Kernel at 4096^3: 2.51 ms; rows outermost
-                    // 2.58 ms, pairs in order 2.52 ms, without the serpentine 2.55 ms.
-#pragma unroll
-                    for (int jj = 0; jj < 4; ++jj)
-#pragma unroll
-                        for (int ii = 0; ii < 8; ++ii) {
-                            const int jp = ((jj & 1) << 1) | (jj >> 1);
-                            const int i = (jj & 1) ? 7 - ii : ii;
-                            chain[i][jp] = fma2_rm(a2[i], b2[jp], chain[i][jp]);
+                        for (int g = 0; g < 2; ++g) {
+                            fa[slot][g] = *reinterpret_cast<const uint4*>(fa_s + kk * UT + g * 64 + ty * 4);
+                            fb[slot][g] = *reinterpret_cast<const uint4*>(fb_s + kk * UT + g * 64 + tx * 4);
                         }
+                    };
+                    fetch(0, 0);
+#pragma unroll
+                    for (int kk = 0; kk < FSTEP; ++kk) {
+                        if (kk + 1 < FSTEP) fetch(kk + 1, (kk + 1) & 1);
+                        uint64_t a2[8], b2[4];
+#pragma unroll
+                        for (int g = 0; g < 2; ++g) {
+                            const uint4 v = fa[kk & 1][g], w = fb[kk & 1][g];
+                            a2[4 * g] = ((uint64_t)v.x << 32) | v.x; a2[4 * g + 1] = ((uint64_t)v.y << 32) | v.y;
+                            a2[4 * g + 2] = ((uint64_t)v.z << 32) | v.z; a2[4 * g + 3] = ((uint64_t)v.w << 32) | v.w;
+                            b2[2 * g] = ((uint64_t)w.y << 32) | w.x; b2[2 * g + 1] = ((uint64_t)w.w << 32) | w.z;
+                        }
+#pragma unroll
+                        for (int jj = 0; jj < 4; ++jj)
+#pragma unroll
+                            for (int ii = 0; ii < 8; ++ii) {
+                                const int jp = ((jj & 1) << 1) | (jj >> 1);
+                                const int i = (jj & 1) ? 7 - ii : ii;
+                                chain[i][jp] = fma2_rm(a2[i], b2[jp], chain[i][jp]);
+                            }
+                    }
+                } else if (!half_m) {
+                    stage_fmas(two_t{}, one_t{});
+                } else if (!half_n) {
+                    stage_fmas(one_t{}, two_t{});
+                } else {
+                    stage_fmas(one_t{}, one_t{});
                 }
                 // Release the stage only once every lane's last fragments have been USED.  With a plain
                 // __syncwarp() before lane 0's arrive, the last A fragment of a stage (its last K step)
@@ -515,9 +574,12 @@ bool gemm_q16_fused_usable(DeviceCtx* ctx) {
     static thread_local bool usable = false;
     if (asked_dev != ctx->device) {
         cudaFuncAttributes fa;
-        usable = cudaFuncGetAttributes(&fa, gemm_q16_fused_kernel) == cudaSuccess && fa.numRegs == 168 &&
-                 cudaFuncSetAttribute(gemm_q16_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      FUSED_SMEM) == cudaSuccess;
+        usable = true;
+        for (int edge = 0; edge < 2 && usable; ++edge) {
+            const void* kern = edge ? (const void*)gemm_q16_fused_kernel<true> : (const void*)gemm_q16_fused_kernel<false>;
+            usable = cudaFuncGetAttributes(&fa, kern) == cudaSuccess && fa.numRegs == 168 &&
+                     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FUSED_SMEM) == cudaSuccess;
+        }
         cudaGetLastError();
         asked_dev = ctx->device;
     }
@@ -579,8 +641,15 @@ int64_t launch_gemm_q16_fused(DeviceCtx* ctx, const uint8_t* const a_limb[4], co
     lc.attrs = at;
     lc.numAttrs = 1;
     prof_begin(ctx);
-    MB200_CUDA(cudaLaunchKernelEx(&lc, gemm_q16_fused_kernel, ta[0], ta[1], ta[2], ta[3], tb[0], tb[1], tb[2], tb[3], taf,
-                                  tbf, tc, p));
+    // tiles whose second half is padding: worth the EDGE build when they are a quarter of all tiles or more
+    const int64_t half_rows = (m - 1) % UT < 64 ? n_tiles : 0, half_cols = (n - 1) % UT < 64 ? m_tiles : 0;
+    const bool edge = 4 * (half_rows + half_cols) >= m_tiles * n_tiles;
+    if (edge)
+        MB200_CUDA(cudaLaunchKernelEx(&lc, gemm_q16_fused_kernel<true>, ta[0], ta[1], ta[2], ta[3], tb[0], tb[1], tb[2],
+                                      tb[3], taf, tbf, tc, p));
+    else
+        MB200_CUDA(cudaLaunchKernelEx(&lc, gemm_q16_fused_kernel<false>, ta[0], ta[1], ta[2], ta[3], tb[0], tb[1], tb[2],
+                                      tb[3], taf, tbf, tc, p));
     prof_end(ctx);
     count_launch();
     return check_launch("gemm_q16_fused_kernel");
