@@ -212,16 +212,20 @@ int64_t mind_b200_profile(int64_t enable);
 int64_t mind_b200_profile_read(int64_t* launches_out, double* total_ms_out);
 
 /* Measured FP64 FMA rate of the current device (FMA per second): a register-only fma.rm.f64
- * loop timed with CUDA events; the ceiling of the Q16.16 GEMM's per-product floor, which is one
- * such FMA per product.  sm_mhz_out (may be NULL) receives the SM clock the loop ran at (cycle
+ * loop timed with CUDA events; the ceiling of the Q16.16 GEMM in the forms that keep the
+ * per-product floor on the FP64 pipe (one such FMA per product: the single-kernel form of small
+ * products and set_gemm_path(14)).  sm_mhz_out (may be NULL) receives the SM clock the loop ran at (cycle
  * counter over wall clock inside the kernel).  Synchronous; a few milliseconds. */
 int64_t mind_b200_fp64_fma_peak(double* fma_per_s_out, double* sm_mhz_out);
 /* The same for the FP32 pipe in its packed round-down form (fma.rm.f32x2, two FMAs per
- * instruction, both counted): the ceiling of the Q16.16 GEMM's floor kernel in its default form,
- * which spends one FP32 FMA per product on floor((a & 0xffff) * (b & 0xffff) / 65536). */
+ * instruction, both counted): the ceiling of the Q16.16 GEMM in its default form for large
+ * products (the fused kernel), which spends one FP32 FMA per product on
+ * floor((a & 0xffff) * (b & 0xffff) / 65536) while the tensor cores form the linear terms. */
 int64_t mind_b200_fp32_fma_peak(double* fma_per_s_out, double* sm_mhz_out);
-/* Q16.16 GEMM hybrid, measurement knob: SMs given to the tensor-core half while the floor kernel
- * runs beside it on the others; 0 = the halves in sequence, -1 = chosen by size (the default). */
+/* Q16.16 GEMM in its two-kernel forms (set_gemm_path 8 / 9 / 14), measurement knob: SMs given to
+ * the tensor-core half while the floor kernel runs beside it on the others; 0 = the halves in
+ * sequence, -1 = chosen by size (the default).  Any value other than -1 also keeps the fused
+ * kernel from being chosen. */
 int64_t mind_b200_set_q16_split(int64_t side_sms);
 
 /* ---- seeded inputs and large-shape checking on the device ------------------------------------- */
